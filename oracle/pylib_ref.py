@@ -1,0 +1,190 @@
+"""NumPy restatement of the pylib glue around the custom ops (TEST
+INFRASTRUCTURE ONLY; see ``oracle/__init__.py``).
+
+Follows the reference's Python callers so that the oracle can be driven exactly
+the way pylib drives the ops:
+  AABB        pylib/pc/PointCloud.py:38-43
+  Grid        pylib/pc/Grid.py:32-83
+  Neighborhood pylib/pc/Neighborhood.py:218-311
+  sample / PointHierarchy  pylib/pc/sampling.py:123-150, PointHierarchy.py:40-98
+  MCConv      pylib/pc/layers/MCConv.py:137-278
+All arithmetic that feeds the ops is done in float32 like the TF code.
+"""
+import numpy as np
+
+import oracle as orc
+
+F32 = np.float32
+
+
+def aabb(points, batch_ids, batch_size):
+  """PointCloud.py:38-43: unsorted_segment_min/max -+ 1e-9 (float32)."""
+  points = np.asarray(points, F32)
+  d = points.shape[1]
+  mn = np.full((batch_size, d), np.inf, F32)
+  mx = np.full((batch_size, d), -np.inf, F32)
+  np.minimum.at(mn, batch_ids, points)
+  np.maximum.at(mx, batch_ids, points)
+  return (mn - F32(1e-9)).astype(F32), (mx + F32(1e-9)).astype(F32)
+
+
+class Grid:
+  """Grid.py:32-83."""
+
+  def __init__(self, points, batch_ids, batch_size, cell_sizes, fused=True):
+    points = np.ascontiguousarray(points, F32)
+    batch_ids = np.ascontiguousarray(batch_ids, np.int32)
+    d = points.shape[1]
+    cell_sizes = np.asarray(cell_sizes, F32).reshape(-1)
+    if cell_sizes.shape[0] == 1:
+      cell_sizes = np.repeat(cell_sizes, d)
+    self.points, self.batch_ids, self.batch_size = points, batch_ids, batch_size
+    self.cell_sizes = cell_sizes
+    self.aabb_min, self.aabb_max = aabb(points, batch_ids, batch_size)
+    sizes = (self.aabb_max - self.aabb_min).astype(F32)
+    bnc = np.ceil((sizes / cell_sizes).astype(F32)).astype(np.int32)
+    self.num_cells = np.maximum(bnc.max(axis=0), 1).astype(np.int32)
+    # custom_ops_wrapper.py:37-43
+    self.scaled_aabb_min = (self.aabb_min / cell_sizes).astype(F32)
+    self.inv_cell_sizes = (F32(1.0) / cell_sizes).astype(F32)
+    self.keys = orc.compute_keys(points, batch_ids, self.scaled_aabb_min,
+                                 self.num_cells, self.inv_cell_sizes, fused)
+    self.sorted_indices, self.sorted_keys = orc.sort_keys_desc(self.keys)
+    self.sorted_points = points[self.sorted_indices]
+    self.sorted_batch_ids = batch_ids[self.sorted_indices]
+    self.fused = fused
+    self._ds = None
+
+  def get_ds(self):
+    if self._ds is None:
+      self._ds = orc.build_grid_ds(self.sorted_keys, self.num_cells,
+                                   self.batch_size)
+    return self._ds
+
+
+class Neighborhood:
+  """Neighborhood.py:218-311."""
+
+  def __init__(self, grid, radii, samples=None, samples_batch_ids=None,
+               max_neighbors=0):
+    d = grid.points.shape[1]
+    radii = np.asarray(radii, F32).reshape(-1)
+    if radii.shape[0] == 1:
+      radii = np.repeat(radii, d)
+    self.grid, self.radii = grid, radii
+    self.equal_samples = samples is None
+    if samples is None:
+      samples, samples_batch_ids = grid.sorted_points, grid.sorted_batch_ids
+    self.samples = np.ascontiguousarray(samples, F32)
+    self.samples_batch_ids = np.ascontiguousarray(samples_batch_ids, np.int32)
+    self.ranges, self.neighbors = orc.find_neighbors(
+        self.samples, self.samples_batch_ids, grid.sorted_points,
+        grid.sorted_keys, grid.num_cells, grid.scaled_aabb_min,
+        grid.inv_cell_sizes, (F32(1.0) / radii).astype(F32), max_neighbors,
+        grid.fused)
+    self.original_neigh_ids = np.stack(
+        [grid.sorted_indices[self.neighbors[:, 0]], self.neighbors[:, 1]],
+        axis=1).astype(np.int32)
+    self._pdf = None
+
+  def get_pdf(self, bandwidth=0.2, mode=0):
+    """Neighborhood.py:257-311 (KDEMode.constant = 0, num_points = 1)."""
+    if self._pdf is None:
+      d = self.samples.shape[1]
+      bw = np.asarray(bandwidth, F32).reshape(-1)
+      if bw.shape[0] == 1:
+        bw = np.repeat(bw, d)
+      nb = self if self.equal_samples else Neighborhood(self.grid, self.radii)
+      self.point_pdf = orc.compute_pdf(
+          self.grid.sorted_points, nb.neighbors, nb.ranges,
+          (F32(1.0) / bw).astype(F32), (F32(1.0) / self.radii).astype(F32), mode)
+      self._pdf = self.point_pdf[self.neighbors[:, 0]]
+    return self._pdf
+
+
+def sample(neigh, mode):
+  """sampling.py:123-150; mode 0 = Poisson disk, 1 = cell average.  Returns
+  (points, batch_ids, original indices or None)."""
+  g = neigh.grid
+  pts, bids, idx = orc.sampling(g.sorted_points, g.sorted_batch_ids,
+                                g.sorted_keys, g.num_cells, neigh.neighbors,
+                                neigh.ranges, mode)
+  if mode == 0:
+    return pts, bids, g.sorted_indices[idx]
+  return pts, bids, None
+
+
+def point_hierarchy(points, batch_ids, batch_size, cell_sizes, mode=0):
+  """PointHierarchy.py:40-98: per level Grid -> self Neighborhood -> sample."""
+  levels = [(np.asarray(points, F32), np.asarray(batch_ids, np.int32), None)]
+  cur_p, cur_b = levels[0][0], levels[0][1]
+  for cs in cell_sizes:
+    g = Grid(cur_p, cur_b, batch_size, cs)
+    nb = Neighborhood(g, cs)
+    cur_p, cur_b, idx = sample(nb, mode)
+    levels.append((cur_p, cur_b, idx))
+  return levels
+
+
+def brute_force_neighbors(samples, samples_batch_ids, points, batch_ids, radii):
+  """custom_ops_tf.py:216-258 (find_neighbors_no_grid) with the strict `<` of
+  the CUDA kernel; float32 arithmetic in the kernel's order.  Returns a list of
+  sorted index arrays, one per sample (indices into `points`)."""
+  samples = np.asarray(samples, F32); points = np.asarray(points, F32)
+  inv_r = (F32(1.0) / np.asarray(radii, F32)).astype(F32)
+  out = []
+  for s in range(samples.shape[0]):
+    t = ((samples[s][None, :] - points).astype(F32) * inv_r).astype(F32)
+    d2 = (t[:, 0] * t[:, 0]).astype(F32)
+    for d in range(1, points.shape[1]):
+      # fma(t,t,d2): exact product in float64, one rounding
+      d2 = (t[:, d].astype(np.float64) * t[:, d].astype(np.float64)
+            + d2.astype(np.float64)).astype(F32)
+    ok = (np.sqrt(d2).astype(F32) < F32(1.0)) & (batch_ids == samples_batch_ids[s])
+    out.append(np.nonzero(ok)[0])
+  return out
+
+
+def leaky_relu(x, alpha=0.2):
+  """tf.nn.leaky_relu default alpha (MCConv.py:27-31)."""
+  return np.where(x > 0, x, x * F32(alpha)).astype(F32)
+
+
+def mcconv_basis(points_in, points_out, neigh, pdf, w1, b1, radius):
+  """MCConv.py:264-269 and :163-171 for a one-hidden-layer kernel MLP.
+  w1 [num_mlps, D, H], b1 [num_mlps, 1, H] -> basis [M, num_mlps*H]."""
+  ids = neigh.original_neigh_ids
+  diff = ((points_in[ids[:, 0]] - points_out[ids[:, 1]]) / F32(radius)).astype(F32)
+  hid = np.einsum('md,gdh->gmh', diff, w1).astype(F32) + b1
+  hid = leaky_relu(hid)
+  hid = np.transpose(hid, (1, 0, 2)).reshape(diff.shape[0], -1)
+  return (hid / pdf.reshape(-1, 1)).astype(F32), diff, hid
+
+
+def mcconv_forward(features, basis, neigh, wf):
+  """MCConv.py:174-194.  wf [num_mlps, Cin*H, Cout/num_mlps] -> [Ns, Cout]."""
+  g = wf.shape[0]
+  cin = features.shape[1]
+  x = orc.basis_proj(basis, features, neigh.original_neigh_ids, neigh.ranges)
+  ns, _, k = x.shape
+  h = k // g
+  xg = np.transpose(x.reshape(ns, cin, g, h), (2, 0, 1, 3)).reshape(g, ns, cin * h)
+  out = np.matmul(xg.astype(np.float64), wf.astype(np.float64))
+  return np.transpose(out, (1, 0, 2)).reshape(ns, -1).astype(F32), x
+
+
+def mcconv_backward(features, basis, neigh, wf, x, d_out):
+  """Analytic gradients of mcconv_forward: returns (d_wf, d_basis, d_feat)."""
+  g = wf.shape[0]
+  ns, cin, k = x.shape
+  h = k // g
+  co = wf.shape[2]
+  dog = np.transpose(d_out.reshape(ns, g, co), (1, 0, 2)).astype(np.float64)
+  xg = np.transpose(x.reshape(ns, cin, g, h), (2, 0, 1, 3)).reshape(g, ns, cin * h)
+  d_wf = np.matmul(np.transpose(xg, (0, 2, 1)).astype(np.float64), dog).astype(F32)
+  dxg = np.matmul(dog, np.transpose(wf, (0, 2, 1)).astype(np.float64))
+  dx = np.transpose(dxg.reshape(g, ns, cin, h), (1, 2, 0, 3)).reshape(ns, cin, k)
+  d_basis, d_feat = orc.basis_proj_grads(basis, features,
+                                         neigh.original_neigh_ids, neigh.ranges,
+                                         dx.astype(F32))
+  return d_wf, d_basis, d_feat, dx.astype(F32)
