@@ -1,0 +1,196 @@
+/*
+ * tfgpc.h -- C ABI of the B200 (sm_100a) implementation of the tfg_custom_ops
+ * hot path of schellmi42/tensorflow_graphics_point_clouds.
+ *
+ * Every entry point takes plain pointers and sizes.  Unless a parameter is
+ * marked [host], pointers are device pointers valid on the current CUDA
+ * device; `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * Work is enqueued on `stream` and the call returns without synchronising,
+ * except for the *_count entry points, which block on the stream once to
+ * return a dynamic output size (the reference blocks at the same places:
+ * find_neighbors/cc/kernels/scan_alg_kernels.cu.cc:253-265,
+ * sampling/cc/kernels/count_sampling_pd_kernels.cu.cc:184-197).
+ *
+ * Return value: 0 on success, otherwise one of TFGPC_E*; the message of the
+ * last failure on the calling thread is returned by tfgpc_last_error().  The
+ * library never exits the process (the reference does on CUDA errors,
+ * shared/cc/kernels/tf_gpu_device.cpp:89-100) and never allocates device
+ * memory: scratch is passed in by the caller as `ws` / `ws_bytes`, sized by
+ * the matching *_workspace_bytes() query (the reference takes it from
+ * allocate_temp, shared/cc/kernels/tf_gpu_device.cpp:122-142).
+ *
+ * Index conventions kept from the reference:
+ *   - keys are sorted in DESCENDING order (pylib/pc/Grid.py:56-57);
+ *   - ranges[s] is the END offset of sample s in the neighbor list (inclusive
+ *     prefix sum); its start is ranges[s-1], or 0 for s == 0;
+ *   - a neighbor entry is the int pair (point index, sample index).
+ * Orders the reference leaves to atomics are fixed here: neighbor lists are
+ * ascending in point index within each sample, Poisson samples are ascending
+ * in point index, cell-average samples are ascending in first point index.
+ */
+#ifndef TFGPC_H_
+#define TFGPC_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TFGPC_OK 0
+#define TFGPC_EINVAL 1   /* bad argument (the reference's InvalidArgument) */
+#define TFGPC_ECUDA 2    /* a CUDA call failed */
+#define TFGPC_ENOMEM 3   /* workspace too small */
+#define TFGPC_ETIMEOUT 4 /* a bounded device-side wait ran out */
+
+#define TFGPC_MIN_DIMS 2 /* shared/cc/kernels/defines.hpp:30-31 */
+#define TFGPC_MAX_DIMS 6
+
+/* Message of the last failed call on this thread ("" if none). */
+const char* tfgpc_last_error(void);
+/* ABI version, bumped when a signature changes. */
+int tfgpc_version(void);
+
+/* ---- ComputeKeys ---------------------------------------------------------
+ * Replaces ComputeKeysOp::Compute (compute_keys/cc/ops/compute_keys_ops.cpp:
+ * 65-117) -> compute_keys_gpu<D> (cc/kernels/compute_keys_kernels.cu.cc:
+ * 76-115).  points [n,D] f32, batch_ids [n] i32, scaled_aabb_min [B,D] f32
+ * (= aabb_min / cell_size), num_cells [D] i32, inv_cell_sizes [D] f32
+ * -> keys [n] i64. */
+int tfgpc_compute_keys(void* stream, int D, int64_t n, const float* points,
+                       const int32_t* batch_ids, int64_t batch_size,
+                       const float* scaled_aabb_min, const int32_t* num_cells,
+                       const float* inv_cell_sizes, int64_t* keys_out);
+
+/* ---- key sort + gather ---------------------------------------------------
+ * Replaces tf.argsort(keys, 'DESCENDING') and the three tf.gather calls of
+ * pylib/pc/Grid.py:56-64.  Stable: equal keys keep the lower original index
+ * first.  key_bits = number of low key bits that can be non-zero (0 = 64).
+ * perm_out [n] i32, sorted_keys_out [n] i64; sorted_points_out [n,D] and
+ * sorted_batch_ids_out [n] may be NULL together to skip the gather. */
+size_t tfgpc_sort_keys_workspace_bytes(int64_t n);
+int tfgpc_sort_keys_desc(void* stream, int D, int64_t n, int key_bits,
+                         const int64_t* keys, const float* points,
+                         const int32_t* batch_ids, int32_t* perm_out,
+                         int64_t* sorted_keys_out, float* sorted_points_out,
+                         int32_t* sorted_batch_ids_out, void* ws,
+                         size_t ws_bytes);
+
+/* ---- BuildGridDs ---------------------------------------------------------
+ * Replaces BuildGridDsOp::Compute (build_grid_ds/cc/ops/build_grid_ds_ops.cpp:
+ * 67-106) -> build_grid_ds_gpu<D> (cc/kernels/build_grid_ds_kernels.cu.cc:
+ * 76-114).  sorted_keys [n] i64, num_cells [D] i32 on the device and the same
+ * values on the host [host] -> ds [batch_size, num_cells[0], num_cells[1], 2]
+ * i32: (first, last+1) index of each (batch, c0, c1) tube, (0,0) if empty. */
+int tfgpc_build_grid_ds(void* stream, int D, int64_t n,
+                        const int64_t* sorted_keys, const int32_t* num_cells,
+                        const int32_t* num_cells_host, int64_t batch_size,
+                        int32_t* ds_out);
+
+/* ---- FindNeighbors -------------------------------------------------------
+ * Replaces FindNeighborsOp::Compute (find_neighbors/cc/ops/
+ * find_neighbors_ops.cpp:86-250) and the kernels it drives
+ * (find_ranges_grid_ds, count_neighbors, scan_alg, elem_wise_min,
+ * store_neighbors).  Two calls, so that the caller owns the dynamic output:
+ *   _count writes ranges_out [ns] i32 (end offsets), blocks on the stream and
+ *          returns the number of pairs M in *total_out [host];
+ *   _fill  writes neigh_out [M,2] i32 in canonical order.
+ * samples [ns,D], samples_batch_ids [ns], points [n,D] (sorted), point_keys
+ * [n] (sorted, descending), ds [batch_size,C0,C1,2], num_cells [D],
+ * scaled_aabb_min [batch_size,D], inv_cell_sizes [D], inv_radii [D].
+ * max_neighs > 0 keeps the first max_neighs neighbors in canonical order (the
+ * reference keeps a time-seeded random subset,
+ * store_neighbors_kernels.cu.cc:51-112,216). */
+size_t tfgpc_find_neighbors_workspace_bytes(int64_t ns);
+int tfgpc_find_neighbors_count(void* stream, int D, int64_t ns,
+                               const float* samples,
+                               const int32_t* samples_batch_ids, int64_t n,
+                               const float* points, const int64_t* point_keys,
+                               const int32_t* ds, int64_t batch_size,
+                               const int32_t* num_cells,
+                               const float* scaled_aabb_min,
+                               const float* inv_cell_sizes,
+                               const float* inv_radii, int max_neighs,
+                               int32_t* ranges_out, void* ws, size_t ws_bytes,
+                               int64_t* total_out);
+int tfgpc_find_neighbors_fill(void* stream, int D, int64_t ns,
+                              const float* samples,
+                              const int32_t* samples_batch_ids, int64_t n,
+                              const float* points, const int64_t* point_keys,
+                              const int32_t* ds, int64_t batch_size,
+                              const int32_t* num_cells,
+                              const float* scaled_aabb_min,
+                              const float* inv_cell_sizes,
+                              const float* inv_radii, int max_neighs,
+                              const int32_t* ranges, int64_t total,
+                              int32_t* neigh_out);
+
+/* ---- ComputePdf / ComputePdfWithPtGrads / ComputePdfPtGrads --------------
+ * Replaces ComputePDFOp::Compute (compute_pdf/cc/ops/compute_pdf_ops.cpp:
+ * 101-154) -> compute_pdf_gpu<D> (cc/kernels/compute_pdf_kernels.cu.cc:
+ * 220-272) and ComputePDFPtGradsOp::Compute (:188-246) ->
+ * compute_pdf_grads_gpu<D> (:275-335).  points [n,D], neighbors [M,2],
+ * ranges [n], inv_bandwidth [D], inv_radii [D]; mode 0 = constant bandwidth,
+ * 1 = sqrt(n) as inverse bandwidth.  pt_grads_out [n,D] is overwritten. */
+int tfgpc_compute_pdf(void* stream, int D, int mode, int64_t n,
+                      const float* points, const int32_t* neighbors, int64_t M,
+                      const int32_t* ranges, const float* inv_bandwidth,
+                      const float* inv_radii, float* pdf_out);
+int tfgpc_compute_pdf_pt_grads(void* stream, int D, int mode, int64_t n,
+                               const float* points, const int32_t* neighbors,
+                               int64_t M, const int32_t* ranges,
+                               const float* inv_bandwidth,
+                               const float* inv_radii, const float* pdf_grads,
+                               float* pt_grads_out);
+
+/* ---- BasisProj / BasisProjGrads ------------------------------------------
+ * Replaces BasisProjOp::Compute (basis_proj/cc/ops/basis_proj_ops.cpp:77-132)
+ * -> basis_proj_gpu<K> (cc/kernels/basis_proj_kernels.cu.cc:132-182) and
+ * BasisProjGradsOp::Compute (:156-222) -> basis_proj_grads_gpu<K>
+ * (cc/kernels/basis_proj_grads_kernels.cu.cc:157-211).
+ * basis [M,K] (K in 8,16,32,64), features [n_in,C] (C < 8 or C % 8 == 0),
+ * neighbors [M,2] (point index into features, sample index), ranges [ns]
+ * -> out [ns,C,K].  Grads: in_grads [ns,C,K] -> dbasis_out [M,K],
+ * dfeat_out [n_in,C] (both overwritten). */
+int tfgpc_basis_proj(void* stream, int K, int C, int64_t ns, int64_t n_in,
+                     int64_t M, const float* basis, const float* features,
+                     const int32_t* neighbors, const int32_t* ranges,
+                     float* out);
+int tfgpc_basis_proj_grads(void* stream, int K, int C, int64_t ns,
+                           int64_t n_in, int64_t M, const float* basis,
+                           const float* features, const int32_t* neighbors,
+                           const int32_t* ranges, const float* in_grads,
+                           float* dbasis_out, float* dfeat_out);
+
+/* ---- Sampling ------------------------------------------------------------
+ * Replaces SamplingOp::Compute (sampling/cc/ops/sampling_ops.cpp:81-195) and
+ * its kernels (count_unique_keys, store_unique_keys, count_sampling_pd,
+ * store_sampled_pts, sampling_avg).  mode 0 = Poisson disk, 1 = cell average
+ * (sampling_ops.cpp:141,174).  Two calls:
+ *   _count selects (state kept in ws), blocks on the stream and returns the
+ *          number of samples S in *num_samples_out [host];
+ *   _store writes sample_pts_out [S,D], sample_batch_ids_out [S] and, for
+ *          mode 0, sample_indices_out [S] (mode 1: not written, may be NULL;
+ *          the reference leaves its [1] tensor unwritten too).
+ * points [n,D], batch_ids [n], point_keys [n] (all sorted), num_cells [D],
+ * neighbors [M,2] and ranges [n] of the self neighborhood.  The same ws must
+ * be passed to both calls with nothing else written to it in between. */
+size_t tfgpc_sampling_workspace_bytes(int64_t n);
+int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n,
+                         const float* points, const int32_t* batch_ids,
+                         const int64_t* point_keys, const int32_t* num_cells,
+                         const int32_t* neighbors, int64_t M,
+                         const int32_t* ranges, void* ws, size_t ws_bytes,
+                         int64_t* num_samples_out);
+int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
+                         const float* points, const int32_t* batch_ids,
+                         const int64_t* point_keys, const int32_t* num_cells,
+                         int64_t num_samples, void* ws, size_t ws_bytes,
+                         float* sample_pts_out, int32_t* sample_batch_ids_out,
+                         int32_t* sample_indices_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFGPC_H_ */

@@ -1,0 +1,74 @@
+"""ctypes binding of libtfgpc.so, the C ABI declared in include/tfgpc.h.
+
+There is no fallback: if the library is missing or a call fails, an exception
+is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtfgpc.so")
+
+_lib = None
+
+c_i64 = ctypes.c_int64
+c_int = ctypes.c_int
+c_vp = ctypes.c_void_p
+c_sz = ctypes.c_size_t
+
+
+class TfgpcError(RuntimeError):
+  """A C-ABI call returned a non-zero status."""
+
+  def __init__(self, code, message):
+    super().__init__("tfgpc error %d: %s" % (code, message))
+    self.code = code
+
+
+# Every symbol include/tfgpc.h declares, with its return type.
+SYMBOLS = {
+    "tfgpc_last_error": ctypes.c_char_p,
+    "tfgpc_version": c_int,
+    "tfgpc_compute_keys": c_int,
+    "tfgpc_sort_keys_workspace_bytes": c_sz,
+    "tfgpc_sort_keys_desc": c_int,
+    "tfgpc_build_grid_ds": c_int,
+    "tfgpc_find_neighbors_workspace_bytes": c_sz,
+    "tfgpc_find_neighbors_count": c_int,
+    "tfgpc_find_neighbors_fill": c_int,
+    "tfgpc_compute_pdf": c_int,
+    "tfgpc_compute_pdf_pt_grads": c_int,
+    "tfgpc_basis_proj": c_int,
+    "tfgpc_basis_proj_grads": c_int,
+    "tfgpc_sampling_workspace_bytes": c_sz,
+    "tfgpc_sampling_count": c_int,
+    "tfgpc_sampling_store": c_int,
+}
+
+
+def lib():
+  """Loads the library once; raises if it has not been built."""
+  global _lib
+  if _lib is None:
+    if not os.path.exists(LIB_PATH):
+      raise RuntimeError(
+          "libtfgpc.so is missing (%s): build it with "
+          "`python -m tensorflow_graphics_point_clouds_b200.build`; there is no "
+          "CPU or eager fallback" % LIB_PATH)
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, restype in SYMBOLS.items():
+      getattr(handle, name).restype = restype
+    _lib = handle
+  return _lib
+
+
+def check(code):
+  if code != 0:
+    raise TfgpcError(code, lib().tfgpc_last_error().decode())
+
+
+def ptr(t):
+  """Device (or host) address of a torch tensor as a void*; None -> NULL."""
+  if t is None:
+    return c_vp(0)
+  return c_vp(t.data_ptr())

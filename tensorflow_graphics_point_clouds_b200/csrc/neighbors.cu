@@ -1,0 +1,227 @@
+// Radius neighbor search on the regular grid: a count pass, a device-wide scan
+// and a fill pass that writes CSR neighbor lists in canonical order (ascending
+// point index inside every sample).
+//
+// One warp owns one sample.  Its lanes first resolve, in parallel, the
+// candidate index range of every neighboring cell column (the reference spends
+// one thread per (sample, offset) in a separate kernel with two interleaved
+// binary searches, find_ranges_grid_ds_kernels.cu.cc:49-169); then the warp
+// walks the ranges from the highest cell key to the lowest -- keys are sorted
+// descending, so this is ascending point index -- testing 32 candidates per
+// step and compacting the hits with a ballot, which gives the canonical order
+// without atomics (the reference: atomicAdd per hit, count_neighbors_kernels.
+// cu.cc:84-87 and store_neighbors_kernels.cu.cc:160-166).
+#include "common.cuh"
+
+namespace tfgpc {
+
+constexpr int kFnThreads = 256;
+
+template <int D>
+__host__ __device__ constexpr int num_offsets() {
+  int n = 1;
+  for (int d = 0; d < (D == 2 ? 2 : D - 1); ++d) n *= 3;
+  return n;
+}
+
+// First index in [lo, hi) of the descending key array with key <= v.
+__device__ __forceinline__ int lower_bound_desc(const int64_t* __restrict__ keys, int lo, int hi,
+                                                int64_t v) {
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (__ldg(keys + mid) > v) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// Candidate range [a, e) of offset code `code` around `cell`.  For D >= 3 the
+// code enumerates the leading D-1 coordinates (most significant first) and the
+// last coordinate's +-1 range is cut out of the (batch, c0, c1) tube by key;
+// for D == 2 the code enumerates both coordinates and the tube is the cell.
+template <int D>
+__device__ __forceinline__ int2 candidate_range(int code, const int* cell, int batch,
+                                                const Grid<D>& g,
+                                                const int64_t* __restrict__ keys,
+                                                const int2* __restrict__ ds) {
+  constexpr int kDigits = (D == 2) ? 2 : D - 1;
+  int cp[D];
+  bool ok = true;
+  int rem = code;
+#pragma unroll
+  for (int d = kDigits - 1; d >= 0; --d) {
+    cp[d] = cell[d] + (rem % 3) - 1;
+    rem /= 3;
+    ok = ok && cp[d] >= 0 && cp[d] < g.nc[d];
+  }
+  if (!ok) return make_int2(0, 0);
+  int2 tube = __ldg(ds + ((int64_t)batch * g.nc[0] + cp[0]) * g.nc[1] + cp[1]);
+  if (D == 2 || tube.y <= tube.x) return tube.y > tube.x ? tube : make_int2(0, 0);
+  int lo_l = max(cell[D - 1] - 1, 0);
+  int hi_l = min(cell[D - 1] + 1, g.nc[D - 1] - 1);
+  cp[D - 1] = hi_l;
+  int64_t k_hi = key_of<D>(cp, g, batch);
+  cp[D - 1] = lo_l;
+  int64_t k_lo = key_of<D>(cp, g, batch);
+  int a = lower_bound_desc(keys, tube.x, tube.y, k_hi);
+  int e = lower_bound_desc(keys, a, tube.y, k_lo - 1);
+  return make_int2(a, e);
+}
+
+// t_d = (s_d - p_d) * inv_r_d, d2 = fma chain from t_0*t_0, sqrtf(d2) < 1
+// (count_neighbors_kernels.cu.cc:84-85, math_helper.h:311-327).
+template <int D>
+__device__ __forceinline__ bool within_radius(const float* s, const float* __restrict__ p,
+                                              const float* inv_r) {
+  float t = __fmul_rn(__fsub_rn(s[0], __ldg(p)), inv_r[0]);
+  float d2 = __fmul_rn(t, t);
+#pragma unroll
+  for (int d = 1; d < D; ++d) {
+    t = __fmul_rn(__fsub_rn(s[d], __ldg(p + d)), inv_r[d]);
+    d2 = __fmaf_rn(t, t, d2);
+  }
+  return __fsqrt_rn(d2) < 1.0f;
+}
+
+template <int D, bool FILL>
+__global__ void __launch_bounds__(kFnThreads)
+find_neighbors_kernel(int64_t ns, const float* __restrict__ samples,
+                      const int32_t* __restrict__ sbatch, const float* __restrict__ pts,
+                      const int64_t* __restrict__ keys, const int2* __restrict__ ds,
+                      int batch_size, const int32_t* __restrict__ num_cells,
+                      const float* __restrict__ smin_all, const float* __restrict__ inv_cell,
+                      const float* __restrict__ inv_radii, int max_neighs,
+                      int32_t* __restrict__ counts, const int32_t* __restrict__ ranges,
+                      int2* __restrict__ neigh_out) {
+  constexpr int kOff = num_offsets<D>();
+  constexpr int kChunks = (kOff + 31) / 32;
+  const Grid<D> g = load_grid<D>(num_cells, inv_cell);
+  float inv_r[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) inv_r[d] = __ldg(inv_radii + d);
+  const int lane = lane_id();
+  const unsigned lt_mask = (1u << lane) - 1u;
+  const int64_t warps = ((int64_t)gridDim.x * kFnThreads) >> 5;
+  for (int64_t s = ((int64_t)blockIdx.x * kFnThreads + threadIdx.x) >> 5; s < ns; s += warps) {
+    float sp[D], smin[D];
+    int cell[D];
+    const int b = __ldg(sbatch + s);
+    const bool b_ok = b >= 0 && b < batch_size;
+    const int bs = b_ok ? b : 0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      sp[d] = __ldg(samples + s * D + d);
+      smin[d] = __ldg(smin_all + (int64_t)bs * D + d);
+    }
+    cell_of<D>(sp, smin, g, cell);
+    int2 my_range[kChunks];
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      int code = c * 32 + lane;
+      my_range[c] = (b_ok && code < kOff) ? candidate_range<D>(code, cell, b, g, keys, ds)
+                                          : make_int2(0, 0);
+    }
+    int count = 0;
+    int64_t out_base = 0;
+    if (FILL) out_base = s ? (int64_t)__ldg(ranges + s - 1) : 0;
+    const int limit = max_neighs > 0 ? max_neighs : INT32_MAX;
+#pragma unroll
+    for (int c = kChunks - 1; c >= 0; --c) {
+      const int top = min(kOff - c * 32, 32) - 1;
+      for (int o = top; o >= 0; --o) {
+        const int a = __shfl_sync(0xffffffffu, my_range[c].x, o);
+        const int e = __shfl_sync(0xffffffffu, my_range[c].y, o);
+        for (int base = a; base < e && count < limit; base += 32) {
+          const int j = base + lane;
+          const bool hit = j < e && within_radius<D>(sp, pts + (int64_t)j * D, inv_r);
+          const unsigned m = __ballot_sync(0xffffffffu, hit);
+          if (FILL && hit) {
+            int pos = count + __popc(m & lt_mask);
+            if (pos < limit) neigh_out[out_base + pos] = make_int2(j, (int)s);
+          }
+          count += __popc(m);
+        }
+      }
+    }
+    if (!FILL && lane == 0) counts[s] = min(count, limit);
+  }
+}
+
+static int check_fn_args(int D, int64_t ns, int64_t n, int64_t batch_size, int max_neighs) {
+  TFGPC_REQUIRE(valid_dims(D), "FindNeighbors expects a valid number of dimension (got %d)", D);
+  TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && n >= 0 && n < (int64_t)INT32_MAX,
+                "FindNeighbors expects 0 <= ns, n < 2^31");
+  TFGPC_REQUIRE(batch_size > 0 && batch_size < (int64_t)INT32_MAX,
+                "FindNeighbors expects a positive batch size");
+  TFGPC_REQUIRE(max_neighs >= 0, "FindNeighbors expects max_neighs >= 0");
+  return TFGPC_OK;
+}
+
+}  // namespace tfgpc
+
+using namespace tfgpc;
+
+extern "C" size_t tfgpc_find_neighbors_workspace_bytes(int64_t ns) {
+  if (ns < 0) ns = 0;
+  return align_up((size_t)(scan_block_sums_elems(ns) + 1) * sizeof(int64_t), 256) + 256;
+}
+
+extern "C" int tfgpc_find_neighbors_count(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
+    void* ws, size_t ws_bytes, int64_t* total_out) {
+  int rc = check_fn_args(D, ns, n, batch_size, max_neighs);
+  if (rc) return rc;
+  TFGPC_REQUIRE(total_out, "FindNeighbors got a null pointer");
+  *total_out = 0;
+  if (ns == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(samples && samples_batch_ids && ds && num_cells && scaled_aabb_min &&
+                inv_cell_sizes && inv_radii && ranges_out && ws && (n == 0 || (points && point_keys)),
+                "FindNeighbors got a null pointer");
+  if (ws_bytes < tfgpc_find_neighbors_workspace_bytes(ns))
+    return fail(TFGPC_ENOMEM, "FindNeighbors workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_find_neighbors_workspace_bytes(ns));
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t* block_sums = (int64_t*)ws;
+  int64_t* total_dev = block_sums + scan_block_sums_elems(ns);
+  unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, false><<<grid, kFnThreads, 0, st>>>(
+      ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+      num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, ranges_out, nullptr,
+      nullptr));
+  TFGPC_LAUNCH_CHECK();
+  rc = inclusive_scan_i32(st, ranges_out, ranges_out, ns, block_sums, total_dev);
+  if (rc) return rc;
+  int64_t total = 0;
+  TFGPC_CUDA(cudaMemcpyAsync(&total, total_dev, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+  TFGPC_CUDA(cudaStreamSynchronize(st));
+  if (total > (int64_t)INT32_MAX)
+    return fail(TFGPC_EINVAL, "FindNeighbors found %lld pairs; the int32 ranges of the op "
+                "contract hold at most 2^31-1", (long long)total);
+  *total_out = total;
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_find_neighbors_fill(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs, const int32_t* ranges,
+    int64_t total, int32_t* neigh_out) {
+  int rc = check_fn_args(D, ns, n, batch_size, max_neighs);
+  if (rc) return rc;
+  TFGPC_REQUIRE(total >= 0 && total <= (int64_t)INT32_MAX, "FindNeighbors expects 0 <= total < 2^31");
+  if (ns == 0 || total == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(samples && samples_batch_ids && points && point_keys && ds && num_cells &&
+                scaled_aabb_min && inv_cell_sizes && inv_radii && ranges && neigh_out,
+                "FindNeighbors got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, true><<<grid, kFnThreads, 0, st>>>(
+      ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+      num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,
+      (int2*)neigh_out));
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}

@@ -1,0 +1,262 @@
+"""The eight callables of the reference's `tfg_custom_ops` package
+(custom_ops/tfg_custom_ops/__init__.py:16-26) over torch CUDA tensors.
+
+Names, argument order and meaning follow the TensorFlow op registrations; each
+function marshals its tensors into one or two C-ABI calls (include/tfgpc.h) on
+torch's current stream.  torch only owns the device memory.  Argument errors
+raise `TfgpcError` with the reference's InvalidArgument conditions.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import c_i64, c_int, c_sz, ptr
+
+
+def _stream():
+  return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f32(t):
+  return t.contiguous().to(torch.float32)
+
+
+def _i32(t):
+  return t.contiguous().to(torch.int32)
+
+
+def _dev_check(*tensors):
+  for t in tensors:
+    if not t.is_cuda:
+      raise ValueError("tfg_custom_ops are registered for the GPU only: got a CPU tensor")
+
+
+def _workspace(nbytes, device):
+  return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+
+def compute_keys(points, batch_ids, scaled_aabb_min, num_cells, inv_cell_sizes):
+  """ComputeKeys (compute_keys/cc/ops/compute_keys_ops.cpp:29-41)."""
+  points, smin, inv = _f32(points), _f32(scaled_aabb_min), _f32(inv_cell_sizes)
+  batch_ids, num_cells = _i32(batch_ids), _i32(num_cells)
+  _dev_check(points, batch_ids, smin, num_cells, inv)
+  n, d = points.shape
+  if batch_ids.shape[0] != n:
+    raise _lib.TfgpcError(1, "ComputeKeysOp expects the same number of points as batch ids")
+  if smin.dim() != 2 or smin.shape[1] != d or num_cells.shape[0] != d or inv.shape[0] != d:
+    raise _lib.TfgpcError(1, "ComputeKeysOp expects inputs with the dimension of the points")
+  keys = torch.empty(n, dtype=torch.int64, device=points.device)
+  _lib.check(_lib.lib().tfgpc_compute_keys(
+      _stream(), c_int(d), c_i64(n), ptr(points), ptr(batch_ids), c_i64(smin.shape[0]),
+      ptr(smin), ptr(num_cells), ptr(inv), ptr(keys)))
+  return keys
+
+
+def sort_keys_desc(keys, points=None, batch_ids=None, key_bits=0):
+  """tf.argsort(keys, 'DESCENDING') plus the gathers of pylib/pc/Grid.py:56-64
+  in one call.  Returns (perm, sorted_keys[, sorted_points, sorted_batch_ids])."""
+  keys = keys.contiguous()
+  _dev_check(keys)
+  n = keys.shape[0]
+  dev = keys.device
+  perm = torch.empty(n, dtype=torch.int32, device=dev)
+  skeys = torch.empty(n, dtype=torch.int64, device=dev)
+  spts = sbid = None
+  d = 3
+  if points is not None:
+    points, batch_ids = _f32(points), _i32(batch_ids)
+    d = points.shape[1]
+    spts = torch.empty_like(points)
+    sbid = torch.empty_like(batch_ids)
+  nbytes = _lib.lib().tfgpc_sort_keys_workspace_bytes(c_i64(n))
+  ws = _workspace(nbytes, dev)
+  _lib.check(_lib.lib().tfgpc_sort_keys_desc(
+      _stream(), c_int(d), c_i64(n), c_int(key_bits), ptr(keys), ptr(points), ptr(batch_ids),
+      ptr(perm), ptr(skeys), ptr(spts), ptr(sbid), ptr(ws), c_sz(nbytes)))
+  if points is None:
+    return perm, skeys
+  return perm, skeys, spts, sbid
+
+
+def build_grid_ds(keys, num_cells_gpu, num_cells_cpu, batch_size):
+  """BuildGridDs (build_grid_ds/cc/ops/build_grid_ds_ops.cpp:27-40).  The third
+  input lives in host memory, as the op's HostMemory("num_cells_cpu") asks."""
+  keys = keys.contiguous()
+  num_cells_gpu = _i32(num_cells_gpu)
+  _dev_check(keys, num_cells_gpu)
+  host = _i32(torch.as_tensor(num_cells_cpu).cpu())
+  d = host.shape[0]
+  if batch_size <= 0:
+    raise _lib.TfgpcError(1, "BuildGridDsOp expects a positive batch size")
+  ds = torch.empty((batch_size, int(host[0]), int(host[1]), 2), dtype=torch.int32,
+                   device=keys.device)
+  _lib.check(_lib.lib().tfgpc_build_grid_ds(
+      _stream(), c_int(d), c_i64(keys.shape[0]), ptr(keys), ptr(num_cells_gpu),
+      ctypes.c_void_p(host.data_ptr()), c_i64(batch_size), ptr(ds)))
+  return ds
+
+
+def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, num_cells,
+                   scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs=0):
+  """FindNeighbors (find_neighbors/cc/ops/find_neighbors_ops.cpp:42-61).
+  Returns (samples_neigh_indices [Ns], neigh_indices [M, 2])."""
+  samples, points = _f32(samples), _f32(points)
+  sbid, nc = _i32(samples_batch_ids), _i32(num_cells)
+  keys, ds = point_keys.contiguous(), _i32(grid_acc_ds)
+  smin, inv_c, inv_r = _f32(scaled_aabb_min), _f32(inv_cell_sizes), _f32(inv_radii)
+  _dev_check(samples, sbid, points, keys, ds, nc, smin, inv_c, inv_r)
+  ns, d = samples.shape
+  n = points.shape[0]
+  if not (nc.shape[0] == d and points.shape[1] == d and smin.shape[1] == d
+          and inv_c.shape[0] == d and inv_r.shape[0] == d):
+    raise _lib.TfgpcError(1, "FindNeighborsOp expects inputs with the dimension of the samples")
+  if sbid.shape[0] != ns:
+    raise _lib.TfgpcError(1, "FindNeighborsOp expects the same number of batch ids as samples.")
+  if keys.shape[0] != n:
+    raise _lib.TfgpcError(1, "FindNeighborsOp expects the same number of keys as points.")
+  if ds.dim() != 4 or ds.shape[3] != 2:
+    raise _lib.TfgpcError(1, "FindNeighborsOp expects a grid acceleration data structure with "
+                          "the right format (B, X, Y, 2).")
+  dev = samples.device
+  ranges = torch.empty(ns, dtype=torch.int32, device=dev)
+  nbytes = _lib.lib().tfgpc_find_neighbors_workspace_bytes(c_i64(ns))
+  ws = _workspace(nbytes, dev)
+  total = c_i64(0)
+  common = (_stream(), c_int(d), c_i64(ns), ptr(samples), ptr(sbid), c_i64(n), ptr(points),
+            ptr(keys), ptr(ds), c_i64(ds.shape[0]), ptr(nc), ptr(smin), ptr(inv_c), ptr(inv_r),
+            c_int(int(max_neighs)))
+  _lib.check(_lib.lib().tfgpc_find_neighbors_count(
+      *common, ptr(ranges), ptr(ws), c_sz(nbytes), ctypes.byref(total)))
+  m = int(total.value)
+  neigh = torch.empty((m, 2), dtype=torch.int32, device=dev)
+  _lib.check(_lib.lib().tfgpc_find_neighbors_fill(*common, ptr(ranges), c_i64(m), ptr(neigh)))
+  return ranges, neigh
+
+
+def _pdf_args(points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii, mode):
+  points = _f32(points)
+  neighbors, ranges = _i32(neighbors), _i32(sample_neigh_indices)
+  inv_bw, inv_r = _f32(inv_bandwidth), _f32(inv_radii)
+  _dev_check(points, neighbors, ranges, inv_bw, inv_r)
+  n, d = points.shape
+  if ranges.shape[0] != n:
+    raise _lib.TfgpcError(1, "ComputePDFOp expects the same number of points as samples")
+  if neighbors.dim() != 2 or neighbors.shape[1] != 2:
+    raise _lib.TfgpcError(1, "ComputePDFOp expects a neighbor tensor with 2 dimensions and 2 "
+                          "indices per neighbor.")
+  if inv_bw.shape[0] != d or inv_r.shape[0] != d:
+    raise _lib.TfgpcError(1, "ComputePDFOp expects bandwidths and radii with the dimension of "
+                          "the points")
+  return points, neighbors, ranges, inv_bw, inv_r, n, d, int(mode)
+
+
+def compute_pdf_with_pt_grads(points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii,
+                              mode):
+  """ComputePdfWithPtGrads (compute_pdf/cc/ops/compute_pdf_ops.cpp:43-56)."""
+  points, neighbors, ranges, inv_bw, inv_r, n, d, mode = _pdf_args(
+      points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii, mode)
+  pdf = torch.empty(n, dtype=torch.float32, device=points.device)
+  _lib.check(_lib.lib().tfgpc_compute_pdf(
+      _stream(), c_int(d), c_int(mode), c_i64(n), ptr(points), ptr(neighbors),
+      c_i64(neighbors.shape[0]), ptr(ranges), ptr(inv_bw), ptr(inv_r), ptr(pdf)))
+  return pdf
+
+
+compute_pdf = compute_pdf_with_pt_grads  # same kernel class (compute_pdf_ops.cpp:257-258)
+
+
+def compute_pdf_pt_grads(points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii,
+                         pdf_grads, mode):
+  """ComputePdfPtGrads (compute_pdf/cc/ops/compute_pdf_ops.cpp:58-74)."""
+  points, neighbors, ranges, inv_bw, inv_r, n, d, mode = _pdf_args(
+      points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii, mode)
+  pdf_grads = _f32(pdf_grads)
+  if pdf_grads.shape[0] != n:
+    raise _lib.TfgpcError(1, "ComputePDFPtGradsOp expects one pdf gradient per point")
+  out = torch.empty((n, d), dtype=torch.float32, device=points.device)
+  _lib.check(_lib.lib().tfgpc_compute_pdf_pt_grads(
+      _stream(), c_int(d), c_int(mode), c_i64(n), ptr(points), ptr(neighbors),
+      c_i64(neighbors.shape[0]), ptr(ranges), ptr(inv_bw), ptr(inv_r), ptr(pdf_grads), ptr(out)))
+  return out
+
+
+def _bp_args(basis, features, neighbors, ranges):
+  basis, features = _f32(basis), _f32(features)
+  neighbors, ranges = _i32(neighbors), _i32(ranges)
+  _dev_check(basis, features, neighbors, ranges)
+  if neighbors.dim() != 2 or neighbors.shape[1] != 2:
+    raise _lib.TfgpcError(1, "BasisProjOp expects a neighbor tensor with 2 dimensions and 2 "
+                          "indices per neighbor.")
+  if basis.shape[0] != neighbors.shape[0]:
+    raise _lib.TfgpcError(1, "BasisProjOp expects the same number of basis as the number of "
+                          "neighbors.")
+  return basis, features, neighbors, ranges
+
+
+def basis_proj(basis_neighbors, pt_features, neighbors, sample_neigh_indices):
+  """BasisProj (basis_proj/cc/ops/basis_proj_ops.cpp:25-39) -> [Ns, C, K]."""
+  basis, feat, neighbors, ranges = _bp_args(basis_neighbors, pt_features, neighbors,
+                                            sample_neigh_indices)
+  k, c, ns = basis.shape[1], feat.shape[1], ranges.shape[0]
+  out = torch.empty((ns, c, k), dtype=torch.float32, device=basis.device)
+  _lib.check(_lib.lib().tfgpc_basis_proj(
+      _stream(), c_int(k), c_int(c), c_i64(ns), c_i64(feat.shape[0]), c_i64(basis.shape[0]),
+      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(out)))
+  return out
+
+
+def basis_proj_grads(basis_neighbors, pt_features, neighbors, sample_neigh_indices,
+                     in_gradients):
+  """BasisProjGrads (basis_proj/cc/ops/basis_proj_ops.cpp:41-53) ->
+  (basis_gradients [M, K], feat_gradients [Nin, C])."""
+  basis, feat, neighbors, ranges = _bp_args(basis_neighbors, pt_features, neighbors,
+                                            sample_neigh_indices)
+  grads = _f32(in_gradients)
+  k, c, ns = basis.shape[1], feat.shape[1], ranges.shape[0]
+  if tuple(grads.shape) != (ns, c, k):
+    raise _lib.TfgpcError(1, "BasisProjGradsOp expects gradients of shape [Ns, C, K]")
+  dbasis = torch.empty_like(basis)
+  dfeat = torch.empty_like(feat)
+  _lib.check(_lib.lib().tfgpc_basis_proj_grads(
+      _stream(), c_int(k), c_int(c), c_i64(ns), c_i64(feat.shape[0]), c_i64(basis.shape[0]),
+      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(grads), ptr(dbasis), ptr(dfeat)))
+  return dbasis, dfeat
+
+
+def sampling(points, batch_ids, point_keys, num_cells, neighbors, sample_neigh_indices, mode):
+  """Sampling (sampling/cc/ops/sampling_ops.cpp:33-53).  mode 0 = Poisson disk,
+  1 = cell average.  Returns (sample_pts [S, D], sample_batch_ids [S],
+  sample_indices [S] or an unwritten [1] tensor for mode 1)."""
+  points, batch_ids, nc = _f32(points), _i32(batch_ids), _i32(num_cells)
+  keys = point_keys.contiguous()
+  neighbors, ranges = _i32(neighbors), _i32(sample_neigh_indices)
+  _dev_check(points, batch_ids, keys, nc, neighbors, ranges)
+  n, d = points.shape
+  if batch_ids.shape[0] != n or keys.shape[0] != n:
+    raise _lib.TfgpcError(1, "SamplingOp expects the same number of keys as number of points.")
+  if nc.shape[0] != d:
+    raise _lib.TfgpcError(1, "SamplingOp expects a number of dimensions in inNumCells equal to "
+                          "the number of dimensions in the input points")
+  if neighbors.dim() != 2 or neighbors.shape[1] != 2:
+    raise _lib.TfgpcError(1, "SamplingOp expects a neighbor tensor with 2 dimensions and 2 "
+                          "indices per neighbor.")
+  if ranges.shape[0] != n:
+    raise _lib.TfgpcError(1, "SamplingOp expects the same number of points in inStartNeighIds "
+                          "as in the points tensor.")
+  dev = points.device
+  nbytes = _lib.lib().tfgpc_sampling_workspace_bytes(c_i64(n))
+  ws = _workspace(nbytes, dev)
+  total = c_i64(0)
+  common = (_stream(), c_int(d), c_int(int(mode)), c_i64(n), ptr(points), ptr(batch_ids),
+            ptr(keys), ptr(nc))
+  _lib.check(_lib.lib().tfgpc_sampling_count(
+      *common, ptr(neighbors), c_i64(neighbors.shape[0]), ptr(ranges), ptr(ws), c_sz(nbytes),
+      ctypes.byref(total)))
+  s = int(total.value)
+  out_pts = torch.empty((s, d), dtype=torch.float32, device=dev)
+  out_bid = torch.empty(s, dtype=torch.int32, device=dev)
+  out_idx = torch.empty(s if int(mode) == 0 else 1, dtype=torch.int32, device=dev)
+  _lib.check(_lib.lib().tfgpc_sampling_store(
+      *common, c_i64(s), ptr(ws), c_sz(nbytes), ptr(out_pts), ptr(out_bid), ptr(out_idx)))
+  return out_pts, out_bid, out_idx

@@ -1,0 +1,161 @@
+"""Callers of the custom ops: torch mirrors of the reference's pylib classes.
+
+  PointCloud / AABB   pylib/pc/PointCloud.py:23-134, 235-247
+  Grid                pylib/pc/Grid.py:20-83
+  Neighborhood        pylib/pc/Neighborhood.py:203-329
+  sample              pylib/pc/sampling.py:23-28, 123-150
+  PointHierarchy      pylib/pc/PointHierarchy.py:25-98
+
+Only what feeds the ops is kept (segmented [N, D] input with batch ids); the
+arithmetic around the ops is float32 torch code that follows the TensorFlow
+expressions of the reference one to one, and the ops themselves run through
+`custom_ops` (the C ABI).
+"""
+import math
+
+import torch
+
+from . import custom_ops as ops
+
+SAMPLE_MODES = {'average': 1, 'cell average': 1, 'cell_average': 1,
+                'poisson': 0, 'poisson disk': 0, 'poisson_disk': 0}
+
+
+def _to_dims(value, dims, device):
+  t = torch.as_tensor(value, dtype=torch.float32, device=device).reshape(-1)
+  if t.shape[0] == 1:
+    t = t.repeat(dims)
+  return t
+
+
+class PointCloud:
+  """Segmented point cloud: points [N, D] float32 and batch ids [N] int32."""
+
+  def __init__(self, points, batch_ids, batch_size=None):
+    self._points = torch.as_tensor(points).to(torch.float32).contiguous()
+    self._batch_ids = torch.as_tensor(batch_ids, device=self._points.device).to(
+        torch.int32).contiguous()
+    if batch_size is None:
+      batch_size = int(self._batch_ids.max().item()) + 1
+    self._batch_size = int(batch_size)
+    self._dimension = self._points.shape[1]
+    self._aabb = None
+
+  def get_AABB(self):
+    """PointCloud.py:38-43: per-cloud min - 1e-9 and max + 1e-9 in float32."""
+    if self._aabb is None:
+      d, b = self._dimension, self._batch_size
+      idx = self._batch_ids.to(torch.int64).unsqueeze(1).expand(-1, d)
+      mn = torch.full((b, d), float('inf'), device=self._points.device)
+      mx = torch.full((b, d), float('-inf'), device=self._points.device)
+      mn = mn.scatter_reduce(0, idx, self._points, reduce='amin')
+      mx = mx.scatter_reduce(0, idx, self._points, reduce='amax')
+      self._aabb = (mn - 1e-9, mx + 1e-9)
+    return self._aabb
+
+
+class Grid:
+  """Grid.py:32-83: keys, descending sort, sorted copies, lazy tube ranges."""
+
+  def __init__(self, point_cloud, cell_sizes):
+    pc = point_cloud
+    dev = pc._points.device
+    self._point_cloud = pc
+    self._batch_size = pc._batch_size
+    self._cell_sizes = _to_dims(cell_sizes, pc._dimension, dev)
+    self._aabb_min, self._aabb_max = pc.get_AABB()
+    sizes = self._aabb_max - self._aabb_min
+    batch_num_cells = torch.ceil(sizes / self._cell_sizes).to(torch.int32)
+    self._num_cells = torch.clamp(batch_num_cells.max(dim=0).values, min=1).to(torch.int32)
+    self._num_cells_host = self._num_cells.cpu()
+    # custom_ops_wrapper.py:37-43
+    self._scaled_aabb_min = self._aabb_min / self._cell_sizes
+    self._inv_cell_sizes = torch.reciprocal(self._cell_sizes)
+    self._cur_keys = ops.compute_keys(pc._points, pc._batch_ids, self._scaled_aabb_min,
+                                      self._num_cells, self._inv_cell_sizes)
+    total = self._batch_size
+    for c in self._num_cells_host.tolist():
+      total *= int(c)
+    key_bits = max(1, int(math.ceil(math.log2(total + 1))))
+    (self._sorted_indices, self._sorted_keys, self._sorted_points,
+     self._sorted_batch_ids) = ops.sort_keys_desc(self._cur_keys, pc._points, pc._batch_ids,
+                                                  key_bits=min(64, key_bits))
+    self._fast_DS = None
+
+  def get_DS(self):
+    if self._fast_DS is None:
+      self._fast_DS = ops.build_grid_ds(self._sorted_keys, self._num_cells,
+                                        self._num_cells_host, self._batch_size)
+    return self._fast_DS
+
+
+class Neighborhood:
+  """Neighborhood.py:218-311."""
+
+  def __init__(self, grid, radius, point_cloud_sample=None, max_neighbors=0):
+    dev = grid._sorted_points.device
+    self._radii = _to_dims(radius, grid._point_cloud._dimension, dev)
+    if point_cloud_sample is None:
+      self._equal_samples = True
+      self._point_cloud_sampled = PointCloud(grid._sorted_points, grid._sorted_batch_ids,
+                                             grid._batch_size)
+    else:
+      self._equal_samples = False
+      self._point_cloud_sampled = point_cloud_sample
+    self._grid = grid
+    self.max_neighbors = max_neighbors
+    smp = self._point_cloud_sampled
+    self._samples_neigh_ranges, self._neighbors = ops.find_neighbors(
+        smp._points, smp._batch_ids, grid._sorted_points, grid._sorted_keys, grid.get_DS(),
+        grid._num_cells, grid._scaled_aabb_min, grid._inv_cell_sizes,
+        torch.reciprocal(self._radii), max_neighbors)
+    orig = grid._sorted_indices[self._neighbors[:, 0].to(torch.int64)]
+    self._original_neigh_ids = torch.stack([orig, self._neighbors[:, 1]], dim=1).contiguous()
+    self._pdf = None
+    self._point_pdf = None
+
+  def compute_pdf(self, bandwidth=0.2, mode=0):
+    """Neighborhood.py:257-311 (mode: 0 constant bandwidth, 1 by point count)."""
+    d = self._point_cloud_sampled._dimension
+    bw = _to_dims(bandwidth, d, self._radii.device)
+    nb = self if self._equal_samples else Neighborhood(self._grid, self._radii)
+    self._point_pdf = ops.compute_pdf_with_pt_grads(
+        self._grid._sorted_points, nb._neighbors, nb._samples_neigh_ranges,
+        torch.reciprocal(bw), torch.reciprocal(self._radii), mode)
+    self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
+
+  def get_pdf(self, **kwargs):
+    if self._pdf is None:
+      self.compute_pdf(**kwargs)
+    return self._pdf
+
+
+def sample(neighborhood, sample_mode='poisson'):
+  """sampling.py:123-150 -> (PointCloud of the samples, original indices or None)."""
+  mode = SAMPLE_MODES[sample_mode.lower()]
+  g = neighborhood._grid
+  pts, bids, idx = ops.sampling(g._sorted_points, g._sorted_batch_ids, g._sorted_keys,
+                                g._num_cells, neighborhood._neighbors,
+                                neighborhood._samples_neigh_ranges, mode)
+  if mode == 0:
+    idx = g._sorted_indices[idx.to(torch.int64)]
+  else:
+    idx = None
+  return PointCloud(pts, bids, g._batch_size), idx
+
+
+class PointHierarchy:
+  """PointHierarchy.py:40-98: per level Grid -> self Neighborhood -> sample."""
+
+  def __init__(self, point_cloud, cell_sizes, sample_mode='poisson'):
+    self._point_clouds = [point_cloud]
+    self._neighborhoods = []
+    self._sample_indices = []
+    cur = point_cloud
+    for cs in cell_sizes:
+      grid = Grid(cur, cs)
+      neigh = Neighborhood(grid, grid._cell_sizes)
+      cur, idx = sample(neigh, sample_mode)
+      self._neighborhoods.append(neigh)
+      self._point_clouds.append(cur)
+      self._sample_indices.append(idx)

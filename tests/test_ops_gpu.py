@@ -1,0 +1,303 @@
+"""Parity of the CUDA library (through the C ABI) with the CPU oracle, op by op.
+
+Integer outputs (keys, permutation, grid ranges, CSR neighbor lists, sampled
+indices) must be bit-exact; float outputs must satisfy
+|x - y| <= 1e-4 * max(|y|, rms(y)).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+from oracle import pylib_ref as pr
+from tensorflow_graphics_point_clouds_b200 import custom_ops as ops
+from tensorflow_graphics_point_clouds_b200 import pc, synthetic
+from tensorflow_graphics_point_clouds_b200._lib import TfgpcError
+
+pytestmark = pytest.mark.gpu
+F32 = np.float32
+DEV = "cuda"
+
+
+def t(a):
+  return torch.as_tensor(np.ascontiguousarray(a)).to(DEV)
+
+
+def close(x, y, rel=1e-4):
+  x = np.asarray(x, np.float64); y = np.asarray(y, np.float64)
+  if y.size == 0:
+    assert x.size == 0
+    return
+  scale = np.maximum(np.abs(y), np.sqrt(np.mean(y * y)))
+  bad = np.abs(x - y) > rel * scale + 1e-30
+  assert not bad.any(), "max rel err %g at %d of %d" % (
+      (np.abs(x - y) / np.maximum(scale, 1e-30)).max(), bad.sum(), y.size)
+
+
+def random_cloud(rng, b, n, d):
+  pts = rng.uniform(0, 1, (n, d)).astype(F32)
+  bid = rng.integers(0, b, n).astype(np.int32)
+  bid[:b] = np.arange(b)
+  return pts, bid
+
+
+def grid_pair(pts, bid, b, cell):
+  """The oracle grid and the CUDA grid of the same cloud."""
+  g_ref = pr.Grid(pts, bid, b, cell)
+  g = pc.Grid(pc.PointCloud(t(pts), t(bid), b), cell)
+  return g_ref, g
+
+
+def assert_grid_equal(g_ref, g):
+  assert np.array_equal(g._num_cells.cpu().numpy(), g_ref.num_cells)
+  assert np.array_equal(g._scaled_aabb_min.cpu().numpy(), g_ref.scaled_aabb_min)
+  assert np.array_equal(g._cur_keys.cpu().numpy(), g_ref.keys)
+  assert np.array_equal(g._sorted_indices.cpu().numpy(), g_ref.sorted_indices)
+  assert np.array_equal(g._sorted_keys.cpu().numpy(), g_ref.sorted_keys)
+  assert np.array_equal(g._sorted_points.cpu().numpy(), g_ref.sorted_points)
+  assert np.array_equal(g._sorted_batch_ids.cpu().numpy(), g_ref.sorted_batch_ids)
+  assert np.array_equal(g.get_DS().cpu().numpy(), g_ref.get_ds())
+
+
+@pytest.mark.parametrize("d", [2, 3, 4, 5, 6])
+@pytest.mark.parametrize("cell", [0.05, 0.3])
+def test_grid_build(d, cell):
+  rng = np.random.default_rng(100 + d)
+  b = 5
+  pts, bid = random_cloud(rng, b, 3000, d)
+  if d >= 5 and cell < 0.1:
+    cell = 0.15
+  g_ref, g = grid_pair(pts, bid, b, cell)
+  assert_grid_equal(g_ref, g)
+
+
+def test_grid_build_large_keys_and_ties():
+  # many points per cell (ties in the sort) and a cloud with a single point
+  rng = np.random.default_rng(7)
+  pts = np.concatenate([rng.uniform(0, 1, (5000, 3)), [[0.5, 0.5, 0.5]]]).astype(F32)
+  bid = np.concatenate([np.zeros(5000), [1]]).astype(np.int32)
+  g_ref, g = grid_pair(pts, bid, 2, 0.5)
+  assert_grid_equal(g_ref, g)
+
+
+def neigh_pair(g_ref, g, radius, smp=None, sbid=None, max_neighbors=0):
+  if smp is None:
+    nb_ref = pr.Neighborhood(g_ref, radius, max_neighbors=max_neighbors)
+    nb = pc.Neighborhood(g, radius, max_neighbors=max_neighbors)
+  else:
+    nb_ref = pr.Neighborhood(g_ref, radius, smp, sbid, max_neighbors)
+    nb = pc.Neighborhood(g, radius, pc.PointCloud(t(smp), t(sbid), g_ref.batch_size),
+                         max_neighbors)
+  return nb_ref, nb
+
+
+def assert_neigh_equal(nb_ref, nb):
+  assert np.array_equal(nb._samples_neigh_ranges.cpu().numpy(), nb_ref.ranges)
+  assert np.array_equal(nb._neighbors.cpu().numpy(), nb_ref.neighbors)
+  assert np.array_equal(nb._original_neigh_ids.cpu().numpy(), nb_ref.original_neigh_ids)
+
+
+@pytest.mark.parametrize("d", [2, 3, 4, 5, 6])
+@pytest.mark.parametrize("radius", [0.08, 0.3, 0.9])
+def test_find_neighbors_random(d, radius):
+  rng = np.random.default_rng(200 + d)
+  b = 4
+  pts, bid = random_cloud(rng, b, 2500, d)
+  smp, sbid = random_cloud(rng, b, 300, d)
+  if d >= 5 and radius < 0.1:
+    radius = 0.2
+  g_ref, g = grid_pair(pts, bid, b, radius)
+  nb_ref, nb = neigh_pair(g_ref, g, radius, smp, sbid)
+  assert_neigh_equal(nb_ref, nb)
+  # self neighborhood
+  nb_ref, nb = neigh_pair(g_ref, g, radius)
+  assert_neigh_equal(nb_ref, nb)
+
+
+@pytest.mark.parametrize("radius,expected", [(0.05, 1), (0.11, 7), (0.142, 19), (0.174, 27)])
+def test_find_neighbors_lattice_known_answers(radius, expected):
+  """neighbors_test.py:113-146."""
+  tk = np.linspace(0, 1, num=10, endpoint=False)
+  pts = np.array(np.meshgrid(tk, tk, tk)).T.reshape(-1, 3).astype(F32)
+  ts = np.linspace(1 / 5, 1, num=4, endpoint=False)
+  smp = np.array(np.meshgrid(ts, ts, ts)).T.reshape(-1, 3).astype(F32)
+  bid = np.zeros(len(pts), np.int32); sbid = np.zeros(len(smp), np.int32)
+  g_ref, g = grid_pair(pts, bid, 1, radius)
+  nb_ref, nb = neigh_pair(g_ref, g, radius, smp, sbid)
+  assert_neigh_equal(nb_ref, nb)
+  counts = np.diff(np.concatenate([[0], nb._samples_neigh_ranges.cpu().numpy()]))
+  assert np.all(counts == expected)
+
+
+def test_find_neighbors_edge_cases():
+  rng = np.random.default_rng(3)
+  pts, bid = random_cloud(rng, 3, 500, 3)
+  g_ref, g = grid_pair(pts, bid, 3, 0.2)
+  # samples outside the bounding box are clamped into border cells
+  smp = np.array([[-0.5, 0.2, 0.2], [1.5, 1.5, 1.5], [0.5, 0.5, 0.5]], F32)
+  sbid = np.array([0, 1, 2], np.int32)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.2, smp, sbid)
+  assert_neigh_equal(nb_ref, nb)
+  # no neighbors at all (M == 0)
+  smp = np.array([[9.0, 9.0, 9.0]], F32); sbid = np.array([0], np.int32)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.2, smp, sbid)
+  assert nb._neighbors.shape == (0, 2)
+  assert_neigh_equal(nb_ref, nb)
+  # max_neighbors keeps the first ones in canonical order
+  nb_ref, nb = neigh_pair(g_ref, g, 0.2, max_neighbors=3)
+  assert_neigh_equal(nb_ref, nb)
+  # zero samples
+  r, nbh = ops.find_neighbors(torch.zeros((0, 3), device=DEV), torch.zeros(0, dtype=torch.int32, device=DEV),
+                              g._sorted_points, g._sorted_keys, g.get_DS(), g._num_cells,
+                              g._scaled_aabb_min, g._inv_cell_sizes, torch.ones(3, device=DEV))
+  assert r.shape[0] == 0 and nbh.shape == (0, 2)
+
+
+def test_single_point_cloud():
+  pts = np.array([[0.3, 0.4, 0.5]], F32); bid = np.zeros(1, np.int32)
+  g_ref, g = grid_pair(pts, bid, 1, 0.1)
+  assert_grid_equal(g_ref, g)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.1)
+  assert_neigh_equal(nb_ref, nb)
+  assert nb._neighbors.cpu().numpy().tolist() == [[0, 0]]
+
+
+@pytest.mark.parametrize("d", [2, 3, 4])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_compute_pdf_and_grads(d, mode):
+  rng = np.random.default_rng(300 + d)
+  b = 3
+  pts, bid = random_cloud(rng, b, 1500, d)
+  radius, bw = 0.25, 0.2
+  g_ref, g = grid_pair(pts, bid, b, radius)
+  nb_ref, nb = neigh_pair(g_ref, g, radius)
+  assert_neigh_equal(nb_ref, nb)
+  inv_bw = np.repeat(F32(1 / bw), d); inv_r = np.repeat(F32(1 / radius), d)
+  ref = orc.compute_pdf(g_ref.sorted_points, nb_ref.neighbors, nb_ref.ranges, inv_bw, inv_r, mode)
+  got = ops.compute_pdf_with_pt_grads(g._sorted_points, nb._neighbors, nb._samples_neigh_ranges,
+                                      t(inv_bw), t(inv_r), mode)
+  close(got.cpu().numpy(), ref)
+  gvec = rng.normal(size=len(pts)).astype(F32)
+  ref_g = orc.compute_pdf_pt_grads(g_ref.sorted_points, nb_ref.neighbors, nb_ref.ranges, inv_bw,
+                                   inv_r, gvec, mode)
+  got_g = ops.compute_pdf_pt_grads(g._sorted_points, nb._neighbors, nb._samples_neigh_ranges,
+                                   t(inv_bw), t(inv_r), t(gvec), mode)
+  close(got_g.cpu().numpy(), ref_g, rel=2e-4)
+
+
+def test_pdf_matches_sklearn_kde():
+  """compute_pdf_test.py:32-108 with a radius that covers the whole cloud."""
+  from sklearn.neighbors import KernelDensity
+  rng = np.random.default_rng(11)
+  d, b, n_per, bw, cell = 3, 4, 100, 0.1, float(np.sqrt(3))
+  pts = rng.uniform(0, 1, (b * n_per, d)).astype(F32)
+  bid = np.repeat(np.arange(b), n_per).astype(np.int32)
+  g = pc.Grid(pc.PointCloud(t(pts), t(bid), b), cell)
+  nb = pc.Neighborhood(g, cell)
+  nb.compute_pdf(bandwidth=bw, mode=0)
+  pdf = nb._point_pdf.cpu().numpy() / n_per
+  sp = g._sorted_points.cpu().numpy(); sb = g._sorted_batch_ids.cpu().numpy()
+  ref = np.zeros(len(pts))
+  for i in range(b):
+    x = sp[sb == i].astype(np.float64) / cell
+    ref[sb == i] = np.exp(KernelDensity(bandwidth=bw).fit(x).score_samples(x))
+  np.testing.assert_allclose(pdf, ref, rtol=1e-4)
+
+
+BP_CASES = [(1, 8, 2), (3, 16, 3), (7, 32, 3), (8, 64, 3), (16, 8, 4), (32, 16, 3),
+            (64, 32, 3), (128, 16, 3), (136, 16, 3), (256, 16, 3), (64, 64, 3)]
+
+
+@pytest.mark.parametrize("c,k,d", BP_CASES)
+def test_basis_proj_and_grads(c, k, d):
+  rng = np.random.default_rng(400 + c + k)
+  b = 3
+  pts, bid = random_cloud(rng, b, 1200, d)
+  smp, sbid = random_cloud(rng, b, 150, d)
+  radius = 0.3
+  g_ref, g = grid_pair(pts, bid, b, radius)
+  nb_ref, nb = neigh_pair(g_ref, g, radius, smp, sbid)
+  m = len(nb_ref.neighbors)
+  basis = rng.normal(size=(m, k)).astype(F32)
+  feat = rng.normal(size=(len(pts), c)).astype(F32)
+  ref = orc.basis_proj(basis, feat, nb_ref.original_neigh_ids, nb_ref.ranges)
+  got = ops.basis_proj(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges)
+  close(got.cpu().numpy(), ref)
+  gin = rng.normal(size=ref.shape).astype(F32)
+  ref_db, ref_df = orc.basis_proj_grads(basis, feat, nb_ref.original_neigh_ids, nb_ref.ranges, gin)
+  got_db, got_df = ops.basis_proj_grads(t(basis), t(feat), nb._original_neigh_ids,
+                                        nb._samples_neigh_ranges, t(gin))
+  close(got_db.cpu().numpy(), ref_db)
+  close(got_df.cpu().numpy(), ref_df)
+
+
+def test_basis_proj_rejects_bad_shapes():
+  z = torch.zeros
+  with pytest.raises(TfgpcError, match="basis functions"):
+    ops.basis_proj(z((4, 12), device=DEV), z((4, 8), device=DEV),
+                   z((4, 2), dtype=torch.int32, device=DEV), z(2, dtype=torch.int32, device=DEV))
+  with pytest.raises(TfgpcError, match="input features"):
+    ops.basis_proj(z((4, 16), device=DEV), z((4, 9), device=DEV),
+                   z((4, 2), dtype=torch.int32, device=DEV), z(2, dtype=torch.int32, device=DEV))
+  with pytest.raises(TfgpcError, match="same number of basis"):
+    ops.basis_proj(z((5, 16), device=DEV), z((4, 8), device=DEV),
+                   z((4, 2), dtype=torch.int32, device=DEV), z(2, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("d,cell", [(2, 0.1), (3, 0.1), (3, 0.3), (4, 0.25)])
+def test_sampling_poisson_and_average(d, cell):
+  rng = np.random.default_rng(500 + d)
+  b = 4
+  pts, bid = random_cloud(rng, b, 4000, d)
+  g_ref, g = grid_pair(pts, bid, b, cell)
+  nb_ref, nb = neigh_pair(g_ref, g, cell)
+  for mode, name in ((0, 'poisson'), (1, 'average')):
+    rp, rb, ri = pr.sample(nb_ref, mode)
+    cloud, idx = pc.sample(nb, name)
+    assert np.array_equal(cloud._batch_ids.cpu().numpy(), rb)
+    if mode == 0:
+      assert np.array_equal(idx.cpu().numpy(), ri)
+      assert np.array_equal(cloud._points.cpu().numpy(), rp)
+    else:
+      assert idx is None
+      close(cloud._points.cpu().numpy(), rp)
+
+
+@pytest.mark.parametrize("n,scale", [(6, 1), (100, 5)])
+def test_poisson_lattice_known_answer(n, scale):
+  """sample_test.py:61-78: n lines of n points, every second point survives."""
+  tk = np.linspace(0, scale, num=n)
+  pts = np.array(np.meshgrid(tk, tk)).T.reshape(-1, 2).astype(F32)
+  bid = np.repeat(np.arange(n), n).astype(np.int32)
+  cs = scale * np.array([2, 2], F32) / n
+  g = pc.Grid(pc.PointCloud(t(pts), t(bid), n), cs)
+  nb = pc.Neighborhood(g, cs)
+  cloud, _ = pc.sample(nb, 'poisson')
+  assert cloud._points.shape[0] == n * n // 2
+
+
+def test_point_hierarchy_matches_oracle():
+  pts, bid = synthetic.gaussian_mixture_clouds(3, 4000, seed=3)
+  radii = [0.025, 0.05, 0.1, 0.2]
+  ref = pr.point_hierarchy(pts, bid, 3, radii, mode=0)
+  hier = pc.PointHierarchy(pc.PointCloud(t(pts), t(bid), 3), radii, 'poisson')
+  for lvl in range(1, 5):
+    assert np.array_equal(hier._point_clouds[lvl]._points.cpu().numpy(), ref[lvl][0])
+    assert np.array_equal(hier._sample_indices[lvl - 1].cpu().numpy(), ref[lvl][2])
+  ref = pr.point_hierarchy(pts, bid, 3, radii, mode=1)
+  hier = pc.PointHierarchy(pc.PointCloud(t(pts), t(bid), 3), radii, 'average')
+  for lvl in range(1, 5):
+    close(hier._point_clouds[lvl]._points.cpu().numpy(), ref[lvl][0])
+    assert np.array_equal(hier._point_clouds[lvl]._batch_ids.cpu().numpy(), ref[lvl][1])
+
+
+def test_results_are_deterministic():
+  pts, bid = synthetic.surface_clouds(2, seed=1, min_points=3000, max_points=5000)
+  outs = []
+  for _ in range(2):
+    g = pc.Grid(pc.PointCloud(t(pts), t(bid), 2), 0.05)
+    nb = pc.Neighborhood(g, 0.05)
+    cloud, idx = pc.sample(nb, 'poisson')
+    outs.append((g._sorted_indices.cpu().numpy().tobytes(), nb._neighbors.cpu().numpy().tobytes(),
+                 idx.cpu().numpy().tobytes()))
+  assert outs[0] == outs[1]
