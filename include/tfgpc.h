@@ -190,6 +190,48 @@ int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
                          float* sample_pts_out, int32_t* sample_batch_ids_out,
                          int32_t* sample_indices_out);
 
+/* ---- MCConv: basis projection fused with the weight GEMMs ----------------
+ * Replaces the BasisProj -> tf.matmul pair of pylib/pc/layers/MCConv.py:
+ * 174-191 (forward) and what TensorFlow's autodiff makes of it (matmul
+ * gradients + BasisProjGrads, custom_ops_wrapper.py:192-198) without writing
+ * the fp32 [ns, C, K] tensor: the projection is produced as the bf16 operand
+ * pair of a tcgen05 tensor-core GEMM (three bf16 passes, fp32 accumulate).
+ * weights [C*K, Cout] row-major in the projection's own reduction order
+ * (row c*K + k; for num_mlps == 1 this is MCConv's final weight matrix as
+ * stored), out [ns, Cout].  Cout must be a multiple of 4.
+ * Backward: out_grads [ns, Cout] -> dbasis_out [M, K], dfeat_out [n_in, C],
+ * dweights_out [C*K, Cout] (all overwritten).  x_in_workspace != 0 tells it
+ * that `ws` still holds the projection written by the forward call for the
+ * same inputs (ws sized for backward); otherwise it is recomputed.
+ * tfgpc_mcconv_status blocks on the stream and returns TFGPC_ETIMEOUT if a
+ * bounded wait inside one of the GEMM kernels that used `ws` ran out. */
+size_t tfgpc_mcconv_workspace_bytes(int K, int C, int Cout, int64_t ns,
+                                    int backward);
+int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_t ns,
+                         int64_t n_in, int64_t M, const float* basis,
+                         const float* features, const int32_t* neighbors,
+                         const int32_t* ranges, const float* weights,
+                         float* out, void* ws, size_t ws_bytes);
+int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64_t ns,
+                          int64_t n_in, int64_t M, const float* basis,
+                          const float* features, const int32_t* neighbors,
+                          const int32_t* ranges, const float* weights,
+                          const float* out_grads, int x_in_workspace,
+                          float* dbasis_out, float* dfeat_out,
+                          float* dweights_out, void* ws, size_t ws_bytes);
+int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out);
+
+/* ---- fp32 matrix product on the tensor cores -----------------------------
+ * c[M,N] = op(a) * op(b) in fp32 accuracy (three bf16 passes), the tf.matmul
+ * of MCConv.py:187-191 as a stand-alone call.  a is [M,K] row-major, or
+ * [K,M] if a_transposed; b is [K,N] row-major, or [N,K] if b_transposed.
+ * Row lengths must be multiples of 8.  The first int of ws is the same
+ * time-out flag that tfgpc_mcconv_status reads. */
+size_t tfgpc_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K,
+                     const float* a, int a_transposed, const float* b,
+                     int b_transposed, float* c, void* ws, size_t ws_bytes);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,12 @@ SYMBOLS = {
     "tfgpc_sampling_workspace_bytes": c_sz,
     "tfgpc_sampling_count": c_int,
     "tfgpc_sampling_store": c_int,
+    "tfgpc_mcconv_workspace_bytes": c_sz,
+    "tfgpc_mcconv_forward": c_int,
+    "tfgpc_mcconv_backward": c_int,
+    "tfgpc_mcconv_status": c_int,
+    "tfgpc_matmul_workspace_bytes": c_sz,
+    "tfgpc_matmul_f32": c_int,
 }
 
 

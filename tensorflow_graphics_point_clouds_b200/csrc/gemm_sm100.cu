@@ -1,0 +1,541 @@
+// tcgen05 / TMEM / TMA GEMM with 3-pass bf16 operand splitting (see
+// gemm_sm100.cuh).  Persistent kernel, one CTA per SM, warp-specialised:
+//   warp 0     TMA producer: streams 128 x 64 tiles of A (hi, mid) and
+//              BN x 64 tiles of B (hi, mid) into a shared-memory ring;
+//   warp 1     allocates tensor memory and issues the tcgen05.mma instructions
+//              (one elected lane); completion is tracked with tcgen05.commit
+//              on mbarriers, which also hands ring slots back to the producer;
+//   warps 2-5  epilogue: tcgen05.ld the 128 x BN fp32 accumulator out of
+//              tensor memory and store it, while the MMA warp already works on
+//              the next tile in the second accumulator buffer.
+// Every wait is bounded: after about a second without progress the kernel sets
+// the caller's error flag, stops waiting and drains, so it always terminates
+// and frees its tensor memory.
+#include <cuda.h>
+
+#include "gemm_sm100.cuh"
+#include "basis_proj.cuh"
+
+namespace tfgpc {
+
+namespace {
+
+constexpr int kBM = 128;           // rows of C per tile (TMEM lanes)
+constexpr int kBNMax = 256;        // columns of C per tile (TMEM columns per buffer)
+constexpr int kBK = 64;            // reduction elements per ring slot: 128 bytes of bf16
+constexpr int kStages = 2;
+constexpr int kUmmaK = 16;         // reduction elements per tcgen05.mma (kind::f16)
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;     // two accumulator buffers of 256 columns
+constexpr uint32_t kABytes = kBM * kBK * 2;        // one A tile (hi or mid)
+constexpr uint32_t kBBytes = kBNMax * kBK * 2;     // one B tile (hi or mid)
+constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kBBytes;
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  `abort_flag` lives in shared memory: once any role gave up,
+// all later waits of the CTA return at once.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* err_flag) {
+  if (mbar_try_wait(bar, parity)) return;
+  const unsigned long long t0 = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      atomicExch(err_flag, 1);
+      return;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+// mbarrier arrive once all tcgen05.mma issued so far by this thread are done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a 128-byte-swizzled tile (descriptor
+// version 1 of sm_100): start address, leading and stride byte offsets in
+// 16-byte units, layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+struct TileSchedule {
+  int m_tiles, n_tiles, k_splits;
+  int k_blocks;         // ring slots over the whole reduction
+  int k_blocks_per_split;
+};
+
+struct Barriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
+                   const __grid_constant__ CUtensorMap tm_a_mid,
+                   const __grid_constant__ CUtensorMap tm_b_hi,
+                   const __grid_constant__ CUtensorMap tm_b_mid, float* __restrict__ c,
+                   int64_t ldc, int64_t split_stride, int64_t m_total, int64_t n_total, int bn,
+                   uint32_t idesc, TileSchedule sch, int* err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  // the swizzled tiles need 1024-byte alignment
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  Barriers* bars = (Barriers*)(smem + (size_t)kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars->acc_full[b]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+    }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  // tile -> (m, n, split); m fastest so that CTAs running together share B/k-slices
+  auto decode = [&](int t, int& m, int& n, int& sp) {
+    m = t % sch.m_tiles;
+    int r = t / sch.m_tiles;
+    n = r % sch.n_tiles;
+    sp = r / sch.n_tiles;
+  };
+  const uint32_t b_tile_bytes = (uint32_t)bn * kBK * 2;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        int m, n, sp;
+        decode(t, m, n, sp);
+        const int kb0 = sp * sch.k_blocks_per_split;
+        const int kb1 = min(kb0 + sch.k_blocks_per_split, sch.k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1, abort_flag, err_flag);
+          const uint32_t full = smem_u32(&bars->full[s]);
+          mbar_expect_tx(full, 2 * kABytes + 2 * b_tile_bytes);
+          uint8_t* st = smem + (size_t)s * kStageBytes;
+          const uint32_t a_hi = smem_u32(st), a_mid = a_hi + kABytes;
+          const uint32_t b_hi = a_mid + kABytes, b_mid = b_hi + kBBytes;
+          if (!A_MN) {
+            tma_load_2d(a_hi, &tm_a_hi, kb * kBK, m * kBM, full);
+            tma_load_2d(a_mid, &tm_a_mid, kb * kBK, m * kBM, full);
+          } else {
+            // two boxes of 64 (M) x 64 (K rows): 8 KB each
+            for (int j = 0; j < kBM / 64; ++j) {
+              tma_load_2d(a_hi + j * 8192, &tm_a_hi, m * kBM + j * 64, kb * kBK, full);
+              tma_load_2d(a_mid + j * 8192, &tm_a_mid, m * kBM + j * 64, kb * kBK, full);
+            }
+          }
+          if (!B_MN) {
+            tma_load_2d(b_hi, &tm_b_hi, kb * kBK, n * bn, full);
+            tma_load_2d(b_mid, &tm_b_mid, kb * kBK, n * bn, full);
+          } else {
+            for (int j = 0; j < bn / 64; ++j) {
+              tma_load_2d(b_hi + j * 8192, &tm_b_hi, n * bn + j * 64, kb * kBK, full);
+              tma_load_2d(b_mid + j * 8192, &tm_b_mid, n * bn + j * 64, kb * kBK, full);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      int tile_iter = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
+        int m, n, sp;
+        decode(t, m, n, sp);
+        const int kb0 = sp * sch.k_blocks_per_split;
+        const int kb1 = min(kb0 + sch.k_blocks_per_split, sch.k_blocks);
+        const int buf = tile_iter & 1;
+        mbar_wait(smem_u32(&bars->acc_empty[buf]), ((tile_iter >> 1) & 1) ^ 1, abort_flag, err_flag);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kBNMax;
+        uint32_t accumulate = 0;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag, err_flag);
+          tc_fence_after();
+          uint8_t* st = smem + (size_t)s * kStageBytes;
+          const uint32_t a_hi = smem_u32(st), a_mid = a_hi + kABytes;
+          const uint32_t b_hi = a_mid + kABytes, b_mid = b_hi + kBBytes;
+          // K-major: rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart;
+          // one UMMA_K step is 32 bytes inside the row.
+          // MN-major: 64 (MN) x 8 (K) atoms of 1024 bytes; atoms along K are
+          // 1024 bytes apart (stride offset), blocks of 64 along MN are 8192
+          // bytes apart (leading offset); one UMMA_K step is 16 K rows.
+          const uint32_t a_step = A_MN ? 16 * 128 : 32;
+          const uint32_t b_step = B_MN ? 16 * 128 : 32;
+          const uint32_t a_lbo = A_MN ? 8192 : 16, b_lbo = B_MN ? 8192 : 16;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, 1024);
+            const uint64_t da_mid = make_desc(a_mid + kk * a_step, a_lbo, 1024);
+            const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, 1024);
+            const uint64_t db_mid = make_desc(b_mid + kk * b_step, b_lbo, 1024);
+            umma_bf16(d_tmem, da_hi, db_mid, idesc, accumulate);
+            umma_bf16(d_tmem, da_mid, db_hi, idesc, 1u);
+            umma_bf16(d_tmem, da_hi, db_hi, idesc, 1u);
+            accumulate = 1u;
+          }
+          umma_commit(smem_u32(&bars->empty[s]));  // slot free once these MMAs have read it
+        }
+        umma_commit(smem_u32(&bars->acc_full[buf]));
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter ...
+    int tile_iter = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
+      int m, n, sp;
+      decode(t, m, n, sp);
+      const int buf = tile_iter & 1;
+      mbar_wait(smem_u32(&bars->acc_full[buf]), (tile_iter >> 1) & 1, abort_flag, err_flag);
+      tc_fence_after();
+      const int64_t row = (int64_t)m * kBM + quarter * 32 + lane;
+      float* crow = c + (int64_t)sp * split_stride + row * ldc + (int64_t)n * bn;
+      const int64_t cols_left = n_total - (int64_t)n * bn;
+      for (int c0 = 0; c0 < bn; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                               (uint32_t)(buf * kBNMax + c0);
+        tmem_ld_32x32(taddr, r);
+        if (row < m_total && !*abort_flag) {
+          if (c0 + 32 <= cols_left && (ldc % 4 == 0)) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(crow + c0 + 4 * q) =
+                  make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (c0 + q < cols_left) crow[c0 + q] = __uint_as_float(r[q]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: dim0 (contiguous) x dim1 rows, 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const __nv_bfloat16* base, int64_t dim0, int64_t dim1, int64_t ld,
+             int box0, int box1) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(TFGPC_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((uintptr_t)base % 16 != 0 || (ld * 2) % 16 != 0)
+    return fail(TFGPC_EINVAL, "tensor-core GEMM operands need 16-byte aligned rows (ld %lld)",
+                (long long)ld);
+  cuuint64_t dims[2] = {(cuuint64_t)dim0, (cuuint64_t)dim1};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TFGPC_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return TFGPC_OK;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: D fp32, A and B bf16.
+uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;                       // D format: f32
+  d |= 1u << 7;                       // A format: bf16
+  d |= 1u << 10;                      // B format: bf16
+  d |= (a_mn ? 1u : 0u) << 15;        // A major: 0 = K, 1 = MN
+  d |= (b_mn ? 1u : 0u) << 16;        // B major
+  d |= (uint32_t)(n >> 3) << 17;      // N / 8
+  d |= (uint32_t)(m >> 4) << 24;      // M / 16
+  return d;
+}
+
+template <bool A_MN, bool B_MN>
+int launch(cudaStream_t st, const CUtensorMap* maps, float* c, int64_t ldc, int64_t split_stride,
+           int64_t M, int64_t N, int bn, TileSchedule sch, int* err_flag) {
+  auto kern = gemm_bf16x3_kernel<A_MN, B_MN>;
+  TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kSmemBytes));
+  const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], c, ldc,
+                                           split_stride, M, N, bn, make_idesc(kBM, bn, A_MN, B_MN),
+                                           sch, err_flag);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+__global__ void split_kernel(const float* __restrict__ x, int64_t n, __nv_bfloat16* __restrict__ hi,
+                             __nv_bfloat16* __restrict__ mid) {
+  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n && ((uintptr_t)x % 16 == 0) && ((uintptr_t)hi % 8 == 0) && ((uintptr_t)mid % 8 == 0)) {
+    float4 v = __ldg(reinterpret_cast<const float4*>(x + i));
+    __nv_bfloat16 h[4], l[4];
+    split_bf16(v.x, h[0], l[0]); split_bf16(v.y, h[1], l[1]);
+    split_bf16(v.z, h[2], l[2]); split_bf16(v.w, h[3], l[3]);
+    *reinterpret_cast<uint2*>(hi + i) = *reinterpret_cast<uint2*>(h);
+    *reinterpret_cast<uint2*>(mid + i) = *reinterpret_cast<uint2*>(l);
+  } else {
+    for (int64_t j = i; j < n && j < i + 4; ++j) split_bf16(__ldg(x + j), hi[j], mid[j]);
+  }
+}
+
+__global__ void split_transpose_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
+                                       __nv_bfloat16* __restrict__ hi_t,
+                                       __nv_bfloat16* __restrict__ mid_t) {
+  __shared__ float tile[32][33];
+  const int64_t r0 = (int64_t)blockIdx.y * 32, c0 = (int64_t)blockIdx.x * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int64_t r = r0 + j, cc = c0 + threadIdx.x;
+    tile[j][threadIdx.x] = (r < rows && cc < cols) ? __ldg(x + r * cols + cc) : 0.0f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int64_t cc = c0 + j, r = r0 + threadIdx.x;
+    if (cc < cols && r < rows) {
+      __nv_bfloat16 h, l;
+      split_bf16(tile[threadIdx.x][j], h, l);
+      hi_t[cc * rows + r] = h;
+      mid_t[cc * rows + r] = l;
+    }
+  }
+}
+
+__global__ void reduce_splits_kernel(const float* __restrict__ partial, int splits, int64_t stride,
+                                     int64_t n, float* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.0f;
+  for (int s = 0; s < splits; ++s) acc += __ldg(partial + (int64_t)s * stride + i);
+  out[i] = acc;
+}
+
+}  // namespace
+
+int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K) {
+  const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBNMax - 1) / kBNMax);
+  const int64_t k_blocks = (K + kBK - 1) / kBK;
+  int64_t splits = sm_count() / (tiles > 0 ? tiles : 1);
+  if (splits < 1) splits = 1;
+  if (splits > k_blocks) splits = k_blocks > 0 ? k_blocks : 1;
+  return (int)splits;
+}
+
+int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,
+                const GemmOperand& b, float* c, int64_t ldc, int k_splits, int64_t split_stride,
+                int* err_flag) {
+  TFGPC_REQUIRE(M > 0 && N > 0 && K > 0, "GEMM expects positive sizes");
+  TFGPC_REQUIRE(M < (int64_t)INT32_MAX && N < (int64_t)INT32_MAX && K < (int64_t)INT32_MAX,
+                "GEMM sizes must stay below 2^31");
+  TFGPC_REQUIRE(k_splits >= 1, "GEMM expects k_splits >= 1");
+  const bool a_mn = a.major == Major::MN, b_mn = b.major == Major::MN;
+  // columns of C per tile: a multiple of 32 (epilogue chunk), of 64 for MN-major B boxes
+  int bn = (int)(N < kBNMax ? N : kBNMax);
+  const int gran = b_mn ? 64 : 32;
+  bn = (bn + gran - 1) / gran * gran;
+  CUtensorMap maps[4];
+  int rc;
+  const __nv_bfloat16* ap[2] = {a.hi, a.mid};
+  const __nv_bfloat16* bp[2] = {b.hi, b.mid};
+  for (int i = 0; i < 2; ++i) {
+    rc = a_mn ? make_map(&maps[i], ap[i], M, K, a.ld, 64, kBK)
+              : make_map(&maps[i], ap[i], K, M, a.ld, kBK, kBM);
+    if (rc) return rc;
+    rc = b_mn ? make_map(&maps[2 + i], bp[i], N, K, b.ld, 64, kBK)
+              : make_map(&maps[2 + i], bp[i], K, N, b.ld, kBK, bn);
+    if (rc) return rc;
+  }
+  TileSchedule sch;
+  sch.m_tiles = (int)((M + kBM - 1) / kBM);
+  sch.n_tiles = (int)((N + bn - 1) / bn);
+  sch.k_blocks = (int)((K + kBK - 1) / kBK);
+  sch.k_splits = k_splits < sch.k_blocks ? k_splits : sch.k_blocks;
+  sch.k_blocks_per_split = (sch.k_blocks + sch.k_splits - 1) / sch.k_splits;
+  // drop empty trailing slices
+  sch.k_splits = (sch.k_blocks + sch.k_blocks_per_split - 1) / sch.k_blocks_per_split;
+  if (sch.k_splits < k_splits) {
+    // the caller sums k_splits slices: the unused ones must read as zero
+    TFGPC_CUDA(cudaMemsetAsync(c + (int64_t)sch.k_splits * split_stride, 0,
+                               sizeof(float) * (size_t)(k_splits - sch.k_splits) * split_stride,
+                               stream));
+  }
+  if (a_mn && b_mn) return launch<true, true>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
+  if (a_mn) return launch<true, false>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
+  if (b_mn) return launch<false, true>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
+  return launch<false, false>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
+}
+
+int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16* hi,
+                  __nv_bfloat16* mid) {
+  if (n <= 0) return TFGPC_OK;
+  split_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, stream>>>(x, n, hi, mid);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+int split_transpose_to_bf16(cudaStream_t stream, const float* x, int64_t rows, int64_t cols,
+                            __nv_bfloat16* hi_t, __nv_bfloat16* mid_t) {
+  if (rows <= 0 || cols <= 0) return TFGPC_OK;
+  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+  split_transpose_kernel<<<grid, dim3(32, 8), 0, stream>>>(x, rows, cols, hi_t, mid_t);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+int reduce_splits(cudaStream_t stream, const float* partial, int splits, int64_t stride, int64_t n,
+                  float* out) {
+  if (n <= 0) return TFGPC_OK;
+  reduce_splits_kernel<<<blocks_for(n, 256), 256, 0, stream>>>(partial, splits, stride, n, out);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+}  // namespace tfgpc

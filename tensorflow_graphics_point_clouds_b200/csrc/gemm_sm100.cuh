@@ -1,0 +1,52 @@
+// fp32-accurate GEMM on the sm_100a tensor cores (tcgen05 + TMEM + TMA).
+//
+// C[M,N] (fp32) = A[M,K] * B[N,K]^T where both operands are given as two bf16
+// arrays each, x ~= hi + mid (see split_bf16): three tensor-core passes
+// (hi*hi + hi*mid + mid*hi) accumulate in fp32 in tensor memory and reproduce
+// the fp32 product to about 2^-17 relative, well inside the 1e-4 parity bound,
+// where a single bf16 or tf32 pass is not.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace tfgpc {
+
+// How an operand lies in global memory.
+enum class Major : int {
+  K = 0,   // [rows, K] row-major: the reduction index is contiguous
+  MN = 1,  // [K, rows] row-major: the M (or N) index is contiguous
+};
+
+struct GemmOperand {
+  const __nv_bfloat16* hi;
+  const __nv_bfloat16* mid;
+  int64_t ld;  // elements between consecutive rows of the global array
+  Major major;
+};
+
+// C = A * B^T over k in [0, K).  With k_splits > 1 the reduction range is cut
+// into k_splits slices and slice s writes its partial result to
+// C + s * split_stride (the caller sums the slices).  M, N, K are the logical
+// sizes; edges are handled by TMA zero fill and masked stores.
+// err_flag (device int, zero-initialised by the caller) is set to 1 if a
+// bounded wait inside the kernel ran out.
+int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,
+                const GemmOperand& b, float* c, int64_t ldc, int k_splits, int64_t split_stride,
+                int* err_flag);
+
+// Number of k slices that fills the GPU for an [M,N] output with reduction K.
+int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K);
+
+// x -> (hi, mid) over n elements.
+int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16* hi,
+                  __nv_bfloat16* mid);
+// [rows, cols] fp32 -> transposed [cols, rows] bf16 pair.
+int split_transpose_to_bf16(cudaStream_t stream, const float* x, int64_t rows, int64_t cols,
+                            __nv_bfloat16* hi_t, __nv_bfloat16* mid_t);
+// out[i] = sum_s partial[s * stride + i], i < n.
+int reduce_splits(cudaStream_t stream, const float* partial, int splits, int64_t stride,
+                  int64_t n, float* out);
+
+}  // namespace tfgpc

@@ -1,0 +1,209 @@
+// Monte-Carlo convolution forward and backward: the basis projection followed
+// by (forward) or preceded by (backward) the weight GEMMs on the tensor cores.
+//
+// Forward:  X[s, c*K+k] = sum_m basis[m,k] * feat[nbr(m), c]   (basis_proj.cu,
+//           written directly as the bf16 hi/mid pair the GEMM consumes)
+//           out = X * W                                        (gemm_sm100.cu)
+// Backward: dX = dOut * W^T, (dbasis, dfeat) = BasisProjGrads(dX),
+//           dW = X^T * dOut  (split over the sample range, slices summed).
+// This is the pair BasisProj -> tf.matmul of pylib/pc/layers/MCConv.py:174-191
+// and its autodiff, without the fp32 [Ns, C, K] tensor between the two.
+#include "basis_proj.cuh"
+#include "gemm_sm100.cuh"
+
+namespace tfgpc {
+
+int basis_proj_split(cudaStream_t st, int K, int C, int64_t ns, const float* basis,
+                     const float* feat, const int32_t* neigh, const int32_t* ranges,
+                     __nv_bfloat16* hi, __nv_bfloat16* mid);
+
+namespace {
+
+struct McWs {
+  int* err;                  // [0] set by a GEMM whose bounded wait ran out
+  __nv_bfloat16 *x_hi, *x_mid;      // [ns, C*K]
+  __nv_bfloat16 *w_hi, *w_mid;      // [C*K, Cout]
+  __nv_bfloat16 *g_hi, *g_mid;      // [ns, Cout]   (backward)
+  float* dx;                        // [ns, C*K]    (backward)
+  float* dw_part;                   // [splits, C*K, Cout] (backward)
+  int dw_splits;
+  size_t bytes;
+};
+
+McWs carve(void* ws, int K, int C, int Cout, int64_t ns, bool backward) {
+  McWs w;
+  char* p = (char*)ws;
+  auto take = [&](size_t b) { char* r = p; p += align_up(b, 1024); return r; };
+  const size_t ck = (size_t)C * K;
+  w.err = (int*)take(256);
+  w.x_hi = (__nv_bfloat16*)take((size_t)ns * ck * 2);
+  w.x_mid = (__nv_bfloat16*)take((size_t)ns * ck * 2);
+  w.w_hi = (__nv_bfloat16*)take(ck * Cout * 2);
+  w.w_mid = (__nv_bfloat16*)take(ck * Cout * 2);
+  w.dw_splits = 1;
+  w.g_hi = w.g_mid = nullptr; w.dx = w.dw_part = nullptr;
+  if (backward) {
+    w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
+    w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
+    w.dx = (float*)take((size_t)ns * ck * 4);
+    w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
+    w.dw_part = (float*)take((size_t)w.dw_splits * ck * Cout * 4);
+  }
+  w.bytes = (size_t)(p - (char*)ws);
+  return w;
+}
+
+int check_mc_args(const char* op, int K, int C, int Cout, int64_t ns, int64_t n_in, int64_t M) {
+  TFGPC_REQUIRE(valid_basis(K), "%s expects a valid number of basis functions.", op);
+  TFGPC_REQUIRE(valid_features(C), "%s expects a valid number of input features, between 1 and 8 "
+                "or multiple of 8", op);
+  TFGPC_REQUIRE(Cout > 0 && Cout % 4 == 0, "%s expects a number of output features that is a "
+                "multiple of 4", op);
+  TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && n_in >= 0 && n_in < (int64_t)INT32_MAX &&
+                M >= 0 && M <= (int64_t)INT32_MAX, "%s expects 0 <= ns, n_in, M < 2^31", op);
+  return TFGPC_OK;
+}
+
+}  // namespace
+}  // namespace tfgpc
+
+using namespace tfgpc;
+
+extern "C" size_t tfgpc_mcconv_workspace_bytes(int K, int C, int Cout, int64_t ns, int backward) {
+  if (K <= 0 || C <= 0 || Cout <= 0 || ns < 0) return 0;
+  return carve(nullptr, K, C, Cout, ns, backward != 0).bytes + 1024;
+}
+
+extern "C" int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in,
+                                    int64_t M, const float* basis, const float* features,
+                                    const int32_t* neighbors, const int32_t* ranges,
+                                    const float* weights, float* out, void* ws, size_t ws_bytes) {
+  int rc = check_mc_args("MCConvForward", K, C, Cout, ns, n_in, M);
+  if (rc) return rc;
+  if (ns == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(ranges && weights && out && ws && (M == 0 || (basis && features && neighbors)),
+                "MCConvForward got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)ws % 1024 == 0,
+                "MCConvForward expects 16-byte aligned buffers and a 1024-byte aligned workspace");
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0))
+    return fail(TFGPC_ENOMEM, "MCConvForward workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0));
+  cudaStream_t st = (cudaStream_t)stream;
+  McWs w = carve(ws, K, C, Cout, ns, false);
+  const int64_t ck = (int64_t)C * K;
+  TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
+  rc = basis_proj_split(st, K, C, ns, basis, features, neighbors, ranges, w.x_hi, w.x_mid);
+  if (rc) return rc;
+  rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
+  if (rc) return rc;
+  GemmOperand a{w.x_hi, w.x_mid, ck, Major::K};
+  GemmOperand b{w.w_hi, w.w_mid, (int64_t)Cout, Major::MN};  // W is [C*K, Cout]: N contiguous
+  return gemm_bf16x3(st, ns, Cout, ck, a, b, out, Cout, 1, 0, w.err);
+}
+
+extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64_t ns,
+                                     int64_t n_in, int64_t M, const float* basis,
+                                     const float* features, const int32_t* neighbors,
+                                     const int32_t* ranges, const float* weights,
+                                     const float* out_grads, int x_in_workspace, float* dbasis_out,
+                                     float* dfeat_out, float* dweights_out, void* ws,
+                                     size_t ws_bytes) {
+  int rc = check_mc_args("MCConvBackward", K, C, Cout, ns, n_in, M);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t ck = (int64_t)C * K;
+  TFGPC_REQUIRE(dweights_out && weights, "MCConvBackward got a null pointer");
+  if (ns == 0 || M == 0) {
+    TFGPC_CUDA(cudaMemsetAsync(dweights_out, 0, sizeof(float) * (size_t)ck * Cout, st));
+    if (M > 0 && dbasis_out) TFGPC_CUDA(cudaMemsetAsync(dbasis_out, 0, sizeof(float) * (size_t)M * K, st));
+    if (n_in > 0 && dfeat_out) TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+    return TFGPC_OK;
+  }
+  TFGPC_REQUIRE(basis && features && neighbors && ranges && out_grads && dbasis_out && dfeat_out && ws,
+                "MCConvBackward got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out_grads % 16 == 0 &&
+                (uintptr_t)ws % 1024 == 0,
+                "MCConvBackward expects 16-byte aligned buffers and a 1024-byte aligned workspace");
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1))
+    return fail(TFGPC_ENOMEM, "MCConvBackward workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1));
+  McWs w = carve(ws, K, C, Cout, ns, true);
+  if (!x_in_workspace) {
+    TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
+    rc = basis_proj_split(st, K, C, ns, basis, features, neighbors, ranges, w.x_hi, w.x_mid);
+    if (rc) return rc;
+    rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
+    if (rc) return rc;
+  }
+  rc = split_to_bf16(st, out_grads, ns * Cout, w.g_hi, w.g_mid);
+  if (rc) return rc;
+  // dX[ns, C*K] = dOut[ns, Cout] * W^T: B rows are W's rows, reduction over Cout
+  GemmOperand g_k{w.g_hi, w.g_mid, (int64_t)Cout, Major::K};
+  GemmOperand w_k{w.w_hi, w.w_mid, (int64_t)Cout, Major::K};
+  rc = gemm_bf16x3(st, ns, ck, Cout, g_k, w_k, w.dx, ck, 1, 0, w.err);
+  if (rc) return rc;
+  rc = tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges, w.dx,
+                              dbasis_out, dfeat_out);
+  if (rc) return rc;
+  // dW[C*K, Cout] = X^T * dOut: both operands have the reduction (sample) index
+  // as their row index, i.e. they are MN-major
+  GemmOperand x_mn{w.x_hi, w.x_mid, ck, Major::MN};
+  GemmOperand g_mn{w.g_hi, w.g_mid, (int64_t)Cout, Major::MN};
+  rc = gemm_bf16x3(st, ck, Cout, ns, x_mn, g_mn, w.dw_part, Cout, w.dw_splits, ck * Cout, w.err);
+  if (rc) return rc;
+  return reduce_splits(st, w.dw_part, w.dw_splits, ck * Cout, ck * Cout, dweights_out);
+}
+
+extern "C" int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out) {
+  TFGPC_REQUIRE(ws && status_out, "mcconv_status got a null pointer");
+  int flag = 0;
+  TFGPC_CUDA(cudaMemcpyAsync(&flag, ws, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  TFGPC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  *status_out = flag ? TFGPC_ETIMEOUT : TFGPC_OK;
+  if (flag) return fail(TFGPC_ETIMEOUT, "a bounded wait inside the tensor-core GEMM ran out");
+  return TFGPC_OK;
+}
+
+// ---- plain fp32 matrix product on the same GEMM -------------------------------
+
+extern "C" size_t tfgpc_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 1024;
+  const int splits = gemm_pick_k_splits(M, N, K);
+  return 1024 + 2 * align_up((size_t)M * K * 2, 1024) + 2 * align_up((size_t)N * K * 2, 1024) +
+         (splits > 1 ? align_up((size_t)splits * M * N * 4, 1024) : 0) + 1024;
+}
+
+extern "C" int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K, const float* a,
+                                int a_transposed, const float* b, int b_transposed, float* c,
+                                void* ws, size_t ws_bytes) {
+  TFGPC_REQUIRE(M > 0 && N > 0 && K > 0, "matmul expects positive sizes");
+  TFGPC_REQUIRE(a && b && c && ws, "matmul got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)ws % 1024 == 0, "matmul expects a 1024-byte aligned workspace");
+  TFGPC_REQUIRE((a_transposed ? M : K) % 8 == 0 && (b_transposed ? K : N) % 8 == 0,
+                "matmul expects row lengths that are multiples of 8");
+  if (ws_bytes < tfgpc_matmul_workspace_bytes(M, N, K))
+    return fail(TFGPC_ENOMEM, "matmul workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_matmul_workspace_bytes(M, N, K));
+  cudaStream_t st = (cudaStream_t)stream;
+  char* p = (char*)ws;
+  int* err = (int*)p; p += 1024;
+  __nv_bfloat16* a_hi = (__nv_bfloat16*)p; p += align_up((size_t)M * K * 2, 1024);
+  __nv_bfloat16* a_mid = (__nv_bfloat16*)p; p += align_up((size_t)M * K * 2, 1024);
+  __nv_bfloat16* b_hi = (__nv_bfloat16*)p; p += align_up((size_t)N * K * 2, 1024);
+  __nv_bfloat16* b_mid = (__nv_bfloat16*)p; p += align_up((size_t)N * K * 2, 1024);
+  float* part = (float*)p;
+  TFGPC_CUDA(cudaMemsetAsync(err, 0, sizeof(int), st));
+  int rc = split_to_bf16(st, a, M * K, a_hi, a_mid);
+  if (rc) return rc;
+  rc = split_to_bf16(st, b, N * K, b_hi, b_mid);
+  if (rc) return rc;
+  // a is [M,K] (K-major) or, transposed, [K,M] (MN-major); b is [K,N] (MN-major)
+  // or, transposed, [N,K] (K-major)
+  GemmOperand ao{a_hi, a_mid, a_transposed ? M : K, a_transposed ? Major::MN : Major::K};
+  GemmOperand bo{b_hi, b_mid, b_transposed ? K : N, b_transposed ? Major::K : Major::MN};
+  const int splits = gemm_pick_k_splits(M, N, K);
+  if (splits <= 1) return gemm_bf16x3(st, M, N, K, ao, bo, c, N, 1, 0, err);
+  rc = gemm_bf16x3(st, M, N, K, ao, bo, part, N, splits, M * N, err);
+  if (rc) return rc;
+  return reduce_splits(st, part, splits, M * N, M * N, c);
+}

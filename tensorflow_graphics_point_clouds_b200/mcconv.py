@@ -1,0 +1,106 @@
+"""Monte-Carlo convolution on the fused C-ABI entry points.
+
+Mirrors `MCConv` of the reference (pylib/pc/layers/MCConv.py:36-278): the
+kernel MLP on the relative neighbor positions gives the per-neighbor basis
+(divided by the density estimate), the basis projection aggregates it with the
+input features, and the final weights map [C_in * K] to C_out.  The projection
+and the final matrix product run as one C-ABI call (tfgpc_mcconv_forward) and
+their gradients as another (tfgpc_mcconv_backward); the small kernel MLP
+([M, D] x [D, K]) stays in torch, like it stays in TensorFlow in the reference.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import c_i64, c_int, c_sz, ptr
+from .custom_ops import _stream, _f32, _i32, _workspace
+
+
+def matmul_f32(a, b, a_transposed=False, b_transposed=False):
+  """c = op(a) @ op(b) in fp32 accuracy on the tensor cores (tfgpc_matmul_f32)."""
+  a, b = _f32(a), _f32(b)
+  m, k = (a.shape[1], a.shape[0]) if a_transposed else a.shape
+  n = b.shape[0] if b_transposed else b.shape[1]
+  kb = b.shape[1] if b_transposed else b.shape[0]
+  if kb != k:
+    raise _lib.TfgpcError(1, "matmul expects matching inner dimensions")
+  c = torch.empty((m, n), dtype=torch.float32, device=a.device)
+  nbytes = _lib.lib().tfgpc_matmul_workspace_bytes(c_i64(m), c_i64(n), c_i64(k))
+  ws = _workspace(nbytes, a.device)
+  _lib.check(_lib.lib().tfgpc_matmul_f32(
+      _stream(), c_i64(m), c_i64(n), c_i64(k), ptr(a), c_int(int(a_transposed)), ptr(b),
+      c_int(int(b_transposed)), ptr(c), ptr(ws), c_sz(nbytes)))
+  status = c_int(0)
+  _lib.check(_lib.lib().tfgpc_mcconv_status(_stream(), ptr(ws), ctypes.byref(status)))
+  return c
+
+
+class ProjectionGemm:
+  """Holds the workspace of one (K, C, Cout, Ns) problem and runs the fused
+  forward / backward entry points on it."""
+
+  def __init__(self, k, c, cout, ns, device, backward=True):
+    self.k, self.c, self.cout, self.ns = int(k), int(c), int(cout), int(ns)
+    self.backward_ws = bool(backward)
+    self.nbytes = _lib.lib().tfgpc_mcconv_workspace_bytes(
+        c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns), c_int(int(backward)))
+    self.ws = _workspace(self.nbytes, device)
+    self._x_valid = False
+
+  def forward(self, basis, features, neighbors, ranges, weights):
+    basis, features, weights = _f32(basis), _f32(features), _f32(weights)
+    neighbors, ranges = _i32(neighbors), _i32(ranges)
+    out = torch.empty((self.ns, self.cout), dtype=torch.float32, device=basis.device)
+    _lib.check(_lib.lib().tfgpc_mcconv_forward(
+        _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
+        c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),
+        ptr(neighbors), ptr(ranges), ptr(weights), ptr(out), ptr(self.ws), c_sz(self.nbytes)))
+    self._x_valid = self.backward_ws
+    return out
+
+  def backward(self, basis, features, neighbors, ranges, weights, out_grads, reuse_forward=True):
+    if not self.backward_ws:
+      raise RuntimeError("this ProjectionGemm was created without backward workspace")
+    basis, features, weights = _f32(basis), _f32(features), _f32(weights)
+    neighbors, ranges, out_grads = _i32(neighbors), _i32(ranges), _f32(out_grads)
+    dbasis = torch.empty_like(basis)
+    dfeat = torch.empty_like(features)
+    dw = torch.empty_like(weights)
+    _lib.check(_lib.lib().tfgpc_mcconv_backward(
+        _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
+        c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),
+        ptr(neighbors), ptr(ranges), ptr(weights), ptr(out_grads),
+        c_int(int(reuse_forward and self._x_valid)), ptr(dbasis), ptr(dfeat), ptr(dw),
+        ptr(self.ws), c_sz(self.nbytes)))
+    return dbasis, dfeat, dw
+
+  def check_status(self):
+    """Blocks on the stream; raises TfgpcError(4) if a GEMM wait timed out."""
+    status = c_int(0)
+    _lib.check(_lib.lib().tfgpc_mcconv_status(_stream(), ptr(self.ws), ctypes.byref(status)))
+
+
+def dense_final_weights(wf, cin, hidden):
+  """MCConv stores its final weights per kernel MLP, [G, cin*hidden, cout/G]
+  (MCConv.py:123-135), and multiplies the projection's columns (c, g*hidden+h)
+  with row c*hidden+h of block g (MCConv.py:174-191).  This returns the same
+  linear map as one [cin*G*hidden, cout] matrix in the projection's own column
+  order c*K + k (zero where a column belongs to another MLP's outputs)."""
+  g, _, co = wf.shape
+  k = g * hidden
+  dense = torch.zeros((cin, k, g * co), dtype=wf.dtype, device=wf.device)
+  w4 = wf.reshape(g, cin, hidden, co)
+  for i in range(g):
+    dense[:, i * hidden:(i + 1) * hidden, i * co:(i + 1) * co] = w4[i]
+  return dense.reshape(cin * k, g * co)
+
+
+def blocks_of_dense_grad(dw_dense, num_mlps, cin, hidden):
+  """Inverse of dense_final_weights for gradients: [cin*K, cout] -> [G, cin*hidden, cout/G]."""
+  k = num_mlps * hidden
+  co = dw_dense.shape[1] // num_mlps
+  d3 = dw_dense.reshape(cin, k, num_mlps * co)
+  out = [d3[:, i * hidden:(i + 1) * hidden, i * co:(i + 1) * co].reshape(cin * hidden, co)
+         for i in range(num_mlps)]
+  return torch.stack(out, dim=0)

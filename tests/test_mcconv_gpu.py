@@ -1,0 +1,75 @@
+"""Tensor-core GEMM and fused MCConv parity (fp32 within rel 1e-4)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+from oracle import pylib_ref as pr
+from tensorflow_graphics_point_clouds_b200 import mcconv, pc, synthetic
+from test_ops_gpu import close, t, grid_pair, neigh_pair, random_cloud
+
+pytestmark = pytest.mark.gpu
+F32 = np.float32
+
+
+@pytest.mark.parametrize("at,bt", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 64, 192), (1000, 256, 2048),
+                                   (256, 2048, 256), (2048, 256, 5000 // 8 * 8), (64, 16, 128)])
+def test_matmul_f32_layouts(at, bt, m, n, k):
+  rng = np.random.default_rng(m + n + k)
+  a = rng.normal(size=(m, k)).astype(F32)
+  b = (rng.uniform(-1, 1, size=(k, n)) * 0.05).astype(F32)
+  ref = a.astype(np.float64) @ b.astype(np.float64)
+  a_dev = t(a.T.copy() if at else a)
+  b_dev = t(b.T.copy() if bt else b)
+  got = mcconv.matmul_f32(a_dev, b_dev, a_transposed=at, b_transposed=bt)
+  close(got.cpu().numpy(), ref, rel=1e-4)
+
+
+def mc_case(rng, c, k, cout, n_pts=3000, n_smp=700, radius=0.25, b=3):
+  pts, bid = random_cloud(rng, b, n_pts, 3)
+  smp, sbid = random_cloud(rng, b, n_smp, 3)
+  g_ref, g = grid_pair(pts, bid, b, radius)
+  nb_ref, nb = neigh_pair(g_ref, g, radius, smp, sbid)
+  m = len(nb_ref.neighbors)
+  basis = rng.normal(size=(m, k)).astype(F32)
+  feat = rng.normal(size=(n_pts, c)).astype(F32)
+  w = synthetic.glorot_uniform(rng, c * k, cout, (1, c * k, cout))
+  return nb_ref, nb, basis, feat, w
+
+
+@pytest.mark.parametrize("c,k,cout", [(8, 16, 16), (128, 16, 256), (32, 8, 64), (64, 32, 128),
+                                      (3, 16, 32), (16, 64, 40)])
+def test_mcconv_forward_backward(c, k, cout):
+  rng = np.random.default_rng(c * 1000 + k + cout)
+  nb_ref, nb, basis, feat, w = mc_case(rng, c, k, cout)
+  ref_out, ref_x = pr.mcconv_forward(feat, basis, nb_ref, w)
+  ns = len(nb_ref.ranges)
+  op = mcconv.ProjectionGemm(k, c, cout, ns, "cuda", backward=True)
+  out = op.forward(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges, t(w[0]))
+  op.check_status()
+  close(out.cpu().numpy(), ref_out)
+  d_out = rng.normal(size=ref_out.shape).astype(F32)
+  ref_dw, ref_db, ref_df, _ = pr.mcconv_backward(feat, basis, nb_ref, w, ref_x, d_out)
+  for reuse in (True, False):
+    db, df, dw = op.backward(t(basis), t(feat), nb._original_neigh_ids,
+                             nb._samples_neigh_ranges, t(w[0]), t(d_out), reuse_forward=reuse)
+    op.check_status()
+    close(dw.cpu().numpy(), ref_dw[0])
+    close(db.cpu().numpy(), ref_db)
+    close(df.cpu().numpy(), ref_df)
+
+
+def test_dense_final_weights_matches_reference_layout():
+  rng = np.random.default_rng(5)
+  cin, g, h, co = 8, 4, 8, 16
+  nb_ref, nb, basis, feat, _ = mc_case(rng, cin, g * h, g * co)
+  wf = rng.normal(size=(g, cin * h, co)).astype(F32) * 0.1
+  ref_out, _ = pr.mcconv_forward(feat, basis, nb_ref, wf)
+  dense = mcconv.dense_final_weights(t(wf), cin, h)
+  op = mcconv.ProjectionGemm(g * h, cin, g * co, len(nb_ref.ranges), "cuda", backward=False)
+  out = op.forward(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges, dense)
+  op.check_status()
+  close(out.cpu().numpy(), ref_out)
+  back = mcconv.blocks_of_dense_grad(dense, g, cin, h)
+  assert torch.equal(back, t(wf))
