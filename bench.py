@@ -1,0 +1,392 @@
+"""Benchmark of the MCConv hot path: one Monte-Carlo convolution layer, forward
+and backward, from raw points (grid build, neighbor search, density estimate,
+kernel basis, basis projection + weight GEMM, and all gradients).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N ...            # CPU port of the reference path
+
+Workload (synthetic, seeded): 32 clouds x 16384 points uniform in [0,1)^3 per
+GPU, radius 0.079 (about 32 neighbors per point), C_in = 128, one kernel MLP
+with 16 hidden units (K = 16), C_out = 256, fp32.  With N GPUs every rank works
+on its own 32 clouds (weak scaling) and the weight gradients are all-reduced.
+Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+F32 = np.float32
+METRIC = "mcconv_fwd_bwd_points_per_s"
+UNIT = "points/s"
+
+
+def parse_args():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=10)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--clouds", type=int, default=32)
+  ap.add_argument("--points", type=int, default=16384)
+  ap.add_argument("--radius", type=float, default=0.079)
+  ap.add_argument("--cin", type=int, default=128)
+  ap.add_argument("--cout", type=int, default=256)
+  ap.add_argument("--hidden", type=int, default=16)
+  ap.add_argument("--cpu-sample-clouds", type=int, default=1)
+  ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--no-e2e", action="store_true")
+  return ap.parse_args()
+
+
+def workload_config(args, world):
+  return {
+      "workload": "MCConv layer fwd+bwd from raw points, %d clouds x %d points per GPU, "
+                  "uniform in [0,1)^3, radius %.3f (~32 neighbors/point), Cin=%d, K=%d, Cout=%d"
+                  % (args.clouds, args.points, args.radius, args.cin, args.hidden, args.cout),
+      "clouds_per_gpu": args.clouds, "points_per_cloud": args.points, "radius": args.radius,
+      "cin": args.cin, "k": args.hidden, "cout": args.cout, "bandwidth": 0.2,
+      "global_points": args.clouds * args.points * world,
+      "parallelism": "clouds sharded over %d GPU(s); weight gradients all-reduced" % world,
+      "l2": "inputs and intermediates are far larger than L2 (features 268 MB, projection "
+            "4.3 GB per step), so no explicit flush between iterations",
+  }
+
+
+def make_inputs(args, rank):
+  """Seeded host inputs of one rank (seed 2 is the single-GPU workload)."""
+  from tensorflow_graphics_point_clouds_b200 import synthetic
+  pts, bid = synthetic.uniform_clouds(args.clouds, args.points, seed=2 + 1000 * rank)
+  rng = np.random.default_rng(12345 + rank)
+  n = pts.shape[0]
+  feat = rng.standard_normal((n, args.cin), dtype=F32)
+  d_out = rng.standard_normal((n, args.cout), dtype=F32)
+  w1, b1, wf = synthetic.mcconv_weights(7, 3, args.cin, args.cout, 1, args.hidden)
+  return pts, bid, feat, d_out, w1, b1, wf
+
+
+# ------------------------------------------------------------------ peaks ----
+
+def measured_peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      p = json.load(f)
+    return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+            "source": "measured"}
+  return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) taken
+# from the ncu captures summarised under profiles/, scaled to this workload by
+# the units processed; None where no capture exists yet.
+NCU_TRAFFIC_BYTES = {}
+
+
+def kernel_model(name, sizes):
+  """Algorithmic work of one launch of a library kernel on this workload:
+  (bound, amount) with amount in bytes (hbm) or flops (tensor)."""
+  n, m = sizes["n"], sizes["m"]
+  c, k, co = sizes["cin"], sizes["k"], sizes["cout"]
+  ck = c * k
+  if name == "basis_proj_split":
+    return "hbm", m * (4 * k + 8) + n * 4 * c + n * 4 + n * ck * 4
+  if name == "basis_proj_grads":
+    return "hbm", n * ck * 4 + m * (4 * k + 8) + n * 4 * c + n * 4 + m * 4 * k + n * 4 * c
+  if name == "gemm_bf16x3_k_mn":      # out = X W
+    return "tensor", 2.0 * n * ck * co
+  if name == "gemm_bf16x3_k_k":       # dX = dOut W^T (its 4-byte output dominates)
+    return "hbm", n * co * 4 + ck * co * 4 + n * ck * 4
+  if name == "gemm_bf16x3_mn_mn":     # dW = X^T dOut
+    return "tensor", 2.0 * n * ck * co
+  if name == "find_neighbors_fill":
+    return "hbm", n * 36 + m * 8
+  if name == "find_neighbors_count":
+    return "hbm", n * 36
+  if name == "compute_pdf":
+    return "hbm", n * 20 + m * 8
+  if name == "split_bf16":
+    return "hbm", None
+  return "hbm", None
+
+
+# ----------------------------------------------------------------- clocks ----
+
+class ClockSampler:
+  """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+  FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+            "clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, index):
+    self.index = index
+    self.proc = None
+    self.lines = []
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(
+          ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+           "--format=csv,noheader,nounits", "-lms", "100"],
+          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+      self.thread = threading.Thread(target=self._read, daemon=True)
+      self.thread.start()
+    except OSError:
+      self.proc = None
+
+  def _read(self):
+    for line in self.proc.stdout:
+      self.lines.append(line.strip())
+
+  def stop(self):
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    sm, mx, reasons = [], None, set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in self.lines:
+      parts = [p.strip() for p in line.split(",")]
+      if len(parts) < 6:
+        continue
+      try:
+        sm.append(float(parts[0])); mx = float(parts[1])
+      except ValueError:
+        continue
+      for nm, val in zip(names, parts[2:6]):
+        if val.lower().startswith("active"):
+          reasons.add(nm)
+    return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+            "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------ CPU baseline ----
+
+def cpu_port_step(args, pts, bid, feat, d_out, w1, b1, wf, clouds):
+  """One forward+backward of the layer on `clouds` clouds through the CPU
+  oracle (C + NumPy restatement of the reference path).  Returns seconds."""
+  import oracle as orc
+  from oracle import pylib_ref as pr
+  n = clouds * args.points
+  pts, bid, feat, d_out = pts[:n], bid[:n], feat[:n], d_out[:n]
+  t0 = time.perf_counter()
+  grid = pr.Grid(pts, bid, clouds, args.radius)
+  neigh = pr.Neighborhood(grid, args.radius, pts, bid)
+  pdf = neigh.get_pdf(bandwidth=0.2, mode=0)
+  basis, diff, hid = pr.mcconv_basis(pts, pts, neigh, pdf, w1, b1, args.radius)
+  out, x = pr.mcconv_forward(feat, basis, neigh, wf)
+  d_wf, d_basis, d_feat, _ = pr.mcconv_backward(feat, basis, neigh, wf, x, d_out)
+  dpre = d_basis / pdf.reshape(-1, 1) * np.where(hid > 0, 1.0, 0.2)
+  _ = diff.T @ dpre
+  return time.perf_counter() - t0
+
+
+def cpu_baseline(args, inputs, reps=1):
+  import oracle as orc
+  clouds = max(1, min(args.cpu_sample_clouds, args.clouds))
+  best = min(cpu_port_step(args, *inputs, clouds) for _ in range(reps))
+  return {"value": clouds * args.points / best, "unit": UNIT, "cores": orc.num_threads(),
+          "kind": "port",
+          "sample": "%d of the %d clouds (%d points), one forward+backward through the C/NumPy "
+                    "oracle with OpenMP and BLAS on all host threads, %.2f s"
+                    % (clouds, args.clouds, clouds * args.points, best)}
+
+
+def run_reference(args, rank, world):
+  """The reference publishes no CPU implementation of its custom ops (they are
+  GPU-only TensorFlow kernels and TensorFlow is not installed), so this arm
+  times the CPU port of the same path on all host threads."""
+  if rank != 0:
+    return
+  import oracle as orc
+  orc.build()
+  inputs = make_inputs(args, 0)
+  clouds = max(1, min(args.cpu_sample_clouds, args.clouds))
+  for _ in range(min(args.warmup, 1)):
+    cpu_port_step(args, *inputs, clouds)
+  times = [cpu_port_step(args, *inputs, clouds) for _ in range(max(1, min(args.steps, 3)))]
+  t = statistics.mean(times)
+  value = clouds * args.points / t
+  line = {
+      "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+      "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t,
+      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+      "data": "synthetic", "config": workload_config(args, world),
+      "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+                       "sample": "each step is %d of the %d clouds (%d points)"
+                                 % (clouds, args.clouds, clouds * args.points)},
+      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+      "gpu_launches": 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- our arm ----
+
+def run_ours(args, rank, local_rank, world):
+  import torch
+  import torch.distributed as dist
+  from tensorflow_graphics_point_clouds_b200 import _lib, build, mcconv, pc
+
+  if not torch.cuda.is_available():
+    raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+  build.build()
+  torch.cuda.set_device(local_rank)
+  dev = torch.device("cuda", local_rank)
+  if world > 1:
+    dist.init_process_group("nccl", device_id=dev)
+
+  inputs = make_inputs(args, rank)
+  pts, bid, feat, d_out, w1, b1, wf = inputs
+  n = pts.shape[0]
+  host = {k: torch.from_numpy(v).pin_memory() for k, v in
+          dict(pts=pts, bid=bid, feat=feat, d_out=d_out).items()}
+  dev_in = {k: v.to(dev) for k, v in host.items()}
+  layer = mcconv.MCConv(torch.from_numpy(w1).to(dev), torch.from_numpy(b1).to(dev),
+                        torch.from_numpy(wf).to(dev), args.cin)
+  sizes = {"n": n, "m": 0, "cin": args.cin, "k": args.hidden, "cout": args.cout}
+
+  def step(x):
+    cloud = pc.PointCloud(x["pts"], x["bid"], args.clouds)
+    out = layer.forward(x["feat"], cloud, cloud, args.radius)
+    sizes["m"] = int(layer._saved[0]._neighbors.shape[0])
+    dfeat, dw1, db1, dwf = layer.backward(x["d_out"])
+    if world > 1:
+      flat = torch.cat([dwf.reshape(-1), dw1.reshape(-1), db1.reshape(-1)])
+      dist.all_reduce(flat)
+    return out, dfeat, dwf, dw1, db1
+
+  def barrier():
+    torch.cuda.synchronize()
+    if world > 1:
+      dist.barrier()
+      torch.cuda.synchronize()
+
+  for _ in range(max(args.warmup, 3)):
+    step(dev_in)
+  layer._op.check_status()
+
+  # ---- device-resident timing
+  sampler = ClockSampler(local_rank)
+  barrier()
+  sampler.start()
+  _lib.profile_enable(True)
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    step(dev_in)
+  e1.record()
+  barrier()
+  records = _lib.profile_collect()
+  _lib.profile_enable(False)
+  clocks = sampler.stop()
+  layer._op.check_status()
+  ms = e0.elapsed_time(e1)
+  t = torch.tensor([ms], device=dev)
+  if world > 1:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  ms_per_step = float(t.item()) / args.steps
+
+  # ---- end to end: host buffers in, host buffers out, every step
+  e2e = None
+  if not args.no_e2e:
+    out_host = None
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = 0
+
+    def e2e_step():
+      nonlocal out_host, d2h
+      x = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+      res = step(x)
+      if out_host is None:
+        out_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        d2h = sum(r.numel() * r.element_size() for r in res)
+      for h, r in zip(out_host, res):
+        h.copy_(r, non_blocking=True)
+
+    for _ in range(2):
+      e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+      e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    e2e = {"value": n * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+  if rank == 0:
+    peaks = measured_peaks()
+    agg = {}
+    for name, kms in records:
+      a = agg.setdefault(name, [0, 0.0])
+      a[0] += 1; a[1] += kms
+    total_kernel_ms = sum(v[1] for v in agg.values())
+    kernels = {k: {"launches_per_step": v[0] / args.steps, "ms_per_step": v[1] / args.steps}
+               for k, v in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+    top = max(agg.items(), key=lambda kv: kv[1][1])[0]
+    bound, amount = kernel_model(top, sizes)
+    avg_ms = agg[top][1] / agg[top][0]
+    if bound == "hbm":
+      achieved = amount / (avg_ms * 1e-3) / 1e9
+      peak, runit = peaks["hbm_gbs"], "GB/s"
+    else:
+      achieved = amount / (avg_ms * 1e-3) / 1e12
+      peak, runit = peaks["bf16_tflops"], "TFLOP/s"
+    roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(top),
+                "avg_launch_ms": avg_ms, "peak_source": peaks["source"],
+                "note": "tensor-bound kernels issue 3 bf16 passes per algorithmic flop"
+                        if bound == "tensor" else "algorithmic bytes / launch time"}
+    line = {
+        "metric": METRIC, "value": n * world / (ms_per_step * 1e-3), "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, world), "clocks": clocks, "e2e": e2e,
+        "gpu_launches": int(sum(v[0] for v in agg.values())),
+        "roofline": roofline,
+        "kernels": kernels,
+        "kernel_ms_per_step": total_kernel_ms / args.steps,
+        "neighbor_pairs": sizes["m"],
+        "neighbor_pairs_per_s": sizes["m"] * world / (ms_per_step * 1e-3),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+      import oracle as orc
+      orc.build()
+      line["cpu_baseline"] = cpu_baseline(args, inputs)
+    print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def main():
+  args = parse_args()
+  rank = int(os.environ.get("RANK", "0"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  if args.impl == "reference":
+    run_reference(args, rank, world)
+  else:
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+  main()

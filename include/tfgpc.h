@@ -232,6 +232,17 @@ int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K,
                      const float* a, int a_transposed, const float* b,
                      int b_transposed, float* c, void* ws, size_t ws_bytes);
 
+/* ---- per-launch timing ---------------------------------------------------
+ * No counterpart in the reference (its DEBUG_INFO timing blocks do not
+ * compile, store_neighbors_kernels.cu.cc:256-269).  While enabled on the
+ * calling thread, every kernel launch group of the library is bracketed by
+ * two CUDA events on its stream; _collect waits for them and returns up to
+ * max_records durations in milliseconds [host] with the matching names joined
+ * by newlines in names_out [host], then clears the records. */
+int tfgpc_profile_enable(int on);
+int tfgpc_profile_collect(char* names_out, size_t names_bytes, float* ms_out,
+                          int max_records, int* count_out);
+
 #ifdef __cplusplus
 }
 #endif

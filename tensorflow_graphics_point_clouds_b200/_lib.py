@@ -49,6 +49,8 @@ SYMBOLS = {
     "tfgpc_mcconv_status": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
+    "tfgpc_profile_enable": c_int,
+    "tfgpc_profile_collect": c_int,
 }
 
 
@@ -78,3 +80,19 @@ def ptr(t):
   if t is None:
     return c_vp(0)
   return c_vp(t.data_ptr())
+
+
+def profile_enable(on=True):
+  """Turns the library's per-launch CUDA-event timing on or off (this thread)."""
+  check(lib().tfgpc_profile_enable(c_int(int(on))))
+
+
+def profile_collect(max_records=65536):
+  """Returns [(name, milliseconds)] of every launch group since the last call."""
+  names = ctypes.create_string_buffer(64 * max_records)
+  ms = (ctypes.c_float * max_records)()
+  count = c_int(0)
+  check(lib().tfgpc_profile_collect(names, c_sz(len(names)), ms, c_int(max_records),
+                                    ctypes.byref(count)))
+  labels = names.value.decode().split("\n")[:count.value]
+  return [(labels[i], float(ms[i])) for i in range(count.value)]

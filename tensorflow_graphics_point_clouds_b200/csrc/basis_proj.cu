@@ -278,6 +278,7 @@ static int launch_basis_proj(cudaStream_t st, int C, int64_t ns, const float* ba
   const size_t smem = G == 32 ? (size_t)(kBpThreads / 32) * 32 * BpCfg<K>::kRow * sizeof(float) : 0;
   const int64_t samples_per_block = (int64_t)(kBpThreads / 32) * (32 / G);
   unsigned grid = min(blocks_for(ns, (int)samples_per_block), (unsigned)(sm_count() * 64));
+  ProfScope prof(st, OUT == 0 ? "basis_proj" : "basis_proj_split");
   if (vec) {
     auto kern = basis_proj_kernel<K, true, OUT>;
     if (smem > 48 * 1024)
@@ -316,6 +317,7 @@ static int launch_basis_proj_grads(cudaStream_t st, int C, int64_t ns, const flo
                    ((uintptr_t)dfeat % 16 == 0);
   const int64_t samples_per_block = (int64_t)(kBpThreads / 32) * (32 / G);
   unsigned grid = min(blocks_for(ns, (int)samples_per_block), (unsigned)(sm_count() * 64));
+  ProfScope prof(st, "basis_proj_grads");
   if (vec)
     basis_proj_grads_kernel<K, true><<<grid, kBpThreads, 0, st>>>(C, ns, G, basis, feat, neigh,
                                                                   ranges, in_grads, dbasis, dfeat);

@@ -43,6 +43,17 @@ void clear_error();
 
 inline bool valid_dims(int D) { return D >= TFGPC_MIN_DIMS && D <= TFGPC_MAX_DIMS; }
 
+// Optional per-launch timing (tfgpc_profile_enable): when on, a ProfScope
+// brackets the launches made inside its lifetime with two CUDA events on the
+// launching stream; tfgpc_profile_collect returns name and duration of every
+// scope.  When off it costs one thread-local load.
+struct ProfScope {
+  ProfScope(cudaStream_t st, const char* name);
+  ~ProfScope();
+  int slot;
+  cudaStream_t st;
+};
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

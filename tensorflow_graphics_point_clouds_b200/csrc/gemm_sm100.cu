@@ -406,6 +406,8 @@ int launch(cudaStream_t st, const CUtensorMap* maps, float* c, int64_t ldc, int6
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  ProfScope prof(st, A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
+                          : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], c, ldc,
                                            split_stride, M, N, bn, make_idesc(kBM, bn, A_MN, B_MN),
                                            sch, err_flag);
@@ -516,6 +518,7 @@ int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const Gemm
 int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16* hi,
                   __nv_bfloat16* mid) {
   if (n <= 0) return TFGPC_OK;
+  ProfScope prof(stream, "split_bf16");
   split_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, stream>>>(x, n, hi, mid);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
@@ -533,6 +536,7 @@ int split_transpose_to_bf16(cudaStream_t stream, const float* x, int64_t rows, i
 int reduce_splits(cudaStream_t stream, const float* partial, int splits, int64_t stride, int64_t n,
                   float* out) {
   if (n <= 0) return TFGPC_OK;
+  ProfScope prof(stream, "reduce_splits");
   reduce_splits_kernel<<<blocks_for(n, 256), 256, 0, stream>>>(partial, splits, stride, n, out);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;

@@ -103,6 +103,7 @@ extern "C" int tfgpc_compute_keys(void* stream, int D, int64_t n, const float* p
                 "ComputeKeys got a null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(n, kKeyThreads), (unsigned)(sm_count() * 16));
+  ProfScope prof(st, "compute_keys");
   TFGPC_DIM_SWITCH(D, compute_keys_kernel<kD><<<grid, kKeyThreads, 0, st>>>(
       n, points, batch_ids, batch_size, scaled_aabb_min, num_cells, inv_cell_sizes, keys_out));
   TFGPC_LAUNCH_CHECK();
@@ -144,14 +145,21 @@ extern "C" int tfgpc_sort_keys_desc(void* stream, int D, int64_t n, int key_bits
   int32_t* iota = (int32_t*)ws;
   void* cub_ws = (char*)ws + align_up((size_t)n * sizeof(int32_t), 256);
   size_t cub_bytes = cub_sort_temp_bytes(n);
-  iota_kernel<<<blocks_for(n, 256), 256, 0, st>>>(iota, n);
+  {
+    ProfScope prof(st, "sort_iota");
+    iota_kernel<<<blocks_for(n, 256), 256, 0, st>>>(iota, n);
+  }
   TFGPC_LAUNCH_CHECK();
   int end_bit = key_bits == 0 ? 64 : key_bits;
   // LSD radix sort: stable, so equal keys keep ascending original index.
-  TFGPC_CUDA(cub::DeviceRadixSort::SortPairsDescending(cub_ws, cub_bytes, keys, sorted_keys_out,
-                                                       (const int32_t*)iota, perm_out, n, 0,
-                                                       end_bit, st));
+  {
+    ProfScope prof(st, "sort_radix");
+    TFGPC_CUDA(cub::DeviceRadixSort::SortPairsDescending(cub_ws, cub_bytes, keys, sorted_keys_out,
+                                                         (const int32_t*)iota, perm_out, n, 0,
+                                                         end_bit, st));
+  }
   if (do_gather) {
+    ProfScope prof(st, "sort_gather");
     TFGPC_DIM_SWITCH(D, gather_sorted_kernel<kD><<<blocks_for(n * kD, 256), 256, 0, st>>>(
         n, perm_out, points, batch_ids, sorted_points_out, sorted_batch_ids_out));
     TFGPC_LAUNCH_CHECK();
@@ -173,6 +181,7 @@ extern "C" int tfgpc_build_grid_ds(void* stream, int D, int64_t n, const int64_t
   TFGPC_CUDA(cudaMemsetAsync(ds_out, 0, sizeof(int32_t) * 2 * (size_t)n_ds, st));
   if (n == 0) return TFGPC_OK;
   TFGPC_REQUIRE(sorted_keys, "BuildGridDs got a null pointer");
+  ProfScope prof(st, "build_grid_ds");
   TFGPC_DIM_SWITCH(D, build_grid_ds_kernel<kD><<<blocks_for(n, 256), 256, 0, st>>>(
       n, sorted_keys, num_cells, n_ds, (int2*)ds_out));
   TFGPC_LAUNCH_CHECK();

@@ -186,10 +186,13 @@ extern "C" int tfgpc_find_neighbors_count(
   int64_t* block_sums = (int64_t*)ws;
   int64_t* total_dev = block_sums + scan_block_sums_elems(ns);
   unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  {
+  ProfScope prof(st, "find_neighbors_count");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, false><<<grid, kFnThreads, 0, st>>>(
       ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
       num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, ranges_out, nullptr,
       nullptr));
+  }
   TFGPC_LAUNCH_CHECK();
   rc = inclusive_scan_i32(st, ranges_out, ranges_out, ns, block_sums, total_dev);
   if (rc) return rc;
@@ -218,6 +221,7 @@ extern "C" int tfgpc_find_neighbors_fill(
                 "FindNeighbors got a null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  ProfScope prof(st, "find_neighbors_fill");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, true><<<grid, kFnThreads, 0, st>>>(
       ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
       num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,

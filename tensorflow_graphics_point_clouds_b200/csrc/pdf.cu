@@ -128,6 +128,7 @@ extern "C" int tfgpc_compute_pdf(void* stream, int D, int mode, int64_t n, const
                 "ComputePdf got a null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(n, kPdfThreads / 32), (unsigned)(sm_count() * 32));
+  ProfScope prof(st, "compute_pdf");
   TFGPC_DIM_SWITCH(D, compute_pdf_kernel<kD><<<grid, kPdfThreads, 0, st>>>(
       mode, n, points, (const int2*)neighbors, ranges, inv_bandwidth, inv_radii, pdf_out));
   TFGPC_LAUNCH_CHECK();
@@ -147,6 +148,7 @@ extern "C" int tfgpc_compute_pdf_pt_grads(void* stream, int D, int mode, int64_t
   cudaStream_t st = (cudaStream_t)stream;
   TFGPC_CUDA(cudaMemsetAsync(pt_grads_out, 0, sizeof(float) * (size_t)n * D, st));
   unsigned grid = min(blocks_for(n, kPdfThreads / 32), (unsigned)(sm_count() * 32));
+  ProfScope prof(st, "compute_pdf_grads");
   TFGPC_DIM_SWITCH(D, compute_pdf_grads_kernel<kD><<<grid, kPdfThreads, 0, st>>>(
       mode, n, points, (const int2*)neighbors, ranges, inv_bandwidth, inv_radii, pdf_grads,
       pt_grads_out));

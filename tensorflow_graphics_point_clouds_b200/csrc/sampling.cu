@@ -182,16 +182,23 @@ extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, co
                 sampling_ws_bytes(n));
   cudaStream_t st = (cudaStream_t)stream;
   SamplingWs w = carve(ws, n);
-  flag_runs_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, point_keys, w.flags);
+  {
+    ProfScope prof(st, "sampling_flag_runs");
+    flag_runs_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, point_keys, w.flags);
+  }
   TFGPC_LAUNCH_CHECK();
   rc = inclusive_scan_i32(st, w.flags, w.run_idx, n, w.block_sums, w.totals);
   if (rc) return rc;
-  compact_runs_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, w.flags, w.run_idx, w.starts);
+  {
+    ProfScope prof(st, "sampling_compact_runs");
+    compact_runs_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, w.flags, w.run_idx, w.starts);
+  }
   TFGPC_LAUNCH_CHECK();
   if (mode == 0) {
     TFGPC_CUDA(cudaMemsetAsync(w.used, 0, sizeof(int32_t) * (size_t)n, st));
     unsigned grid = min(blocks_for(n, kSmpThreads / 32), (unsigned)(sm_count() * 32));
     for (int pass = 0; pass < (1 << D); ++pass) {
+      ProfScope prof(st, "sampling_poisson_pass");
       TFGPC_DIM_SWITCH(D, poisson_pass_kernel<kD><<<grid, kSmpThreads, 0, st>>>(
           pass, n, w.totals, w.starts, point_keys, num_cells, (const int2*)neighbors, ranges,
           w.used));
@@ -224,6 +231,7 @@ extern "C" int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n, co
                 sampling_ws_bytes(n));
   cudaStream_t st = (cudaStream_t)stream;
   SamplingWs w = carve(ws, n);
+  ProfScope prof(st, mode == 0 ? "sampling_store_poisson" : "sampling_cell_average");
   if (mode == 0) {
     TFGPC_DIM_SWITCH(D, store_poisson_kernel<kD><<<blocks_for(n, 256), 256, 0, st>>>(
         n, w.used, w.used_scan, points, batch_ids, sample_pts_out, sample_batch_ids_out,

@@ -129,6 +129,7 @@ int inclusive_scan_i32(cudaStream_t stream, const int32_t* in, int32_t* out, int
     return TFGPC_OK;
   }
   int64_t tiles = (n + kScanTile - 1) / kScanTile;
+  ProfScope prof(stream, "scan_i32");
   scan_reduce_kernel<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, n, block_sums);
   TFGPC_LAUNCH_CHECK();
   scan_tile_sums_kernel<<<1, 1024, 0, stream>>>(block_sums, tiles, total);

@@ -104,3 +104,71 @@ def blocks_of_dense_grad(dw_dense, num_mlps, cin, hidden):
   out = [d3[:, i * hidden:(i + 1) * hidden, i * co:(i + 1) * co].reshape(cin * hidden, co)
          for i in range(num_mlps)]
   return torch.stack(out, dim=0)
+
+
+def leaky_relu(x, alpha=0.2):
+  return torch.where(x > 0, x, x * alpha)
+
+
+class MCConv:
+  """Monte-Carlo convolution layer (MCConv.py:36-278) with explicit backward.
+
+  Weights use the reference's layouts: w1 [G, D, H], b1 [G, 1, H] (one hidden
+  layer kernel MLP), wf [G, C_in*H, C_out/G]."""
+
+  def __init__(self, w1, b1, wf, num_features_in):
+    self.w1, self.b1, self.wf = _f32(w1), _f32(b1), _f32(wf)
+    self.num_mlps, self.dims, self.hidden = self.w1.shape
+    self.cin = int(num_features_in)
+    self.cout = self.wf.shape[2] * self.num_mlps
+    self.k = self.num_mlps * self.hidden
+    self._op = None
+    self._saved = None
+
+  def _dense_weights(self):
+    if self.num_mlps == 1:
+      return self.wf[0]
+    return dense_final_weights(self.wf, self.cin, self.hidden)
+
+  def build_neighborhood(self, point_cloud_in, point_cloud_out, radius):
+    """MCConv.py:254-261: grid and neighborhood of the input cloud around the
+    output points."""
+    from . import pc
+    grid = pc.Grid(point_cloud_in, radius)
+    same = point_cloud_out is point_cloud_in
+    neigh = pc.Neighborhood(grid, radius, point_cloud_out)
+    return neigh
+
+  def forward(self, features, point_cloud_in, point_cloud_out, radius, neighborhood=None,
+              bandwidth=0.2, keep_for_backward=True):
+    neigh = neighborhood or self.build_neighborhood(point_cloud_in, point_cloud_out, radius)
+    pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
+    ids = neigh._original_neigh_ids.to(torch.int64)
+    # MCConv.py:264-269
+    diff = (point_cloud_in._points[ids[:, 0]] - point_cloud_out._points[ids[:, 1]]) / float(radius)
+    # MCConv.py:163-171: [M, D] x [G, D, H] -> [M, G*H], nonlinearity, / pdf
+    w1 = self.w1.permute(1, 0, 2).reshape(self.dims, self.k)
+    pre = diff @ w1 + self.b1.reshape(1, self.k)
+    basis = leaky_relu(pre) / pdf.unsqueeze(1)
+    ns = point_cloud_out._points.shape[0]
+    if (self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward):
+      self._op = ProjectionGemm(self.k, self.cin, self.cout, ns, features.device,
+                                backward=keep_for_backward)
+    wd = self._dense_weights()
+    out = self._op.forward(basis, features, neigh._original_neigh_ids,
+                           neigh._samples_neigh_ranges, wd)
+    if keep_for_backward:
+      self._saved = (neigh, diff, pre, pdf, basis, _f32(features), wd)
+    return out
+
+  def backward(self, out_grads):
+    """Gradients of the last forward call: (d_features, d_w1, d_b1, d_wf)."""
+    neigh, diff, pre, pdf, basis, features, wd = self._saved
+    dbasis, dfeat, dwd = self._op.backward(basis, features, neigh._original_neigh_ids,
+                                           neigh._samples_neigh_ranges, wd, out_grads)
+    dpre = dbasis / pdf.unsqueeze(1) * torch.where(pre > 0, 1.0, 0.2)
+    dw1 = (diff.t() @ dpre).reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2)
+    db1 = dpre.sum(dim=0).reshape(self.num_mlps, 1, self.hidden)
+    dwf = (dwd.unsqueeze(0) if self.num_mlps == 1
+           else blocks_of_dense_grad(dwd, self.num_mlps, self.cin, self.hidden))
+    return dfeat, dw1.contiguous(), db1, dwf
