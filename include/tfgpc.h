@@ -221,6 +221,30 @@ int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64_t ns,
                           float* dweights_out, void* ws, size_t ws_bytes);
 int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out);
 
+/* ---- MCConv kernel basis --------------------------------------------------
+ * Replaces the TensorFlow op chain of pylib/pc/layers/MCConv.py:264-269 and
+ * :163-171 for a kernel MLP with one hidden layer: per neighbor pair
+ *   diff = (points_in[nbr.x] - points_out[nbr.y]) * inv_radius
+ *   basis[m, k] = act(diff . w1[:, k] + b1[k]) / pdf[m]
+ * points_in [n_in,D], points_out [ns,D], neighbors [M,2] (point index into
+ * points_in, sample index into points_out), pdf [M] (density per pair), w1
+ * [D,K] row-major (column k = mlp * hidden + h of the reference's
+ * [num_mlps, D, hidden] weights), b1 [K].  activation 0 = leaky ReLU with slope
+ * alpha (0.2 is tf.nn.leaky_relu's default, 0 gives ReLU), 1 = ELU.
+ * _grads: basis_grads [M,K] -> dw1_out [D,K], db1_out [K] (overwritten). */
+int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M,
+                       const float* points_in, const float* points_out,
+                       const int32_t* neighbors, const float* pdf,
+                       const float* w1, const float* b1, float inv_radius,
+                       int activation, float alpha, float* basis_out);
+int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
+                             const float* points_in, const float* points_out,
+                             const int32_t* neighbors, const float* pdf,
+                             const float* w1, const float* b1, float inv_radius,
+                             int activation, float alpha,
+                             const float* basis_grads, float* dw1_out,
+                             float* db1_out);
+
 /* ---- fp32 matrix product on the tensor cores -----------------------------
  * c[M,N] = op(a) * op(b) in fp32 accuracy (three bf16 passes), the tf.matmul
  * of MCConv.py:187-191 as a stand-alone call.  a is [M,K] row-major, or

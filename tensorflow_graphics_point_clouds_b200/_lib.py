@@ -47,6 +47,8 @@ SYMBOLS = {
     "tfgpc_mcconv_forward": c_int,
     "tfgpc_mcconv_backward": c_int,
     "tfgpc_mcconv_status": c_int,
+    "tfgpc_kernel_basis": c_int,
+    "tfgpc_kernel_basis_grads": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
     "tfgpc_profile_enable": c_int,

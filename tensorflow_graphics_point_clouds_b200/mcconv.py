@@ -106,15 +106,43 @@ def blocks_of_dense_grad(dw_dense, num_mlps, cin, hidden):
   return torch.stack(out, dim=0)
 
 
-def leaky_relu(x, alpha=0.2):
-  return torch.where(x > 0, x, x * alpha)
+def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
+                 alpha=0.2):
+  """basis[m, k] = act(diff_m . w1[:, k] + b1[k]) / pdf[m] (tfgpc_kernel_basis).
+  w1 [D, K], b1 [K]; neighbors hold (index into points_in, index into points_out)."""
+  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
+  d, k = w1.shape
+  m = neighbors.shape[0]
+  basis = torch.empty((m, k), dtype=torch.float32, device=points_in.device)
+  _lib.check(_lib.lib().tfgpc_kernel_basis(
+      _stream(), c_int(d), c_int(k), c_i64(m), ptr(points_in), ptr(points_out), ptr(neighbors),
+      ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)), c_int(activation),
+      ctypes.c_float(alpha), ptr(basis)))
+  return basis
+
+
+def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, basis_grads,
+                       activation=0, alpha=0.2):
+  """Gradients of kernel_basis with respect to w1 and b1 (tfgpc_kernel_basis_grads)."""
+  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
+  basis_grads = _f32(basis_grads)
+  d, k = w1.shape
+  dw1 = torch.empty_like(w1)
+  db1 = torch.empty_like(b1)
+  _lib.check(_lib.lib().tfgpc_kernel_basis_grads(
+      _stream(), c_int(d), c_int(k), c_i64(neighbors.shape[0]), ptr(points_in), ptr(points_out),
+      ptr(neighbors), ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)),
+      c_int(activation), ctypes.c_float(alpha), ptr(basis_grads), ptr(dw1), ptr(db1)))
+  return dw1, db1
 
 
 class MCConv:
   """Monte-Carlo convolution layer (MCConv.py:36-278) with explicit backward.
 
   Weights use the reference's layouts: w1 [G, D, H], b1 [G, 1, H] (one hidden
-  layer kernel MLP), wf [G, C_in*H, C_out/G]."""
+  layer kernel MLP, leaky ReLU), wf [G, C_in*H, C_out/G]."""
 
   def __init__(self, w1, b1, wf, num_features_in):
     self.w1, self.b1, self.wf = _f32(w1), _f32(b1), _f32(wf)
@@ -130,26 +158,25 @@ class MCConv:
       return self.wf[0]
     return dense_final_weights(self.wf, self.cin, self.hidden)
 
+  def _flat_kernel_weights(self):
+    # [G, D, H] -> [D, G*H]: column k = g*H + h (MCConv.py:169-171)
+    return (self.w1.permute(1, 0, 2).reshape(self.dims, self.k).contiguous(),
+            self.b1.reshape(self.k).contiguous())
+
   def build_neighborhood(self, point_cloud_in, point_cloud_out, radius):
-    """MCConv.py:254-261: grid and neighborhood of the input cloud around the
+    """MCConv.py:254-261: grid of the input cloud, neighborhood around the
     output points."""
     from . import pc
     grid = pc.Grid(point_cloud_in, radius)
-    same = point_cloud_out is point_cloud_in
-    neigh = pc.Neighborhood(grid, radius, point_cloud_out)
-    return neigh
+    return pc.Neighborhood(grid, radius, point_cloud_out)
 
   def forward(self, features, point_cloud_in, point_cloud_out, radius, neighborhood=None,
               bandwidth=0.2, keep_for_backward=True):
     neigh = neighborhood or self.build_neighborhood(point_cloud_in, point_cloud_out, radius)
     pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
-    ids = neigh._original_neigh_ids.to(torch.int64)
-    # MCConv.py:264-269
-    diff = (point_cloud_in._points[ids[:, 0]] - point_cloud_out._points[ids[:, 1]]) / float(radius)
-    # MCConv.py:163-171: [M, D] x [G, D, H] -> [M, G*H], nonlinearity, / pdf
-    w1 = self.w1.permute(1, 0, 2).reshape(self.dims, self.k)
-    pre = diff @ w1 + self.b1.reshape(1, self.k)
-    basis = leaky_relu(pre) / pdf.unsqueeze(1)
+    w1, b1 = self._flat_kernel_weights()
+    basis = kernel_basis(point_cloud_in._points, point_cloud_out._points,
+                         neigh._original_neigh_ids, pdf, w1, b1, radius)
     ns = point_cloud_out._points.shape[0]
     if (self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward):
       self._op = ProjectionGemm(self.k, self.cin, self.cout, ns, features.device,
@@ -158,17 +185,20 @@ class MCConv:
     out = self._op.forward(basis, features, neigh._original_neigh_ids,
                            neigh._samples_neigh_ranges, wd)
     if keep_for_backward:
-      self._saved = (neigh, diff, pre, pdf, basis, _f32(features), wd)
+      self._saved = (neigh, point_cloud_in, point_cloud_out, radius, pdf, basis,
+                     _f32(features), wd, w1, b1)
     return out
 
   def backward(self, out_grads):
-    """Gradients of the last forward call: (d_features, d_w1, d_b1, d_wf)."""
-    neigh, diff, pre, pdf, basis, features, wd = self._saved
+    """Gradients of the last forward call: (d_features, d_w1, d_b1, d_wf) in the
+    layouts of the weights."""
+    neigh, pc_in, pc_out, radius, pdf, basis, features, wd, w1, b1 = self._saved
     dbasis, dfeat, dwd = self._op.backward(basis, features, neigh._original_neigh_ids,
                                            neigh._samples_neigh_ranges, wd, out_grads)
-    dpre = dbasis / pdf.unsqueeze(1) * torch.where(pre > 0, 1.0, 0.2)
-    dw1 = (diff.t() @ dpre).reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2)
-    db1 = dpre.sum(dim=0).reshape(self.num_mlps, 1, self.hidden)
+    dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, neigh._original_neigh_ids, pdf,
+                                  w1, b1, radius, dbasis)
+    dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()
+    db1 = db1.reshape(self.num_mlps, 1, self.hidden)
     dwf = (dwd.unsqueeze(0) if self.num_mlps == 1
            else blocks_of_dense_grad(dwd, self.num_mlps, self.cin, self.hidden))
-    return dfeat, dw1.contiguous(), db1, dwf
+    return dfeat, dw1, db1, dwf

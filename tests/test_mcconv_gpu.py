@@ -73,3 +73,38 @@ def test_dense_final_weights_matches_reference_layout():
   close(out.cpu().numpy(), ref_out)
   back = mcconv.blocks_of_dense_grad(dense, g, cin, h)
   assert torch.equal(back, t(wf))
+
+
+@pytest.mark.parametrize("d,g,h", [(3, 1, 16), (3, 4, 8), (2, 1, 8), (4, 2, 32)])
+def test_mcconv_layer_matches_oracle(d, g, h):
+  """Whole layer from raw points (MCConv.py:196-278): output and all gradients."""
+  rng = np.random.default_rng(900 + d + g)
+  b, n_pts, cin, cout, radius = 3, 2500, 16, 32, 0.3
+  pts, bid = random_cloud(rng, b, n_pts, d)
+  feat = rng.normal(size=(n_pts, cin)).astype(F32)
+  w1 = rng.normal(size=(g, d, h)).astype(F32)
+  b1 = (rng.normal(size=(g, 1, h)) * 0.1).astype(F32)
+  wf = (rng.normal(size=(g, cin * h, cout // g)) * 0.05).astype(F32)
+  d_out = rng.normal(size=(n_pts, cout)).astype(F32)
+  # oracle
+  g_ref = pr.Grid(pts, bid, b, radius)
+  nb_ref = pr.Neighborhood(g_ref, radius, pts, bid)
+  pdf = nb_ref.get_pdf(bandwidth=0.2, mode=0)
+  basis, diff, hid = pr.mcconv_basis(pts, pts, nb_ref, pdf, w1, b1, radius)
+  ref_out, x = pr.mcconv_forward(feat, basis, nb_ref, wf)
+  ref_dwf, ref_db, ref_df, _ = pr.mcconv_backward(feat, basis, nb_ref, wf, x, d_out)
+  dpre = ref_db.astype(np.float64) / pdf.reshape(-1, 1) * np.where(hid > 0, 1.0, 0.2)
+  ref_dw1 = (diff.astype(np.float64).T @ dpre).reshape(d, g, h).transpose(1, 0, 2)
+  ref_db1 = dpre.sum(axis=0).reshape(g, 1, h)
+  # library
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  layer = mcconv.MCConv(t(w1), t(b1), t(wf), cin)
+  out = layer.forward(t(feat), cloud, cloud, radius)
+  dfeat, dw1, db1, dwf = layer.backward(t(d_out))
+  layer._op.check_status()
+  close(layer._saved[5].cpu().numpy(), basis)
+  close(out.cpu().numpy(), ref_out)
+  close(dfeat.cpu().numpy(), ref_df)
+  close(dwf.cpu().numpy(), ref_dwf)
+  close(dw1.cpu().numpy(), ref_dw1, rel=2e-4)
+  close(db1.cpu().numpy(), ref_db1, rel=2e-4)
