@@ -9,6 +9,7 @@
 // block per (sample, 8 channels), two __syncthreads per neighbor step,
 // basis_proj_kernels.cu.cc:30-127.)
 #include "basis_proj.cuh"
+#include "basis_proj_wide.cuh"
 
 namespace tfgpc {
 
@@ -279,6 +280,21 @@ static int launch_basis_proj(cudaStream_t st, int C, int64_t ns, const float* ba
   const int64_t samples_per_block = (int64_t)(kBpThreads / 32) * (32 / G);
   unsigned grid = min(blocks_for(ns, (int)samples_per_block), (unsigned)(sm_count() * 64));
   ProfScope prof(st, OUT == 0 ? "basis_proj" : "basis_proj_split");
+  if (G == 32 && C % kCpl == 0 && ((uintptr_t)feat % 16 == 0) && (C * 4) % (kCpl * 4) == 0) {
+    auto kern = basis_proj_wide_kernel<K, OUT>;
+    const size_t wsmem = (size_t)(kBpwThreads / 32) * 32 * BpCfg<K>::kRow * sizeof(float);
+    TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem));
+    TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared));
+    // exactly one resident wave: all warps then sweep the samples in lock step
+    // and the feature rows they gather stay within a few clouds, i.e. in L2
+    int per_sm = 1;
+    TFGPC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kBpwThreads, wsmem));
+    unsigned wgrid = min(blocks_for(ns, kBpwThreads / 32), (unsigned)(sm_count() * max(per_sm, 1)));
+    kern<<<wgrid, kBpwThreads, wsmem, st>>>(C, ns, basis, feat, neigh, ranges, out, hi, mid);
+    TFGPC_LAUNCH_CHECK();
+    return TFGPC_OK;
+  }
   if (vec) {
     auto kern = basis_proj_kernel<K, true, OUT>;
     if (smem > 48 * 1024)
@@ -318,6 +334,21 @@ static int launch_basis_proj_grads(cudaStream_t st, int C, int64_t ns, const flo
   const int64_t samples_per_block = (int64_t)(kBpThreads / 32) * (32 / G);
   unsigned grid = min(blocks_for(ns, (int)samples_per_block), (unsigned)(sm_count() * 64));
   ProfScope prof(st, "basis_proj_grads");
+  if (G == 32 && C % kCpl == 0 && ((uintptr_t)feat % 16 == 0) && ((uintptr_t)dfeat % 16 == 0) &&
+      ((uintptr_t)dbasis % 16 == 0)) {
+    auto kern = basis_proj_grads_wide_kernel<K>;
+    const size_t wsmem = (size_t)(kBpwThreads / 32) * 2 * 32 * K * sizeof(float);
+    TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem));
+    TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared));
+    int per_sm = 1;
+    TFGPC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kBpwThreads, wsmem));
+    unsigned wgrid = min(blocks_for(ns, kBpwThreads / 32), (unsigned)(sm_count() * max(per_sm, 1)));
+    kern<<<wgrid, kBpwThreads, wsmem, st>>>(C, ns, basis, feat, neigh, ranges, in_grads, dbasis,
+                                            dfeat);
+    TFGPC_LAUNCH_CHECK();
+    return TFGPC_OK;
+  }
   if (vec)
     basis_proj_grads_kernel<K, true><<<grid, kBpThreads, 0, st>>>(C, ns, G, basis, feat, neigh,
                                                                   ranges, in_grads, dbasis, dfeat);
