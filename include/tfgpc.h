@@ -126,6 +126,38 @@ int tfgpc_find_neighbors_fill(void* stream, int D, int64_t ns,
                               const int32_t* ranges, int64_t total,
                               int32_t* neigh_out);
 
+/* ---- FindNeighbors count pass with built-in scratch ------------------------
+ * No counterpart in the reference.  Same inputs, outputs and blocking
+ * behaviour as tfgpc_find_neighbors_count, but without the ws / ws_bytes
+ * pair: the scan's scratch is a fixed array inside the library image, and the
+ * call makes no cudaMalloc / cudaFree and uses no allocating routine.  It is
+ * meant for hosts that cannot get temporary device memory at the point where
+ * the neighbor count is needed -- e.g. a plugin whose framework owns all
+ * device memory and only lends buffers for declared outputs, or a service that
+ * has already committed its whole memory budget and must not trigger a device
+ * allocation (with its implicit synchronisation) on the request path.
+ * Limits: at most tfgpc_find_neighbors_static_max_samples() (2^24) samples per
+ * call, larger ns is rejected with TFGPC_EINVAL; the array (about 33 KB) stays
+ * resident on every GPU that loads the library until the process exits.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current; make that first call
+ * outside of any stream capture.  All calls on a device share the one array,
+ * which keeps the previous call's contents (nothing in it needs clearing: each
+ * call overwrites what it reads); two calls whose GPU work overlaps -- from
+ * different streams or threads -- race on it, so serialise them. */
+int64_t tfgpc_find_neighbors_static_max_samples(void);
+int tfgpc_find_neighbors_count_static(void* stream, int D, int64_t ns,
+                                      const float* samples,
+                                      const int32_t* samples_batch_ids,
+                                      int64_t n, const float* points,
+                                      const int64_t* point_keys,
+                                      const int32_t* ds, int64_t batch_size,
+                                      const int32_t* num_cells,
+                                      const float* scaled_aabb_min,
+                                      const float* inv_cell_sizes,
+                                      const float* inv_radii, int max_neighs,
+                                      int32_t* ranges_out, int64_t* total_out);
+
 /* ---- ComputePdf / ComputePdfWithPtGrads / ComputePdfPtGrads --------------
  * Replaces ComputePDFOp::Compute (compute_pdf/cc/ops/compute_pdf_ops.cpp:
  * 101-154) -> compute_pdf_gpu<D> (cc/kernels/compute_pdf_kernels.cu.cc:

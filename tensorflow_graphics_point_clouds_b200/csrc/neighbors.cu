@@ -11,6 +11,8 @@
 // step and compacting the hits with a ballot, which gives the canonical order
 // without atomics (the reference: atomicAdd per hit, count_neighbors_kernels.
 // cu.cc:84-87 and store_neighbors_kernels.cu.cc:160-166).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace tfgpc {
@@ -228,4 +230,74 @@ extern "C" int tfgpc_find_neighbors_fill(
       (int2*)neigh_out));
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
+}
+
+// ---- FindNeighbors count pass without caller scratch ---------------------------
+//
+// Scratch of tfgpc_find_neighbors_count_static: the tile sums of the device-wide
+// scan plus its 64-bit total, for up to kStaticMaxSamples samples.  The array
+// lives in the library image, so every GPU that loads the library keeps these
+// bytes resident until the process exits.
+namespace tfgpc {
+namespace {
+
+constexpr int64_t kStaticMaxSamples = int64_t(1) << 24;                   // 16,777,216 samples
+constexpr size_t kStaticScratchBytes = ((size_t(1) << 24) / 4096 + 2) * 8 + 256 + 256;  // ~33 KB
+
+static __device__ __align__(256) unsigned char g_fn_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device.  The array's name
+// is only a host-side handle in host code, so the address is looked up once
+// per device (with that device current) and cached.
+int static_scratch_ptr(void** out) {
+  int dev = -1;
+  TFGPC_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(TFGPC_EINVAL, "device ordinal %d outside the supported range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_fn_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(TFGPC_ECUDA, "cudaGetSymbolAddress(static scratch) failed: %s",
+                  cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return TFGPC_OK;
+}
+
+}  // namespace
+}  // namespace tfgpc
+
+extern "C" int64_t tfgpc_find_neighbors_static_max_samples(void) {
+  return tfgpc::kStaticMaxSamples;
+}
+
+extern "C" int tfgpc_find_neighbors_count_static(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
+    int64_t* total_out) {
+  if (ns > kStaticMaxSamples)
+    return fail(TFGPC_EINVAL, "find_neighbors_count_static handles at most %lld samples per call "
+                "(got %lld); use tfgpc_find_neighbors_count with a caller workspace for more",
+                (long long)kStaticMaxSamples, (long long)ns);
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  if (tfgpc_find_neighbors_workspace_bytes(ns) > kStaticScratchBytes)
+    return fail(TFGPC_ENOMEM, "static scratch of %zu bytes is too small for %lld samples",
+                kStaticScratchBytes, (long long)ns);
+  // Nothing in the scratch has to start at zero: the scan overwrites every tile
+  // sum and the total before it reads them, so stale contents are harmless.
+  return tfgpc_find_neighbors_count(stream, D, ns, samples, samples_batch_ids, n, points,
+                                    point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                    inv_cell_sizes, inv_radii, max_neighs, ranges_out, scratch,
+                                    kStaticScratchBytes, total_out);
 }
