@@ -240,6 +240,7 @@ def run_ours(args, rank, local_rank, world):
   import torch
   import torch.distributed as dist
   from tensorflow_graphics_point_clouds_b200 import _lib, build, mcconv, pc
+  from tensorflow_graphics_point_clouds_b200 import dist as tdist
 
   if not torch.cuda.is_available():
     raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
@@ -264,9 +265,7 @@ def run_ours(args, rank, local_rank, world):
     out = layer.forward(x["feat"], cloud, cloud, args.radius)
     sizes["m"] = int(layer._saved[0]._neighbors.shape[0])
     dfeat, dw1, db1, dwf = layer.backward(x["d_out"])
-    if world > 1:
-      flat = torch.cat([dwf.reshape(-1), dw1.reshape(-1), db1.reshape(-1)])
-      dist.all_reduce(flat)
+    tdist.allreduce_sum_([dwf, dw1, db1])   # the path's only exchange step
     return out, dfeat, dwf, dw1, db1
 
   def barrier():
@@ -294,11 +293,7 @@ def run_ours(args, rank, local_rank, world):
   _lib.profile_enable(False)
   clocks = sampler.stop()
   layer._op.check_status()
-  ms = e0.elapsed_time(e1)
-  t = torch.tensor([ms], device=dev)
-  if world > 1:
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-  ms_per_step = float(t.item()) / args.steps
+  ms_per_step = tdist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
 
   # ---- end to end: host buffers in, host buffers out, every step
   e2e = None
@@ -325,10 +320,7 @@ def run_ours(args, rank, local_rank, world):
       e2e_step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
+    e2e_ms = tdist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
     e2e = {"value": n * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
