@@ -282,7 +282,7 @@ static int launch_basis_proj(cudaStream_t st, int C, int64_t ns, const float* ba
   ProfScope prof(st, OUT == 0 ? "basis_proj" : "basis_proj_split");
   if (G == 32 && C % kCpl == 0 && ((uintptr_t)feat % 16 == 0) && (C * 4) % (kCpl * 4) == 0) {
     auto kern = basis_proj_wide_kernel<K, OUT>;
-    const size_t wsmem = (size_t)(kBpwThreads / 32) * 32 * BpCfg<K>::kRow * sizeof(float);
+    const size_t wsmem = (size_t)(kBpwThreads / 32) * bpw_warp_floats<K>() * sizeof(float);
     TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem));
     TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared));
@@ -337,7 +337,7 @@ static int launch_basis_proj_grads(cudaStream_t st, int C, int64_t ns, const flo
   if (G == 32 && C % kCpl == 0 && ((uintptr_t)feat % 16 == 0) && ((uintptr_t)dfeat % 16 == 0) &&
       ((uintptr_t)dbasis % 16 == 0)) {
     auto kern = basis_proj_grads_wide_kernel<K>;
-    const size_t wsmem = (size_t)(kBpwThreads / 32) * 2 * 32 * K * sizeof(float);
+    const size_t wsmem = (size_t)(kBpwThreads / 32) * bpw_grads_warp_floats<K>() * sizeof(float);
     TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem));
     TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared));

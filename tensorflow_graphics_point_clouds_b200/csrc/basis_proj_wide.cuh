@@ -49,6 +49,59 @@ __device__ __forceinline__ void stage_basis_chunk(float* tile, const float* __re
   for (int i = lane; i < cnt * (K / 4); i += 32) dst[i] = __ldg(src + i);
 }
 
+// ---- small PTX helpers ---------------------------------------------------------
+
+// Two fp32 FMAs per instruction (sm_100 packed fp32): d = a * b + c on both
+// halves of 64-bit register pairs.  Halves the issue slots of the FMA-bound
+// inner loops below.
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
+                                                    unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// Asynchronous global -> shared copy of one lane's slice of a feature row.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_row(float* dst_smem, const float* src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(dst_smem);
+  if (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src), "n"(BYTES)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kBpwRing = 8;  // feature rows in flight per warp
+
+// Floats of shared memory one warp needs: the output staging tile, or the ring
+// of in-flight feature rows plus the staged basis rows, whichever is larger.
+template <int K>
+__host__ __device__ constexpr int bpw_warp_floats() {
+  return (32 * BpCfg<K>::kRow > kBpwRing * 32 * BpCfg<K>::kCpl + 32 * K)
+             ? 32 * BpCfg<K>::kRow
+             : kBpwRing * 32 * BpCfg<K>::kCpl + 32 * K;
+}
+
 template <int K, int OUT>
 __global__ void __launch_bounds__(kBpwThreads, 2)
 basis_proj_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
@@ -59,10 +112,13 @@ basis_proj_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
   constexpr int kAcc = BpCfg<K>::kAcc;
   constexpr int kRow = BpCfg<K>::kRow;
   constexpr int kChunk = 32 * kCpl;
+  constexpr int R = kBpwRing;
   typedef typename FeatVec<kCpl>::type fvec;
   extern __shared__ __align__(16) float smem_all[];
   const int lane = lane_id();
-  float* tile = smem_all + (size_t)(threadIdx.x >> 5) * 32 * kRow;
+  float* tile = smem_all + (size_t)(threadIdx.x >> 5) * bpw_warp_floats<K>();
+  float* ring = tile;                           // [R][32 lanes][CPL]
+  float* wtile = tile + R * 32 * kCpl;          // [32 neighbors][K]
   const int64_t warps = ((int64_t)gridDim.x * kBpwThreads) >> 5;
   for (int64_t s = ((int64_t)blockIdx.x * kBpwThreads + threadIdx.x) >> 5; s < ns; s += warps) {
     const int a = s ? __ldg(ranges + s - 1) : 0;
@@ -70,68 +126,67 @@ basis_proj_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
     for (int c0 = 0; c0 < C; c0 += kChunk) {
       const int cbase = c0 + lane * kCpl;
       const bool c_ok = cbase < C;  // C is a multiple of CPL on this path
-      float acc[kCpl][K];
+      unsigned long long acc[kCpl][K / 2];
 #pragma unroll
       for (int cc = 0; cc < kCpl; ++cc)
 #pragma unroll
-        for (int k = 0; k < K; ++k) acc[cc][k] = 0.0f;
+        for (int k = 0; k < K / 2; ++k) acc[cc][k] = 0ull;
       for (int base = a; base < e; base += 32) {
         const int cnt = min(32, e - base);
         __syncwarp();
         const int my_j = lane < cnt ? __ldg(&neigh[base + lane].x) : 0;
-        stage_basis_chunk<K>(tile, basis, base, cnt, lane);
+        stage_basis_chunk<K>(wtile, basis, base, cnt, lane);
+        // fill the ring: rows 0 .. R-1 of the chunk (one commit group per row)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int j = __shfl_sync(0xffffffffu, my_j, r);
+          if (r < cnt && c_ok)
+            cp_async_row<kCpl * 4>(ring + (r * 32 + lane) * kCpl, feat + (int64_t)j * C + cbase);
+          cp_async_commit();
+        }
         __syncwarp();
-        // Feature rows are fetched one group of U ahead of their use.
-        fvec cur[kBpwUnroll], nxt[kBpwUnroll];
-        auto fetch = [&](fvec* dst, int it) {
+        for (int it = 0; it < cnt; ++it) {
+          cp_async_wait<R - 1>();  // row `it` has landed (each lane reads only what it copied)
+          float f[kCpl];
+          if (c_ok) {
+            FeatVec<kCpl>::unpack(*reinterpret_cast<const fvec*>(ring + ((it & (R - 1)) * 32 + lane) * kCpl), f);
+          } else {
 #pragma unroll
-          for (int u = 0; u < kBpwUnroll; ++u) {
-            const int j = __shfl_sync(0xffffffffu, my_j, (it + u) & 31);
-            if (it + u < cnt && c_ok)
-              dst[u] = __ldg(reinterpret_cast<const fvec*>(feat + (int64_t)j * C + cbase));
+            for (int cc = 0; cc < kCpl; ++cc) f[cc] = 0.0f;
           }
-        };
-        auto consume = [&](const fvec* src, int it) {
+          unsigned long long ff[kCpl];
 #pragma unroll
-          for (int u = 0; u < kBpwUnroll; ++u) {
-            if (it + u < cnt) {
-              float f[kCpl];
-              if (c_ok) FeatVec<kCpl>::unpack(src[u], f);
-              else {
+          for (int cc = 0; cc < kCpl; ++cc) ff[cc] = pack2(f[cc], f[cc]);
+          const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(wtile + it * K);
 #pragma unroll
-                for (int cc = 0; cc < kCpl; ++cc) f[cc] = 0.0f;
-              }
-              const float4* wrow = reinterpret_cast<const float4*>(tile + (it + u) * K);
+          for (int q = 0; q < K / 4; ++q) {
+            const ulonglong2 w = wrow[q];
 #pragma unroll
-              for (int q = 0; q < K / 4; ++q) {
-                const float4 w = wrow[q];
-#pragma unroll
-                for (int cc = 0; cc < kCpl; ++cc) {
-                  acc[cc][4 * q] = fmaf(f[cc], w.x, acc[cc][4 * q]);
-                  acc[cc][4 * q + 1] = fmaf(f[cc], w.y, acc[cc][4 * q + 1]);
-                  acc[cc][4 * q + 2] = fmaf(f[cc], w.z, acc[cc][4 * q + 2]);
-                  acc[cc][4 * q + 3] = fmaf(f[cc], w.w, acc[cc][4 * q + 3]);
-                }
-              }
+            for (int cc = 0; cc < kCpl; ++cc) {
+              acc[cc][2 * q] = ffma2(ff[cc], w.x, acc[cc][2 * q]);
+              acc[cc][2 * q + 1] = ffma2(ff[cc], w.y, acc[cc][2 * q + 1]);
             }
           }
-        };
-        fetch(cur, 0);
-        for (int it = 0; it < cnt; it += 2 * kBpwUnroll) {
-          fetch(nxt, it + kBpwUnroll);
-          consume(cur, it);
-          fetch(cur, it + 2 * kBpwUnroll);
-          consume(nxt, it + kBpwUnroll);
+          // refill the slot just consumed with row it + R
+          const int nxt = it + R;
+          const int jn = __shfl_sync(0xffffffffu, my_j, nxt & 31);
+          if (nxt < cnt && c_ok)
+            cp_async_row<kCpl * 4>(ring + ((it & (R - 1)) * 32 + lane) * kCpl,
+                                   feat + (int64_t)jn * C + cbase);
+          cp_async_commit();
         }
+        cp_async_wait<0>();
       }
       // stage the warp's 32 x (CPL*K) results, then store 512 contiguous bytes
       // per warp instruction
       __syncwarp();
 #pragma unroll
-      for (int q = 0; q < kAcc / 4; ++q)
-        *reinterpret_cast<float4*>(tile + lane * kRow + 4 * q) =
-            make_float4(acc[(4 * q) / K][(4 * q) % K], acc[(4 * q + 1) / K][(4 * q + 1) % K],
-                        acc[(4 * q + 2) / K][(4 * q + 2) % K], acc[(4 * q + 3) / K][(4 * q + 3) % K]);
+      for (int q = 0; q < kAcc / 4; ++q) {
+        float4 v;
+        unpack2(acc[(4 * q) / K][((4 * q) % K) / 2], v.x, v.y);
+        unpack2(acc[(4 * q) / K][((4 * q) % K) / 2 + 1], v.z, v.w);
+        *reinterpret_cast<float4*>(tile + lane * kRow + 4 * q) = v;
+      }
       __syncwarp();
       const int valid = min(kChunk, C - c0) * K;
       const int64_t obase = s * (int64_t)C * K + (int64_t)c0 * K;
@@ -158,6 +213,11 @@ basis_proj_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
 // shared-memory tile [32 neighbors x K], which is written out with contiguous
 // stores once per chunk -- no atomics on dbasis.
 template <int K>
+__host__ __device__ constexpr int bpw_grads_warp_floats() {
+  return kBpwRing * 32 * BpCfg<K>::kCpl + 2 * 32 * K;
+}
+
+template <int K>
 __global__ void __launch_bounds__(kBpwThreads, 2)
 basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
                              const float* __restrict__ feat, const int2* __restrict__ neigh,
@@ -166,12 +226,13 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
                              float* __restrict__ dfeat) {
   constexpr int kCpl = BpCfg<K>::kCpl;
   constexpr int kChunk = 32 * kCpl;
-  constexpr int kU = 4;
+  constexpr int R = kBpwRing;
   typedef typename FeatVec<kCpl>::type fvec;
   extern __shared__ __align__(16) float smem_all[];
   const int lane = lane_id();
-  float* wtile = smem_all + (size_t)(threadIdx.x >> 5) * 2 * 32 * K;  // staged basis rows
-  float* dtile = wtile + 32 * K;                                      // dbasis of the chunk
+  float* ring = smem_all + (size_t)(threadIdx.x >> 5) * bpw_grads_warp_floats<K>();  // [R][32][CPL]
+  float* wtile = ring + R * 32 * kCpl;   // staged basis rows [32][K]
+  float* dtile = wtile + 32 * K;         // dbasis of the chunk [32][K]
   const int64_t warps = ((int64_t)gridDim.x * kBpwThreads) >> 5;
   // which basis function this lane holds after the butterfly (see below)
   int kbase = 0;
@@ -189,100 +250,112 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
       const int my_j = lane < cnt ? __ldg(&neigh[base + lane].x) : 0;
       stage_basis_chunk<K>(wtile, basis, base, cnt, lane);
       for (int i = lane; i < 32 * K; i += 32) dtile[i] = 0.0f;
-      __syncwarp();
       for (int c0 = 0; c0 < C; c0 += kChunk) {
         const int cbase = c0 + lane * kCpl;
         const bool c_ok = cbase < C;
-        float g[kCpl][K];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int j = __shfl_sync(0xffffffffu, my_j, r);
+          if (r < cnt && c_ok)
+            cp_async_row<kCpl * 4>(ring + (r * 32 + lane) * kCpl, feat + (int64_t)j * C + cbase);
+          cp_async_commit();
+        }
+        // this lane's CPL x K tile of the incoming gradient, as packed pairs over k
+        unsigned long long g[kCpl][K / 2];
 #pragma unroll
         for (int cc = 0; cc < kCpl; ++cc) {
-          const float4* src = reinterpret_cast<const float4*>(
+          const ulonglong2* src = reinterpret_cast<const ulonglong2*>(
               in_grads + s * (int64_t)C * K + (int64_t)(cbase + cc) * K);
 #pragma unroll
           for (int q = 0; q < K / 4; ++q) {
-            const float4 v = c_ok ? __ldg(src + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            g[cc][4 * q] = v.x; g[cc][4 * q + 1] = v.y; g[cc][4 * q + 2] = v.z; g[cc][4 * q + 3] = v.w;
+            const ulonglong2 v = c_ok ? __ldg(src + q) : make_ulonglong2(0ull, 0ull);
+            g[cc][2 * q] = v.x; g[cc][2 * q + 1] = v.y;
           }
         }
-        for (int it = 0; it < cnt; it += kU) {
-          fvec fv[kU];
-          int js[kU];
+        __syncwarp();
+        for (int it = 0; it < cnt; ++it) {
+          cp_async_wait<R - 1>();
+          float f[kCpl];
+          if (c_ok) {
+            FeatVec<kCpl>::unpack(*reinterpret_cast<const fvec*>(ring + ((it & (R - 1)) * 32 + lane) * kCpl), f);
+          } else {
 #pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            js[u] = __shfl_sync(0xffffffffu, my_j, (it + u) & 31);
-            if (it + u < cnt && c_ok)
-              fv[u] = __ldg(reinterpret_cast<const fvec*>(feat + (int64_t)js[u] * C + cbase));
+            for (int cc = 0; cc < kCpl; ++cc) f[cc] = 0.0f;
           }
+          const int j = __shfl_sync(0xffffffffu, my_j, it);
+          unsigned long long w[K / 2];
+          const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(wtile + it * K);
 #pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            if (it + u < cnt) {  // warp-uniform
-              float f[kCpl], w[K], part[K];
-              if (c_ok) FeatVec<kCpl>::unpack(fv[u], f);
-              else {
+          for (int q = 0; q < K / 4; ++q) {
+            const ulonglong2 v = wrow[q];
+            w[2 * q] = v.x; w[2 * q + 1] = v.y;
+          }
+          // dfeat[nbr, c] += sum_k g[c,k] * basis[m,k]
+          float df[kCpl];
 #pragma unroll
-                for (int cc = 0; cc < kCpl; ++cc) f[cc] = 0.0f;
-              }
-              const float4* wrow = reinterpret_cast<const float4*>(wtile + (it + u) * K);
+          for (int cc = 0; cc < kCpl; ++cc) {
+            unsigned long long acc2 = 0ull;
 #pragma unroll
-              for (int q = 0; q < K / 4; ++q) {
-                const float4 v = wrow[q];
-                w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
-              }
-              float df[kCpl];
-#pragma unroll
-              for (int cc = 0; cc < kCpl; ++cc) {
-                float accv = 0.0f;
-#pragma unroll
-                for (int k = 0; k < K; ++k) accv = fmaf(g[cc][k], w[k], accv);
-                df[cc] = accv;
-              }
-              if (c_ok) {
-                float* dst = dfeat + (int64_t)js[u] * C + cbase;
-                if (kCpl == 4) {
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
-                               "f"(df[0]), "f"(df[1]), "f"(df[2]), "f"(df[3]) : "memory");
-                } else if (kCpl == 2) {
-                  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(dst), "f"(df[0]),
-                               "f"(df[1 % kCpl]) : "memory");
-                } else {
-                  atomicAdd(dst, df[0]);
-                }
-              }
-#pragma unroll
-              for (int k = 0; k < K; ++k) {
-                float accv = 0.0f;
-#pragma unroll
-                for (int cc = 0; cc < kCpl; ++cc) accv = fmaf(g[cc][k], f[cc], accv);
-                part[k] = accv;
-              }
-              // halving butterfly over xor distances 1, 2, 4, ...: lanes with
-              // the distance bit set keep the upper half of their values
-#pragma unroll
-              for (int t = 0; t < 5; ++t) {
-                const int half = 1 << t;
-                const int width = K >> (t + 1);
-                if (width >= 1) {
-                  const bool upper = (lane & half) != 0;
-#pragma unroll
-                  for (int k = 0; k < K / 2; ++k) {
-                    if (k < width) {
-                      const float send = upper ? part[k] : part[k + width];
-                      const float keep = upper ? part[k + width] : part[k];
-                      part[k] = keep + __shfl_xor_sync(0xffffffffu, send, half);
-                    }
-                  }
-                } else {
-                  part[0] += __shfl_xor_sync(0xffffffffu, part[0], half);
-                }
-              }
-              if (owner) {
-#pragma unroll
-                for (int q = 0; q < K; ++q)
-                  if (q < own_cnt) dtile[(it + u) * K + kbase + q] += part[q];
-              }
+            for (int kp = 0; kp < K / 2; ++kp) acc2 = ffma2(g[cc][kp], w[kp], acc2);
+            float lo, hi;
+            unpack2(acc2, lo, hi);
+            df[cc] = lo + hi;
+          }
+          if (c_ok) {
+            float* dst = dfeat + (int64_t)j * C + cbase;
+            if (kCpl == 4) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(df[0]),
+                           "f"(df[1 % kCpl]), "f"(df[2 % kCpl]), "f"(df[3 % kCpl]) : "memory");
+            } else if (kCpl == 2) {
+              asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(dst), "f"(df[0]),
+                           "f"(df[1 % kCpl]) : "memory");
+            } else {
+              atomicAdd(dst, df[0]);
             }
           }
+          // dbasis[m, k]: partial sums over this lane's channels ...
+          float part[K];
+#pragma unroll
+          for (int kp = 0; kp < K / 2; ++kp) {
+            unsigned long long acc2 = 0ull;
+#pragma unroll
+            for (int cc = 0; cc < kCpl; ++cc) acc2 = ffma2(g[cc][kp], pack2(f[cc], f[cc]), acc2);
+            unpack2(acc2, part[2 * kp], part[2 * kp + 1]);
+          }
+          // ... folded over the 32 lanes by a halving butterfly over xor distances
+          // 1, 2, 4, ...: lanes with the distance bit set keep the upper half
+#pragma unroll
+          for (int t = 0; t < 5; ++t) {
+            const int half = 1 << t;
+            const int width = K >> (t + 1);
+            if (width >= 1) {
+              const bool upper = (lane & half) != 0;
+#pragma unroll
+              for (int k = 0; k < K / 2; ++k) {
+                if (k < width) {
+                  const float send = upper ? part[k] : part[k + width];
+                  const float keep = upper ? part[k + width] : part[k];
+                  part[k] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+                }
+              }
+            } else {
+              part[0] += __shfl_xor_sync(0xffffffffu, part[0], half);
+            }
+          }
+          if (owner) {
+#pragma unroll
+            for (int q = 0; q < K; ++q)
+              if (q < own_cnt) dtile[it * K + kbase + q] += part[q];
+          }
+          // refill the ring slot just consumed
+          const int nxt = it + R;
+          const int jn = __shfl_sync(0xffffffffu, my_j, nxt & 31);
+          if (nxt < cnt && c_ok)
+            cp_async_row<kCpl * 4>(ring + ((it & (R - 1)) * 32 + lane) * kCpl,
+                                   feat + (int64_t)jn * C + cbase);
+          cp_async_commit();
         }
+        cp_async_wait<0>();
       }
       __syncwarp();
       float4* dst = reinterpret_cast<float4*>(dbasis + (int64_t)base * K);
