@@ -63,6 +63,15 @@ int tfgpc_compute_keys(void* stream, int D, int64_t n, const float* points,
                        const float* scaled_aabb_min, const int32_t* num_cells,
                        const float* inv_cell_sizes, int64_t* keys_out);
 
+/* ---- per-cloud bounding box ------------------------------------------------
+ * Replaces the tf.math.unsorted_segment_min / _max pair of
+ * pylib/pc/PointCloud.py:38-43 (the -+1e-9 margins stay with the caller).
+ * points [n,D], batch_ids [n] -> aabb_min_out, aabb_max_out [batch_size,D];
+ * clouds without points keep +inf / -inf. */
+int tfgpc_compute_aabb(void* stream, int D, int64_t n, const float* points,
+                       const int32_t* batch_ids, int64_t batch_size,
+                       float* aabb_min_out, float* aabb_max_out);
+
 /* ---- key sort + gather ---------------------------------------------------
  * Replaces tf.argsort(keys, 'DESCENDING') and the three tf.gather calls of
  * pylib/pc/Grid.py:56-64.  Stable: equal keys keep the lower original index
@@ -175,6 +184,19 @@ int tfgpc_compute_pdf_pt_grads(void* stream, int D, int mode, int64_t n,
                                const float* inv_bandwidth,
                                const float* inv_radii, const float* pdf_grads,
                                float* pt_grads_out);
+
+/* Density at arbitrary sample positions: the same sum as tfgpc_compute_pdf but
+ * centred on samples [ns,D] whose neighbor lists (neighbors [M,2], ranges
+ * [ns]) index points [n,D]; mode 1 uses sqrt(n).  When the samples are the
+ * grid's own points in another order this equals ComputePdf on the self
+ * neighborhood, so MCConv on one cloud needs a single neighbor search where
+ * pylib builds a second one (pylib/pc/Neighborhood.py:284). */
+int tfgpc_compute_pdf_at_samples(void* stream, int D, int mode, int64_t ns,
+                                 const float* samples, int64_t n,
+                                 const float* points, const int32_t* neighbors,
+                                 int64_t M, const int32_t* ranges,
+                                 const float* inv_bandwidth,
+                                 const float* inv_radii, float* pdf_out);
 
 /* ---- BasisProj / BasisProjGrads ------------------------------------------
  * Replaces BasisProjOp::Compute (basis_proj/cc/ops/basis_proj_ops.cpp:77-132)

@@ -30,6 +30,8 @@ SYMBOLS = {
     "tfgpc_last_error": ctypes.c_char_p,
     "tfgpc_version": c_int,
     "tfgpc_compute_keys": c_int,
+    "tfgpc_compute_aabb": c_int,
+    "tfgpc_compute_pdf_at_samples": c_int,
     "tfgpc_sort_keys_workspace_bytes": c_sz,
     "tfgpc_sort_keys_desc": c_int,
     "tfgpc_build_grid_ds": c_int,

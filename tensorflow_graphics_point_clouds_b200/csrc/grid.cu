@@ -88,6 +88,68 @@ __global__ void build_grid_ds_kernel(int64_t n, const int64_t* __restrict__ keys
   if (i + 1 == n || __ldg(keys + i + 1) / div != cur) ds[cur].y = (int)(i + 1);
 }
 
+// Per-cloud axis-aligned bounding box (the unsorted_segment_min / _max of
+// pylib/pc/PointCloud.py:38-43).  Floats are ordered through their bit
+// patterns: non-negative values compare like signed ints, negative values like
+// reversed unsigned ints, so one integer atomic per value is enough.
+__device__ __forceinline__ void atomic_min_float(float* addr, float v) {
+  if (v >= 0.0f) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
+}
+
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  if (v >= 0.0f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
+}
+
+__global__ void fill_kernel(float* out, int64_t n, float v) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = v;
+}
+
+// Each thread folds a run of consecutive points that share a batch id in
+// registers and issues atomics only when the id changes, so clouds stored
+// contiguously cost a handful of atomics per thread.
+template <int D>
+__global__ void __launch_bounds__(256)
+aabb_kernel(int64_t n, const float* __restrict__ pts, const int32_t* __restrict__ batch_ids,
+            int batch_size, float* __restrict__ mn, float* __restrict__ mx) {
+  constexpr int kPer = 16;
+  const int64_t begin = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * kPer;
+  if (begin >= n) return;
+  const int64_t end = min(begin + kPer, n);
+  int cur = -1;
+  float lo[D], hi[D];
+  for (int64_t i = begin; i < end; ++i) {
+    const int b = __ldg(batch_ids + i);
+    if (b != cur) {
+      if (cur >= 0 && cur < batch_size) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+          atomic_min_float(mn + (int64_t)cur * D + d, lo[d]);
+          atomic_max_float(mx + (int64_t)cur * D + d, hi[d]);
+        }
+      }
+      cur = b;
+#pragma unroll
+      for (int d = 0; d < D; ++d) { lo[d] = INFINITY; hi[d] = -INFINITY; }
+    }
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      const float v = __ldg(pts + i * D + d);
+      lo[d] = fminf(lo[d], v);
+      hi[d] = fmaxf(hi[d], v);
+    }
+  }
+  if (cur >= 0 && cur < batch_size) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      atomic_min_float(mn + (int64_t)cur * D + d, lo[d]);
+      atomic_max_float(mx + (int64_t)cur * D + d, hi[d]);
+    }
+  }
+}
+
 }  // namespace tfgpc
 
 using namespace tfgpc;
@@ -184,6 +246,27 @@ extern "C" int tfgpc_build_grid_ds(void* stream, int D, int64_t n, const int64_t
   ProfScope prof(st, "build_grid_ds");
   TFGPC_DIM_SWITCH(D, build_grid_ds_kernel<kD><<<blocks_for(n, 256), 256, 0, st>>>(
       n, sorted_keys, num_cells, n_ds, (int2*)ds_out));
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_compute_aabb(void* stream, int D, int64_t n, const float* points,
+                                  const int32_t* batch_ids, int64_t batch_size, float* aabb_min_out,
+                                  float* aabb_max_out) {
+  TFGPC_REQUIRE(valid_dims(D), "ComputeAabb expects a valid number of dimension (got %d)", D);
+  TFGPC_REQUIRE(n >= 0 && batch_size > 0 && batch_size < (int64_t)INT32_MAX,
+                "ComputeAabb expects n >= 0 and a positive batch size");
+  TFGPC_REQUIRE(aabb_min_out && aabb_max_out, "ComputeAabb got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  ProfScope prof(st, "compute_aabb");
+  const int64_t cells = batch_size * D;
+  fill_kernel<<<blocks_for(cells, 256), 256, 0, st>>>(aabb_min_out, cells, INFINITY);
+  fill_kernel<<<blocks_for(cells, 256), 256, 0, st>>>(aabb_max_out, cells, -INFINITY);
+  TFGPC_LAUNCH_CHECK();
+  if (n == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(points && batch_ids, "ComputeAabb got a null pointer");
+  TFGPC_DIM_SWITCH(D, aabb_kernel<kD><<<blocks_for((n + 15) / 16, 256), 256, 0, st>>>(
+      n, points, batch_ids, (int)batch_size, aabb_min_out, aabb_max_out));
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

@@ -83,8 +83,8 @@ extern "C" int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_
   if (ns == 0) return TFGPC_OK;
   TFGPC_REQUIRE(ranges && weights && out && ws && (M == 0 || (basis && features && neighbors)),
                 "MCConvForward got a null pointer");
-  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)ws % 1024 == 0,
-                "MCConvForward expects 16-byte aligned buffers and a 1024-byte aligned workspace");
+  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)ws % 256 == 0,
+                "MCConvForward expects 16-byte aligned buffers and a 256-byte aligned workspace");
   if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0))
     return fail(TFGPC_ENOMEM, "MCConvForward workspace too small: %zu < %zu", ws_bytes,
                 tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0));
@@ -122,8 +122,8 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   TFGPC_REQUIRE(basis && features && neighbors && ranges && out_grads && dbasis_out && dfeat_out && ws,
                 "MCConvBackward got a null pointer");
   TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out_grads % 16 == 0 &&
-                (uintptr_t)ws % 1024 == 0,
-                "MCConvBackward expects 16-byte aligned buffers and a 1024-byte aligned workspace");
+                (uintptr_t)ws % 256 == 0,
+                "MCConvBackward expects 16-byte aligned buffers and a 256-byte aligned workspace");
   if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1))
     return fail(TFGPC_ENOMEM, "MCConvBackward workspace too small: %zu < %zu", ws_bytes,
                 tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1));
@@ -178,7 +178,7 @@ extern "C" int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K, c
                                 void* ws, size_t ws_bytes) {
   TFGPC_REQUIRE(M > 0 && N > 0 && K > 0, "matmul expects positive sizes");
   TFGPC_REQUIRE(a && b && c && ws, "matmul got a null pointer");
-  TFGPC_REQUIRE((uintptr_t)ws % 1024 == 0, "matmul expects a 1024-byte aligned workspace");
+  TFGPC_REQUIRE((uintptr_t)ws % 256 == 0, "matmul expects a 256-byte aligned workspace");
   TFGPC_REQUIRE((a_transposed ? M : K) % 8 == 0 && (b_transposed ? K : N) % 8 == 0,
                 "matmul expects row lengths that are multiples of 8");
   if (ws_bytes < tfgpc_matmul_workspace_bytes(M, N, K))

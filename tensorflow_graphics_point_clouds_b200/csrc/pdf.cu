@@ -27,12 +27,13 @@ __device__ __forceinline__ void load_bandwidth(int mode, int64_t n, const float*
 
 template <int D>
 __global__ void __launch_bounds__(kPdfThreads)
-compute_pdf_kernel(int mode, int64_t n, const float* __restrict__ pts,
+compute_pdf_kernel(int mode, int64_t n, int64_t n_bw, const float* __restrict__ centers,
+                   const float* __restrict__ pts,
                    const int2* __restrict__ neigh, const int32_t* __restrict__ ranges,
                    const float* __restrict__ inv_bw, const float* __restrict__ inv_r,
                    float* __restrict__ pdf_out) {
   float bw[D], ir[D];
-  load_bandwidth<D>(mode, n, inv_bw, inv_r, bw, ir);
+  load_bandwidth<D>(mode, n_bw, inv_bw, inv_r, bw, ir);
   const int lane = lane_id();
   const int64_t warps = ((int64_t)gridDim.x * kPdfThreads) >> 5;
   for (int64_t i = ((int64_t)blockIdx.x * kPdfThreads + threadIdx.x) >> 5; i < n; i += warps) {
@@ -40,7 +41,7 @@ compute_pdf_kernel(int mode, int64_t n, const float* __restrict__ pts,
     const int e = __ldg(ranges + i);
     float p[D];
 #pragma unroll
-    for (int d = 0; d < D; ++d) p[d] = __ldg(pts + i * D + d);
+    for (int d = 0; d < D; ++d) p[d] = __ldg(centers + i * D + d);
     float acc = 0.0f;
     for (int m = a + lane; m < e; m += 32) {
       const int j = __ldg(&neigh[m].x);
@@ -130,7 +131,29 @@ extern "C" int tfgpc_compute_pdf(void* stream, int D, int mode, int64_t n, const
   unsigned grid = min(blocks_for(n, kPdfThreads / 32), (unsigned)(sm_count() * 32));
   ProfScope prof(st, "compute_pdf");
   TFGPC_DIM_SWITCH(D, compute_pdf_kernel<kD><<<grid, kPdfThreads, 0, st>>>(
-      mode, n, points, (const int2*)neighbors, ranges, inv_bandwidth, inv_radii, pdf_out));
+      mode, n, n, points, points, (const int2*)neighbors, ranges, inv_bandwidth, inv_radii,
+      pdf_out));
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_compute_pdf_at_samples(void* stream, int D, int mode, int64_t ns,
+                                            const float* samples, int64_t n, const float* points,
+                                            const int32_t* neighbors, int64_t M,
+                                            const int32_t* ranges, const float* inv_bandwidth,
+                                            const float* inv_radii, float* pdf_out) {
+  int rc = check_pdf_args("ComputePdfAtSamples", D, mode, ns, M);
+  if (rc) return rc;
+  TFGPC_REQUIRE(n >= 0 && n < (int64_t)INT32_MAX, "ComputePdfAtSamples expects 0 <= n < 2^31");
+  if (ns == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(samples && points && ranges && inv_bandwidth && inv_radii && pdf_out &&
+                (M == 0 || neighbors), "ComputePdfAtSamples got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned grid = min(blocks_for(ns, kPdfThreads / 32), (unsigned)(sm_count() * 32));
+  ProfScope prof(st, "compute_pdf");
+  TFGPC_DIM_SWITCH(D, compute_pdf_kernel<kD><<<grid, kPdfThreads, 0, st>>>(
+      mode, ns, n, samples, points, (const int2*)neighbors, ranges, inv_bandwidth, inv_radii,
+      pdf_out));
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

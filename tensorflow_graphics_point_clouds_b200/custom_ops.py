@@ -53,6 +53,19 @@ def compute_keys(points, batch_ids, scaled_aabb_min, num_cells, inv_cell_sizes):
   return keys
 
 
+def compute_aabb(points, batch_ids, batch_size):
+  """Per-cloud bounding box (unsorted_segment_min/max of PointCloud.py:38-43)."""
+  points, batch_ids = _f32(points), _i32(batch_ids)
+  _dev_check(points, batch_ids)
+  n, d = points.shape
+  mn = torch.empty((batch_size, d), dtype=torch.float32, device=points.device)
+  mx = torch.empty_like(mn)
+  _lib.check(_lib.lib().tfgpc_compute_aabb(
+      _stream(), c_int(d), c_i64(n), ptr(points), ptr(batch_ids), c_i64(batch_size), ptr(mn),
+      ptr(mx)))
+  return mn, mx
+
+
 def sort_keys_desc(keys, points=None, batch_ids=None, key_bits=0):
   """tf.argsort(keys, 'DESCENDING') plus the gathers of pylib/pc/Grid.py:56-64
   in one call.  Returns (perm, sorted_keys[, sorted_points, sorted_batch_ids])."""
@@ -164,6 +177,26 @@ def compute_pdf_with_pt_grads(points, neighbors, sample_neigh_indices, inv_bandw
 
 
 compute_pdf = compute_pdf_with_pt_grads  # same kernel class (compute_pdf_ops.cpp:257-258)
+
+
+def compute_pdf_at_samples(samples, points, neighbors, sample_neigh_indices, inv_bandwidth,
+                           inv_radii, mode):
+  """Density estimate centred on `samples` over their neighbor lists into
+  `points` (tfgpc_compute_pdf_at_samples)."""
+  samples = _f32(samples)
+  points = _f32(points)
+  neighbors, ranges = _i32(neighbors), _i32(sample_neigh_indices)
+  inv_bw, inv_r = _f32(inv_bandwidth), _f32(inv_radii)
+  _dev_check(samples, points, neighbors, ranges, inv_bw, inv_r)
+  ns, d = samples.shape
+  if ranges.shape[0] != ns:
+    raise _lib.TfgpcError(1, "ComputePdfAtSamples expects one range per sample")
+  pdf = torch.empty(ns, dtype=torch.float32, device=samples.device)
+  _lib.check(_lib.lib().tfgpc_compute_pdf_at_samples(
+      _stream(), c_int(d), c_int(int(mode)), c_i64(ns), ptr(samples), c_i64(points.shape[0]),
+      ptr(points), ptr(neighbors), c_i64(neighbors.shape[0]), ptr(ranges), ptr(inv_bw),
+      ptr(inv_r), ptr(pdf)))
+  return pdf
 
 
 def compute_pdf_pt_grads(points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii,

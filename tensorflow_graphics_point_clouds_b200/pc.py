@@ -44,12 +44,7 @@ class PointCloud:
   def get_AABB(self):
     """PointCloud.py:38-43: per-cloud min - 1e-9 and max + 1e-9 in float32."""
     if self._aabb is None:
-      d, b = self._dimension, self._batch_size
-      idx = self._batch_ids.to(torch.int64).unsqueeze(1).expand(-1, d)
-      mn = torch.full((b, d), float('inf'), device=self._points.device)
-      mx = torch.full((b, d), float('-inf'), device=self._points.device)
-      mn = mn.scatter_reduce(0, idx, self._points, reduce='amin')
-      mx = mx.scatter_reduce(0, idx, self._points, reduce='amax')
+      mn, mx = ops.compute_aabb(self._points, self._batch_ids, self._batch_size)
       self._aabb = (mn - 1e-9, mx + 1e-9)
     return self._aabb
 
@@ -109,20 +104,49 @@ class Neighborhood:
         smp._points, smp._batch_ids, grid._sorted_points, grid._sorted_keys, grid.get_DS(),
         grid._num_cells, grid._scaled_aabb_min, grid._inv_cell_sizes,
         torch.reciprocal(self._radii), max_neighbors)
-    orig = grid._sorted_indices[self._neighbors[:, 0].to(torch.int64)]
-    self._original_neigh_ids = torch.stack([orig, self._neighbors[:, 1]], dim=1).contiguous()
+    self._orig_ids = None
     self._pdf = None
     self._point_pdf = None
 
+  @property
+  def _original_neigh_ids(self):
+    """Neighbor ids mapped back to the unsorted point order
+    (Neighborhood.py:246-250), built on first use."""
+    if self._orig_ids is None:
+      orig = self._grid._sorted_indices[self._neighbors[:, 0].to(torch.int64)]
+      self._orig_ids = torch.stack([orig, self._neighbors[:, 1]], dim=1).contiguous()
+    return self._orig_ids
+
+  def _samples_are_grid_points(self):
+    return self._equal_samples or (self._point_cloud_sampled is self._grid._point_cloud
+                                   and self.max_neighbors == 0)
+
   def compute_pdf(self, bandwidth=0.2, mode=0):
-    """Neighborhood.py:257-311 (mode: 0 constant bandwidth, 1 by point count)."""
+    """Neighborhood.py:257-311 (mode: 0 constant bandwidth, 1 by point count).
+    The density is needed at every neighbor point.  pylib gets it from a second,
+    self neighborhood of the grid (Neighborhood.py:284); when the samples are the
+    grid's own cloud that second search is skipped: the density at sample s is
+    the density of the point it coincides with."""
     d = self._point_cloud_sampled._dimension
     bw = _to_dims(bandwidth, d, self._radii.device)
-    nb = self if self._equal_samples else Neighborhood(self._grid, self._radii)
-    self._point_pdf = ops.compute_pdf_with_pt_grads(
-        self._grid._sorted_points, nb._neighbors, nb._samples_neigh_ranges,
-        torch.reciprocal(bw), torch.reciprocal(self._radii), mode)
-    self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
+    inv_bw, inv_r = torch.reciprocal(bw), torch.reciprocal(self._radii)
+    g = self._grid
+    if self._equal_samples:
+      self._point_pdf = ops.compute_pdf_with_pt_grads(
+          g._sorted_points, self._neighbors, self._samples_neigh_ranges, inv_bw, inv_r, mode)
+      self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
+    elif self._samples_are_grid_points():
+      sample_pdf = ops.compute_pdf_at_samples(
+          self._point_cloud_sampled._points, g._sorted_points, self._neighbors,
+          self._samples_neigh_ranges, inv_bw, inv_r, mode)
+      # sample s is point s of the unsorted cloud: index by the neighbors' original ids
+      self._point_pdf = sample_pdf[g._sorted_indices.to(torch.int64)]
+      self._pdf = sample_pdf[self._original_neigh_ids[:, 0].to(torch.int64)]
+    else:
+      nb = Neighborhood(g, self._radii)
+      self._point_pdf = ops.compute_pdf_with_pt_grads(
+          g._sorted_points, nb._neighbors, nb._samples_neigh_ranges, inv_bw, inv_r, mode)
+      self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
 
   def get_pdf(self, **kwargs):
     if self._pdf is None:

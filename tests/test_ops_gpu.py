@@ -301,3 +301,38 @@ def test_results_are_deterministic():
     outs.append((g._sorted_indices.cpu().numpy().tobytes(), nb._neighbors.cpu().numpy().tobytes(),
                  idx.cpu().numpy().tobytes()))
   assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("d", [2, 3, 6])
+def test_compute_aabb(d):
+  rng = np.random.default_rng(600 + d)
+  b = 7
+  pts = (rng.normal(size=(5000, d)) * 3).astype(F32)      # negative and positive values
+  bid = rng.integers(0, b - 1, 5000).astype(np.int32)     # cloud b-1 stays empty
+  mn, mx = ops.compute_aabb(t(pts), t(bid), b)
+  ref_mn = np.full((b, d), np.inf, F32); ref_mx = np.full((b, d), -np.inf, F32)
+  np.minimum.at(ref_mn, bid, pts); np.maximum.at(ref_mx, bid, pts)
+  assert np.array_equal(mn.cpu().numpy(), ref_mn)
+  assert np.array_equal(mx.cpu().numpy(), ref_mx)
+  # contiguous clouds (the common layout)
+  bid2 = np.sort(bid)
+  mn, mx = ops.compute_aabb(t(pts), t(bid2), b)
+  ref_mn[:] = np.inf; ref_mx[:] = -np.inf
+  np.minimum.at(ref_mn, bid2, pts); np.maximum.at(ref_mx, bid2, pts)
+  assert np.array_equal(mn.cpu().numpy(), ref_mn) and np.array_equal(mx.cpu().numpy(), ref_mx)
+
+
+def test_pdf_without_second_neighbor_search_matches_self_neighborhood():
+  """A neighborhood whose samples are the grid's own cloud (unsorted) gets its
+  densities from one search; pylib's route is the sorted self neighborhood."""
+  rng = np.random.default_rng(42)
+  b = 3
+  pts, bid = random_cloud(rng, b, 3000, 3)
+  g_ref = pr.Grid(pts, bid, b, 0.2)
+  nb_ref = pr.Neighborhood(g_ref, 0.2, pts, bid)
+  ref_pdf = nb_ref.get_pdf(bandwidth=0.2, mode=0)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  nb = pc.Neighborhood(pc.Grid(cloud, 0.2), 0.2, cloud)
+  assert nb._samples_are_grid_points() and not nb._equal_samples
+  close(nb.get_pdf(bandwidth=0.2, mode=0).cpu().numpy(), ref_pdf)
+  close(nb._point_pdf.cpu().numpy(), nb_ref.point_pdf)
