@@ -6,8 +6,9 @@
 //              (one elected lane); completion is tracked with tcgen05.commit
 //              on mbarriers, which also hands ring slots back to the producer;
 //   warps 2-5  epilogue: tcgen05.ld the 128 x BN fp32 accumulator out of
-//              tensor memory and store it, while the MMA warp already works on
-//              the next tile in the second accumulator buffer.
+//              tensor memory, stage it in swizzled 32 x 32 boxes and hand those
+//              to TMA stores, while the MMA warp already works on the next tile
+//              in the second accumulator buffer.
 // Every wait is bounded: after about a second without progress the kernel sets
 // the caller's error flag, stops waiting and drains, so it always terminates
 // and frees its tensor memory.
@@ -30,7 +31,10 @@ constexpr int kTmemCols = 512;     // two accumulator buffers of 256 columns
 constexpr uint32_t kABytes = kBM * kBK * 2;        // one A tile (hi or mid)
 constexpr uint32_t kBBytes = kBNMax * kBK * 2;     // one B tile (hi or mid)
 constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kBBytes;
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr uint32_t kOutBoxBytes = 32 * 32 * 4;     // one 32 x 32 fp32 box of the epilogue
+constexpr uint32_t kOutStageBytes = 4 * 2 * kOutBoxBytes;  // 4 epilogue warps, double buffered
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kOutStageBytes +
+                              1024 /*alignment*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -90,6 +94,24 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Asynchronous store of a shared-memory box into a 3-D tensor (col, row, slice);
+// elements outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y,
+                                             int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -176,13 +198,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
                    const __grid_constant__ CUtensorMap tm_a_mid,
                    const __grid_constant__ CUtensorMap tm_b_hi,
-                   const __grid_constant__ CUtensorMap tm_b_mid, float* __restrict__ c,
-                   int64_t ldc, int64_t split_stride, int64_t m_total, int64_t n_total, int bn,
-                   uint32_t idesc, TileSchedule sch, int* err_flag) {
+                   const __grid_constant__ CUtensorMap tm_b_mid,
+                   const __grid_constant__ CUtensorMap tm_c, int64_t m_total, int64_t n_total,
+                   int bn, uint32_t idesc, TileSchedule sch, int* err_flag) {
   extern __shared__ uint8_t smem_raw[];
   // the swizzled tiles need 1024-byte alignment
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  Barriers* bars = (Barriers*)(smem + (size_t)kStages * kStageBytes);
+  uint8_t* out_stage = smem + (size_t)kStages * kStageBytes;  // 1024-byte aligned
+  Barriers* bars = (Barriers*)(out_stage + kOutStageBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
@@ -304,7 +327,14 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
     }
   } else {
     // -------------------------------------------------------------- epilogue
+    // Each warp drains its 32 accumulator rows 32 columns at a time: tcgen05.ld
+    // to registers, a 128-byte-swizzled 32 x 32 box in shared memory (lane =
+    // row, so the swizzle makes the 16-byte writes of a quarter warp hit
+    // distinct banks), then one TMA store per box, double buffered.  TMA clips
+    // the rows and columns beyond the edge of C.
     const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter ...
+    uint8_t* my_stage = out_stage + (size_t)quarter * 2 * kOutBoxBytes;
+    uint32_t box_iter = 0;
     int tile_iter = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
       int m, n, sp;
@@ -312,32 +342,32 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
       const int buf = tile_iter & 1;
       mbar_wait(smem_u32(&bars->acc_full[buf]), (tile_iter >> 1) & 1, abort_flag, err_flag);
       tc_fence_after();
-      const int64_t row = (int64_t)m * kBM + quarter * 32 + lane;
-      float* crow = c + (int64_t)sp * split_stride + row * ldc + (int64_t)n * bn;
-      const int64_t cols_left = n_total - (int64_t)n * bn;
-      for (int c0 = 0; c0 < bn; c0 += 32) {
+      const int row0 = m * kBM + quarter * 32;
+      for (int c0 = 0; c0 < bn; c0 += 32, ++box_iter) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                (uint32_t)(buf * kBNMax + c0);
         tmem_ld_32x32(taddr, r);
-        if (row < m_total && !*abort_flag) {
-          if (c0 + 32 <= cols_left && (ldc % 4 == 0)) {
+        uint8_t* box = my_stage + (size_t)(box_iter & 1) * kOutBoxBytes;
+        if (lane == 0) tma_store_wait_read<1>();  // the store that last used this box has read it
+        __syncwarp();
+        float4* rowp = reinterpret_cast<float4*>(box + lane * 128);
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(crow + c0 + 4 * q) =
-                  make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-          } else {
-#pragma unroll
-            for (int q = 0; q < 32; ++q)
-              if (c0 + q < cols_left) crow[c0 + q] = __uint_as_float(r[q]);
-          }
-        }
+        for (int q = 0; q < 8; ++q)
+          rowp[q ^ (lane & 7)] =
+              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        fence_proxy_async();
+        __syncwarp();
+        const int col0 = n * bn + c0;
+        if (lane == 0 && row0 < m_total && col0 < n_total && !*abort_flag)
+          tma_store_3d(&tm_c, smem_u32(box), col0, row0, sp);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
     }
+    if (lane == 0) tma_store_wait_read<0>();
   }
   tc_fence_before();
   __syncthreads();
@@ -385,6 +415,27 @@ int make_map(CUtensorMap* map, const __nv_bfloat16* base, int64_t dim0, int64_t 
   return TFGPC_OK;
 }
 
+// 3-D fp32 tensor map of C: (columns, rows, k slices), boxes of 32 x 32 x 1 with
+// the 128-byte swizzle the epilogue writes its staging boxes in.
+int make_map_c(CUtensorMap* map, float* base, int64_t n, int64_t m, int64_t slices, int64_t ldc,
+               int64_t split_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(TFGPC_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((uintptr_t)base % 16 != 0 || ldc % 4 != 0 || split_stride % 4 != 0)
+    return fail(TFGPC_EINVAL, "tensor-core GEMM output needs 16-byte aligned rows (ld %lld)",
+                (long long)ldc);
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)slices};
+  cuuint64_t strides[2] = {(cuuint64_t)ldc * 4,
+                           (cuuint64_t)(slices > 1 ? split_stride : m * ldc) * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TFGPC_ECUDA, "cuTensorMapEncodeTiled (C) failed with %d", (int)r);
+  return TFGPC_OK;
+}
+
 // Instruction descriptor of tcgen05.mma kind::f16: D fp32, A and B bf16.
 uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
   uint32_t d = 0;
@@ -399,8 +450,8 @@ uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
 }
 
 template <bool A_MN, bool B_MN>
-int launch(cudaStream_t st, const CUtensorMap* maps, float* c, int64_t ldc, int64_t split_stride,
-           int64_t M, int64_t N, int bn, TileSchedule sch, int* err_flag) {
+int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int bn,
+           TileSchedule sch, int* err_flag) {
   auto kern = gemm_bf16x3_kernel<A_MN, B_MN>;
   TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)kSmemBytes));
@@ -408,9 +459,8 @@ int launch(cudaStream_t st, const CUtensorMap* maps, float* c, int64_t ldc, int6
   const int grid = tiles < sm_count() ? tiles : sm_count();
   ProfScope prof(st, A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
                           : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
-  kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], c, ldc,
-                                           split_stride, M, N, bn, make_idesc(kBM, bn, A_MN, B_MN),
-                                           sch, err_flag);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
+                                           make_idesc(kBM, bn, A_MN, B_MN), sch, err_flag);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -483,7 +533,7 @@ int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const Gemm
   int bn = (int)(N < kBNMax ? N : kBNMax);
   const int gran = b_mn ? 64 : 32;
   bn = (bn + gran - 1) / gran * gran;
-  CUtensorMap maps[4];
+  CUtensorMap maps[5];
   int rc;
   const __nv_bfloat16* ap[2] = {a.hi, a.mid};
   const __nv_bfloat16* bp[2] = {b.hi, b.mid};
@@ -509,10 +559,12 @@ int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const Gemm
                                sizeof(float) * (size_t)(k_splits - sch.k_splits) * split_stride,
                                stream));
   }
-  if (a_mn && b_mn) return launch<true, true>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
-  if (a_mn) return launch<true, false>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
-  if (b_mn) return launch<false, true>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
-  return launch<false, false>(stream, maps, c, ldc, split_stride, M, N, bn, sch, err_flag);
+  rc = make_map_c(&maps[4], c, N, M, sch.k_splits, ldc, split_stride);
+  if (rc) return rc;
+  if (a_mn && b_mn) return launch<true, true>(stream, maps, M, N, bn, sch, err_flag);
+  if (a_mn) return launch<true, false>(stream, maps, M, N, bn, sch, err_flag);
+  if (b_mn) return launch<false, true>(stream, maps, M, N, bn, sch, err_flag);
+  return launch<false, false>(stream, maps, M, N, bn, sch, err_flag);
 }
 
 int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16* hi,
