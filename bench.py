@@ -34,7 +34,7 @@ UNIT = "points/s"
 def parse_args():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=10)
+  ap.add_argument("--steps", type=int, default=20)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--clouds", type=int, default=32)
@@ -90,7 +90,14 @@ def measured_peaks():
 # Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) taken
 # from the ncu captures summarised under profiles/, scaled to this workload by
 # the units processed; None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/projection_and_gemm_kernels_16_clouds.md, scaled x2 (16 -> 32 clouds)
+    "basis_proj_split": 2 * (1.030125e9 + 2.100271e9),
+    "basis_proj_grads": 2 * (4.091760e9 + 1.135269e9),
+    "gemm_bf16x3_k_mn": 2 * (2.176671e9 + 0.255460e9),
+    "gemm_bf16x3_k_k": 2 * (2.150015e9 + 2.098627e9),
+    "gemm_bf16x3_mn_mn": 2 * (2.415946e9 + 0.004173e9),
+}
 
 
 def kernel_model(name, sizes):
