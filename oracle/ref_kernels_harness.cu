@@ -43,6 +43,26 @@ namespace {
 
 int g_error = 0;  // sticky: first CUDA error seen by check_error
 
+// Device buffers are recycled between calls, so that a repeated call measures
+// the kernels and not cudaMalloc (the reference gets its temporaries from
+// TensorFlow's pooled allocator).
+struct PoolEntry { void* p; size_t bytes; bool busy; };
+std::vector<PoolEntry> g_pool;
+
+void* pool_get(size_t bytes) {
+  for (auto& e : g_pool)
+    if (!e.busy && e.bytes >= bytes && e.bytes <= 2 * bytes + 4096) { e.busy = true; return e.p; }
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
+  g_pool.push_back({p, bytes, true});
+  return p;
+}
+
+void pool_put(void* p) {
+  for (auto& e : g_pool)
+    if (e.p == p) e.busy = false;
+}
+
 class PlainCudaDevice : public mccnn::IGPUDevice {
  public:
   PlainCudaDevice() : stream_(0) {
@@ -63,7 +83,7 @@ class PlainCudaDevice : public mccnn::IGPUDevice {
   }
   ~PlainCudaDevice() override {
     cudaStreamSynchronize(stream_);
-    for (void* p : dev_) cudaFree(p);
+    for (void* p : dev_) pool_put(p);
     for (void* p : host_) cudaFreeHost(p);
   }
   void memset(void* d, int v, size_t n) override { cudaMemsetAsync(d, v, n, stream_); }
@@ -120,7 +140,7 @@ class PlainCudaDevice : public mccnn::IGPUDevice {
     void* p = nullptr;
     if (bytes == 0) bytes = 4;
     if (cpu) { cudaMallocHost(&p, bytes); host_.push_back(p); }
-    else { cudaMalloc(&p, bytes); dev_.push_back(p); }
+    else { p = pool_get(bytes); dev_.push_back(p); }
     return p;
   }
   cudaStream_t stream_;

@@ -1,0 +1,99 @@
+"""Times the reference's own CUDA kernels (oracle/_ref, compiled for sm_100a)
+against this library's kernels on the same B200 and the same seeded inputs
+(TEST INFRASTRUCTURE; needs a GPU).  Prints one table; the times are CUDA-event
+times around the kernel sequence of each op, host copies excluded.
+
+Usage: python oracle/time_ref_kernels.py [clouds] [points_per_cloud]
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from oracle import pylib_ref as pr  # noqa: E402
+from oracle import ref_kernels as ref  # noqa: E402
+from tensorflow_graphics_point_clouds_b200 import _lib, custom_ops as ops, pc, synthetic  # noqa: E402
+
+F32 = np.float32
+
+
+def ours(fn, name_prefixes, reps=3):
+  for _ in range(2):
+    fn()
+  torch.cuda.synchronize()
+  _lib.profile_enable(True)
+  for _ in range(reps):
+    fn()
+  torch.cuda.synchronize()
+  rec = _lib.profile_collect()
+  _lib.profile_enable(False)
+  return sum(ms for n, ms in rec if n.startswith(name_prefixes)) / reps
+
+
+def main():
+  clouds = int(sys.argv[1]) if len(sys.argv) > 1 else 8
+  per = int(sys.argv[2]) if len(sys.argv) > 2 else 16384
+  radius, cin, k = 0.079, 128, 16
+  pts, bid = synthetic.uniform_clouds(clouds, per, seed=2)
+  n = len(pts)
+  rng = np.random.default_rng(0)
+  t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+  cloud = pc.PointCloud(t(pts), t(bid), clouds)
+  grid = pc.Grid(cloud, radius)
+  neigh = pc.Neighborhood(grid, radius)               # self neighborhood, sorted order
+  g_np = dict(sp=grid._sorted_points.cpu().numpy(), sb=grid._sorted_batch_ids.cpu().numpy(),
+              sk=grid._sorted_keys.cpu().numpy(), ds=grid.get_DS().cpu().numpy(),
+              nc=grid._num_cells.cpu().numpy(), smin=grid._scaled_aabb_min.cpu().numpy(),
+              ic=grid._inv_cell_sizes.cpu().numpy())
+  inv_r = np.repeat(F32(1) / F32(radius), 3)
+  inv_bw = np.repeat(F32(5.0), 3)
+  nb = neigh._neighbors.cpu().numpy(); rg = neigh._samples_neigh_ranges.cpu().numpy()
+  m = len(nb)
+  rows = []
+
+  def twice(fn):     # the second call reuses the harness' device buffers: kernels only
+    fn()
+    return fn()
+
+  _, ms = twice(lambda: ref.compute_keys(pts, bid, g_np["smin"], g_np["nc"], g_np["ic"]))
+  mine = ours(lambda: ops.compute_keys(cloud._points, cloud._batch_ids, grid._scaled_aabb_min,
+                                       grid._num_cells, grid._inv_cell_sizes), ("compute_keys",))
+  rows.append(("ComputeKeys", ms, mine))
+  _, ms = twice(lambda: ref.build_grid_ds(g_np["sk"], g_np["nc"], clouds))
+  mine = ours(lambda: ops.build_grid_ds(grid._sorted_keys, grid._num_cells, grid._num_cells_host,
+                                        clouds), ("build_grid_ds",))
+  rows.append(("BuildGridDs", ms, mine))
+  _, _, ms = twice(lambda: ref.find_neighbors(g_np["sp"], g_np["sb"], g_np["sp"], g_np["sk"],
+                                              g_np["ds"], g_np["nc"], g_np["smin"], g_np["ic"],
+                                              inv_r, capacity=m + 16))
+  mine = ours(lambda: pc.Neighborhood(grid, radius), ("find_neighbors", "scan_i32"))
+  rows.append(("FindNeighbors", ms, mine))
+  _, _, ms = twice(lambda: ref.compute_pdf(g_np["sp"], nb, rg, inv_bw, inv_r, 0))
+  mine = ours(lambda: ops.compute_pdf(grid._sorted_points, neigh._neighbors,
+                                      neigh._samples_neigh_ranges, t(inv_bw), t(inv_r), 0),
+              ("compute_pdf",))
+  rows.append(("ComputePdf", ms, mine))
+  basis = rng.standard_normal((m, k), dtype=F32)
+  feat = rng.standard_normal((n, cin), dtype=F32)
+  out, _, _, ms = twice(lambda: ref.basis_proj(basis, feat, nb, rg))
+  tb, tf = t(basis), t(feat)
+  mine = ours(lambda: ops.basis_proj(tb, tf, neigh._neighbors, neigh._samples_neigh_ranges),
+              ("basis_proj",))
+  rows.append(("BasisProj [%d,%d,%d]" % (n, cin, k), ms, mine))
+  _, _, _, ms = twice(lambda: ref.sampling(g_np["sp"], g_np["sb"], g_np["sk"], g_np["nc"], nb, rg, 0))
+  mine = ours(lambda: pc.sample(neigh, "poisson"), ("sampling", "scan_i32"))
+  rows.append(("Sampling (Poisson)", ms, mine))
+
+  print("%d clouds x %d points, radius %.3f, %d neighbor pairs" % (clouds, per, radius, m))
+  print("| op | reference kernels (ms) | this library (ms) | ratio |")
+  print("|---|---:|---:|---:|")
+  for name, r, o in rows:
+    print("| %s | %.3f | %.3f | %.1fx |" % (name, r, o, r / o if o > 0 else float("nan")))
+
+
+if __name__ == "__main__":
+  main()
