@@ -39,7 +39,8 @@ def mc_case(rng, c, k, cout, n_pts=3000, n_smp=700, radius=0.25, b=3):
 
 
 @pytest.mark.parametrize("c,k,cout", [(8, 16, 16), (128, 16, 256), (32, 8, 64), (64, 32, 128),
-                                      (3, 16, 32), (16, 64, 40)])
+                                      (3, 16, 32), (16, 64, 40), (256, 16, 64), (128, 32, 32),
+                                      (128, 64, 16), (384, 16, 32)])
 def test_mcconv_forward_backward(c, k, cout):
   rng = np.random.default_rng(c * 1000 + k + cout)
   nb_ref, nb, basis, feat, w = mc_case(rng, c, k, cout)
