@@ -46,6 +46,10 @@ def parse_args():
   ap.add_argument("--cpu-sample-clouds", type=int, default=1)
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--workload", default="mcconv", choices=["mcconv", "neighbors", "hierarchy"],
+                  help="mcconv: the headline step; neighbors: grid build + neighbor search + pdf "
+                       "on 16 surface clouds (radius 0.05); hierarchy: 4-level Poisson-disk and "
+                       "cell-average sampling of 8 x 100000 Gaussian-mixture points")
   return ap.parse_args()
 
 
@@ -376,12 +380,135 @@ def run_ours(args, rank, local_rank, world):
     dist.destroy_process_group()
 
 
+
+# ------------------------------------------------- secondary workloads -------
+
+SIDE_MODELS = {
+    # algorithmic bytes per launch: n points / samples, m neighbor pairs, s samples out
+    "compute_aabb": lambda n, m, s: n * 16 ,
+    "compute_keys": lambda n, m, s: n * 24,
+    "sort_radix": lambda n, m, s: n * 36,
+    "sort_gather": lambda n, m, s: n * 36,
+    "build_grid_ds": lambda n, m, s: n * 8,
+    "find_neighbors_count": lambda n, m, s: n * 36,
+    "find_neighbors_fill": lambda n, m, s: n * 36 + m * 8,
+    "compute_pdf": lambda n, m, s: n * 20 + m * 8,
+    "sampling_poisson_pass": lambda n, m, s: (n * 8 + m * 12) / 8.0,
+    "sampling_store_poisson": lambda n, m, s: n * 8 + s * 20,
+    "sampling_cell_average": lambda n, m, s: n * 20 + s * 16,
+}
+
+
+def run_side_workload(args):
+  """Grid / neighbor / pdf (surface clouds) or the sampling hierarchy (Gaussian
+  mixtures) on one GPU: per-kernel time and algorithmic GB/s against the HBM peak."""
+  import torch
+  from tensorflow_graphics_point_clouds_b200 import _lib, build, pc, synthetic
+  if not torch.cuda.is_available():
+    raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+  build.build()
+  dev = torch.device("cuda", 0)
+  peaks = measured_peaks()
+  if args.workload == "neighbors":
+    pts, bid = synthetic.surface_clouds(16, seed=1)
+    batch, radii = 16, [0.05]
+  else:
+    pts, bid = synthetic.gaussian_mixture_clouds(8, 100000, seed=3)
+    batch, radii = 8, [0.025, 0.05, 0.1, 0.2]
+  tp, tb = torch.from_numpy(pts).to(dev), torch.from_numpy(bid).to(dev)
+  sizes = []   # (n, m, s) per level, in launch order
+
+  def step(record):
+    cloud = pc.PointCloud(tp, tb, batch)
+    if args.workload == "neighbors":
+      grid = pc.Grid(cloud, radii[0])
+      neigh = pc.Neighborhood(grid, radii[0])
+      neigh.compute_pdf(bandwidth=0.2, mode=0)
+      if record:
+        sizes.append((tp.shape[0], neigh._neighbors.shape[0], 0))
+      return neigh._neighbors.shape[0]
+    pairs = 0
+    for mode in ("poisson", "average"):
+      cur = cloud
+      for r in radii:
+        grid = pc.Grid(cur, r)
+        neigh = pc.Neighborhood(grid, r)
+        nxt, _ = pc.sample(neigh, mode)
+        if record:
+          sizes.append((cur._points.shape[0], neigh._neighbors.shape[0], nxt._points.shape[0]))
+        pairs += neigh._neighbors.shape[0]
+        cur = nxt
+    return pairs
+
+  for _ in range(max(args.warmup, 3)):
+    step(False)
+  torch.cuda.synchronize()
+  pairs = step(True)
+  sampler = ClockSampler(0)
+  sampler.start()
+  _lib.profile_enable(True)
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    step(False)
+  e1.record()
+  torch.cuda.synchronize()
+  records = _lib.profile_collect()
+  _lib.profile_enable(False)
+  clocks = sampler.stop()
+  ms = e0.elapsed_time(e1) / args.steps
+  per_step = len(records) // args.steps
+  # attribute every launch to the level (point count, pair count) it worked on
+  agg = {}
+  counters = {}
+  for idx, (name, kms) in enumerate(records):
+    pos_in_step = counters.get(name, 0)
+    counters[name] = pos_in_step + 1
+    a = agg.setdefault(name, [0, 0.0, 0.0])
+    a[0] += 1; a[1] += kms
+    model = SIDE_MODELS.get(name)
+    if model is not None and sizes:
+      launches_per_step = sum(1 for n2, _ in records[:per_step] if n2 == name) or 1
+      k = pos_in_step % launches_per_step
+      per_level = 8 if name == "sampling_poisson_pass" else 1
+      if name in ("sampling_store_poisson",):
+        lvl = k                                   # Poisson levels come first
+      elif name == "sampling_cell_average":
+        lvl = len(radii) + k
+      else:
+        lvl = min(k // per_level, len(sizes) - 1)
+      n, m, so = sizes[min(lvl, len(sizes) - 1)]
+      a[2] += model(n, m, so)
+  kernels = {}
+  for name, (cnt, tot, bytes_) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+    entry = {"launches_per_step": cnt / args.steps, "ms_per_step": tot / args.steps}
+    if bytes_ > 0:
+      gbs = bytes_ / (tot * 1e-3) / 1e9
+      entry["algorithmic_gbs"] = gbs
+      entry["frac_of_hbm_peak"] = gbs / peaks["hbm_gbs"]
+    kernels[name] = entry
+  n_pts = tp.shape[0]
+  line = {
+      "metric": "neighbor_pairs_per_s", "value": pairs / (ms * 1e-3), "unit": "pairs/s",
+      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+      "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+      "config": {"workload": args.workload, "points": int(n_pts), "neighbor_pairs": int(pairs),
+                 "radii": radii, "levels": [list(map(int, x)) for x in sizes]},
+      "clocks": clocks, "kernels": kernels, "peak_hbm_gbs": peaks["hbm_gbs"],
+      "peak_source": peaks["source"],
+  }
+  print(json.dumps(line), flush=True)
+
+
 def main():
   args = parse_args()
   rank = int(os.environ.get("RANK", "0"))
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
-  if args.impl == "reference":
+  if args.workload != "mcconv":
+    if rank == 0:
+      run_side_workload(args)
+  elif args.impl == "reference":
     run_reference(args, rank, world)
   else:
     run_ours(args, rank, local_rank, world)

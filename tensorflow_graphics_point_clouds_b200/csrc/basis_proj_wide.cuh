@@ -241,6 +241,17 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
     if ((K >> (t + 1)) >= 1 && (lane & (1 << t))) kbase += K >> (t + 1);
   const int own_cnt = K >= 32 ? K / 32 : 1;
   const bool owner = K >= 32 || lane < K;
+  // The first butterfly steps (those that still move whole groups of 4 values)
+  // need no selects if every lane keeps its gradient tile and basis row in a
+  // lane-dependent order: register r holds basis function r ^ perm, where perm
+  // flips, for every such step, the half the lane has to give away.  Partners
+  // then always exchange registers [width, 2*width) and keep [0, width).
+  constexpr int kFreeSteps = (K == 8) ? 1 : (K == 16) ? 2 : (K == 32) ? 3 : 4;
+  int perm = 0;
+#pragma unroll
+  for (int t = 0; t < kFreeSteps; ++t)
+    if (lane & (1 << t)) perm += K >> (t + 1);
+  const int permq = perm >> 2;  // in units of 4 values (one 128-bit load)
   for (int64_t s = ((int64_t)blockIdx.x * kBpwThreads + threadIdx.x) >> 5; s < ns; s += warps) {
     const int a = s ? __ldg(ranges + s - 1) : 0;
     const int e = __ldg(ranges + s);
@@ -268,7 +279,7 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
               in_grads + s * (int64_t)C * K + (int64_t)(cbase + cc) * K);
 #pragma unroll
           for (int q = 0; q < K / 4; ++q) {
-            const ulonglong2 v = c_ok ? __ldg(src + q) : make_ulonglong2(0ull, 0ull);
+            const ulonglong2 v = c_ok ? __ldg(src + (q ^ permq)) : make_ulonglong2(0ull, 0ull);
             g[cc][2 * q] = v.x; g[cc][2 * q + 1] = v.y;
           }
         }
@@ -287,7 +298,7 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
           const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(wtile + it * K);
 #pragma unroll
           for (int q = 0; q < K / 4; ++q) {
-            const ulonglong2 v = wrow[q];
+            const ulonglong2 v = wrow[q ^ permq];
             w[2 * q] = v.x; w[2 * q + 1] = v.y;
           }
           // dfeat[nbr, c] += sum_k g[c,k] * basis[m,k]
@@ -323,12 +334,17 @@ basis_proj_grads_wide_kernel(int C, int64_t ns, const float* __restrict__ basis,
             unpack2(acc2, part[2 * kp], part[2 * kp + 1]);
           }
           // ... folded over the 32 lanes by a halving butterfly over xor distances
-          // 1, 2, 4, ...: lanes with the distance bit set keep the upper half
+          // 1, 2, 4, ...: the select-free steps first (see perm above), then the
+          // last steps, where lanes with the distance bit set keep the upper half
 #pragma unroll
           for (int t = 0; t < 5; ++t) {
             const int half = 1 << t;
             const int width = K >> (t + 1);
-            if (width >= 1) {
+            if (t < kFreeSteps) {
+#pragma unroll
+              for (int k = 0; k < K / 2; ++k)
+                if (k < width) part[k] += __shfl_xor_sync(0xffffffffu, part[k + width], half);
+            } else if (width >= 1) {
               const bool upper = (lane & half) != 0;
 #pragma unroll
               for (int k = 0; k < K / 2; ++k) {

@@ -70,7 +70,11 @@ __device__ __forceinline__ int2 candidate_range(int code, const int* cell, int b
 }
 
 // t_d = (s_d - p_d) * inv_r_d, d2 = fma chain from t_0*t_0, sqrtf(d2) < 1
-// (count_neighbors_kernels.cu.cc:84-85, math_helper.h:311-327).
+// (count_neighbors_kernels.cu.cc:84-85, math_helper.h:311-327).  The square
+// root is not evaluated: a correctly rounded sqrtf maps every float below 1
+// to a float below 1 (the largest, 1 - 2^-24, goes to 1 - 2^-24) and every
+// float >= 1 to a float >= 1, so `sqrtf(d2) < 1.0f` and `d2 < 1.0f` decide
+// identically, NaN included.
 template <int D>
 __device__ __forceinline__ bool within_radius(const float* s, const float* __restrict__ p,
                                               const float* inv_r) {
@@ -81,7 +85,7 @@ __device__ __forceinline__ bool within_radius(const float* s, const float* __res
     t = __fmul_rn(__fsub_rn(s[d], __ldg(p + d)), inv_r[d]);
     d2 = __fmaf_rn(t, t, d2);
   }
-  return __fsqrt_rn(d2) < 1.0f;
+  return d2 < 1.0f;
 }
 
 template <int D, bool FILL>

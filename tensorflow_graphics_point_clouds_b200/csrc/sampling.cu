@@ -17,6 +17,7 @@
 namespace tfgpc {
 
 constexpr int kSmpThreads = 256;
+constexpr int kCellBits = 4096;  // points of one cell tracked in the per-warp bit set
 
 struct SamplingWs {
   int32_t* flags;      // [n] 1 where a run of equal keys starts
@@ -68,6 +69,8 @@ poisson_pass_kernel(int pass, int64_t n, const int64_t* __restrict__ num_runs,
                     const int32_t* __restrict__ starts, const int64_t* __restrict__ keys,
                     const int32_t* __restrict__ num_cells, const int2* __restrict__ neigh,
                     const int32_t* __restrict__ ranges, int32_t* used) {
+  __shared__ uint32_t bits_all[(kSmpThreads / 32) * (kCellBits / 32)];
+  uint32_t* bits = bits_all + (threadIdx.x >> 5) * (kCellBits / 32);
   const int64_t runs = *num_runs;
   const int lane = lane_id();
   int nc[D];
@@ -86,6 +89,16 @@ poisson_pass_kernel(int pass, int64_t n, const int64_t* __restrict__ num_runs,
       mine = mine && ((c & 1) == ((pass >> d) & 1));
     }
     if (!mine) continue;
+    // Flags of points outside this cell cannot change during this pass (cells of
+    // equal parity are never neighbors), so they are read through the caches;
+    // the flags of the cell's own points are kept in a per-warp bit set in
+    // shared memory (cells of up to kCellBits points; larger cells fall back to
+    // uncached global reads), which takes the L2 round trip out of the
+    // point-after-point dependency chain.
+    const bool local = end - begin <= kCellBits;
+    if (local)
+      for (int i = lane; i < kCellBits / 32; i += 32) bits[i] = 0u;
+    __syncwarp();
     for (int q = begin; q < end; ++q) {
       const int a = q ? __ldg(ranges + q - 1) : 0;
       const int e = __ldg(ranges + q);
@@ -95,13 +108,19 @@ poisson_pass_kernel(int pass, int64_t n, const int64_t* __restrict__ num_runs,
         bool hit = false;
         if (m < e) {
           const int j = __ldg(&neigh[m].x);
-          // earlier points of this cell were marked by this warp a moment ago:
-          // read around L1
-          hit = (j >= 0 && j < n) && __ldcg(used + j) != 0;
+          if (j >= begin && j < end) {
+            hit = local ? ((bits[(j - begin) >> 5] >> ((j - begin) & 31)) & 1u) != 0u
+                        : __ldcg(used + j) != 0;
+          } else if (j >= 0 && j < n) {
+            hit = used[j] != 0;
+          }
         }
         taken_nb = __any_sync(0xffffffffu, hit);
       }
-      if (!taken_nb && lane == 0) __stcg(used + q, 1);
+      if (!taken_nb && lane == 0) {
+        __stcg(used + q, 1);
+        if (local) bits[(q - begin) >> 5] |= 1u << ((q - begin) & 31);
+      }
       __syncwarp();
     }
   }
