@@ -94,13 +94,13 @@ def measured_peaks():
 # Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) taken
 # from the ncu captures summarised under profiles/, scaled to this workload by
 # the units processed; None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {
-    # profiles/projection_and_gemm_kernels_16_clouds.md, scaled x2 (16 -> 32 clouds)
-    "basis_proj_split": 2 * (1.030125e9 + 2.100271e9),
-    "basis_proj_grads": 2 * (4.091760e9 + 1.135269e9),
-    "gemm_bf16x3_k_mn": 2 * (2.176671e9 + 0.255460e9),
-    "gemm_bf16x3_k_k": 2 * (2.150015e9 + 2.098627e9),
-    "gemm_bf16x3_mn_mn": 2 * (2.415946e9 + 0.004173e9),
+NCU_TRAFFIC_BYTES_PER_POINT = {
+    # profiles/projection_and_gemm_kernels_16_clouds.md: bytes of one launch / 262144 points
+    "basis_proj_split": (1.030125e9 + 2.100271e9) / 262144,
+    "basis_proj_grads": (4.091760e9 + 1.135269e9) / 262144,
+    "gemm_bf16x3_k_mn": (2.176671e9 + 0.255460e9) / 262144,
+    "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
+    "gemm_bf16x3_mn_mn": (2.415946e9 + 0.004173e9) / 262144,
 }
 
 
@@ -148,7 +148,7 @@ class ClockSampler:
     try:
       self.proc = subprocess.Popen(
           ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-           "--format=csv,noheader,nounits", "-lms", "100"],
+           "--format=csv,noheader,nounits", "-lms", "50"],
           stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
       self.thread = threading.Thread(target=self._read, daemon=True)
       self.thread.start()
@@ -285,14 +285,17 @@ def run_ours(args, rank, local_rank, world):
       dist.barrier()
       torch.cuda.synchronize()
 
+  # nvidia-smi needs a few hundred ms to deliver its first sample: start it
+  # before the warm-up so that it is sampling (under the same load) throughout
+  # the timed region
+  sampler = ClockSampler(local_rank)
+  sampler.start()
   for _ in range(max(args.warmup, 3)):
     step(dev_in)
   layer._op.check_status()
 
   # ---- device-resident timing
-  sampler = ClockSampler(local_rank)
   barrier()
-  sampler.start()
   _lib.profile_enable(True)
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   e0.record()
@@ -309,26 +312,62 @@ def run_ours(args, rank, local_rank, world):
   # ---- end to end: host buffers in, host buffers out, every step
   e2e = None
   if not args.no_e2e:
-    out_host = None
+    # Every step copies its inputs from pinned host memory and its results back
+    # to pinned host memory.  The copies run on two copy streams so that the
+    # upload of step i+1 and the download of step i-1 overlap the kernels of
+    # step i (two sets of device input buffers and of host output buffers).
     h2d = sum(v.numel() * v.element_size() for v in host.values())
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_bufs = [{k: torch.empty_like(v, device=dev) for k, v in host.items()} for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]   # step that used the buffer set has finished
+    ev_out = [torch.cuda.Event() for _ in range(2)]    # download into the host set has finished
+    out_host = [None, None]
     d2h = 0
 
-    def e2e_step():
-      nonlocal out_host, d2h
-      x = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-      res = step(x)
-      if out_host is None:
-        out_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
-        d2h = sum(r.numel() * r.element_size() for r in res)
-      for h, r in zip(out_host, res):
-        h.copy_(r, non_blocking=True)
+    def upload(i):
+      b = i % 2
+      with torch.cuda.stream(s_in):
+        s_in.wait_event(ev_free[b])
+        for k, v in host.items():
+          dev_bufs[b][k].copy_(v, non_blocking=True)
+        ev_in[b].record(s_in)
 
-    for _ in range(2):
-      e2e_step()
+    def run(i):
+      nonlocal d2h
+      b = i % 2
+      main.wait_event(ev_in[b])
+      res = step(dev_bufs[b])
+      ev_free[b].record(main)
+      done = torch.cuda.Event()
+      done.record(main)
+      if out_host[b] is None:
+        out_host[b] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        d2h = sum(r.numel() * r.element_size() for r in res)
+      with torch.cuda.stream(s_out):
+        s_out.wait_event(done)
+        s_out.wait_event(ev_out[b])
+        for h, r in zip(out_host[b], res):
+          r.record_stream(s_out)
+          h.copy_(r, non_blocking=True)
+        ev_out[b].record(s_out)
+
+    def e2e_loop(count):
+      upload(0)
+      for i in range(count):
+        if i + 1 < count:
+          upload(i + 1)
+        run(i)
+      main.wait_stream(s_out)
+
+    for b in range(2):
+      ev_free[b].record(main)
+      ev_out[b].record(main)
+    e2e_loop(2)
     barrier()
     e0.record()
-    for _ in range(args.steps):
-      e2e_step()
+    e2e_loop(args.steps)
     e1.record()
     barrier()
     e2e_ms = tdist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
@@ -354,7 +393,8 @@ def run_ours(args, rank, local_rank, world):
       achieved = amount / (avg_ms * 1e-3) / 1e12
       peak, runit = peaks["bf16_tflops"], "TFLOP/s"
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(top),
+                "frac": achieved / peak, "traffic": (NCU_TRAFFIC_BYTES_PER_POINT[top] * n
+                            if top in NCU_TRAFFIC_BYTES_PER_POINT else None),
                 "avg_launch_ms": avg_ms, "peak_source": peaks["source"],
                 "note": "tensor-bound kernels issue 3 bf16 passes per algorithmic flop"
                         if bound == "tensor" else "algorithmic bytes / launch time"}
