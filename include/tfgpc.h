@@ -135,6 +135,17 @@ int tfgpc_find_neighbors_fill(void* stream, int D, int64_t ns,
                               const int32_t* ranges, int64_t total,
                               int32_t* neigh_out);
 
+/* Neighbor ids in the unsorted point order: ids_out[m] = (sorted_indices[
+ * neighbors[m].x], neighbors[m].y), the gather + concat of
+ * pylib/pc/Neighborhood.py:246-250; optionally also the per-pair density
+ * pdf_out[m] = pdf_by_original[that original id] (:287).  Pass both density
+ * pointers or neither. */
+int tfgpc_original_neighbor_ids(void* stream, int64_t M,
+                                const int32_t* neighbors, int64_t n,
+                                const int32_t* sorted_indices,
+                                const float* pdf_by_original, int32_t* ids_out,
+                                float* pdf_out);
+
 /* ---- FindNeighbors count pass with built-in scratch ------------------------
  * No counterpart in the reference.  Same inputs, outputs and blocking
  * behaviour as tfgpc_find_neighbors_count, but without the ws / ws_bytes

@@ -236,6 +236,46 @@ extern "C" int tfgpc_find_neighbors_fill(
   return TFGPC_OK;
 }
 
+// ---- neighbor ids in the unsorted point order, per-pair densities -----------------
+//
+// pylib maps the sorted neighbor ids back to the original point order with a
+// gather and a concat (pylib/pc/Neighborhood.py:246-250) and gathers the
+// per-point density per neighbor pair (:287); both are one pass over the pairs.
+namespace tfgpc {
+__global__ void original_ids_kernel(int64_t m, const int2* __restrict__ neigh,
+                                    const int32_t* __restrict__ sorted_indices,
+                                    const float* __restrict__ pdf_by_original, int64_t n,
+                                    int2* __restrict__ out_ids, float* __restrict__ out_pdf) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < m;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int2 nb = __ldg(neigh + i);
+    int orig = 0;
+    if (nb.x >= 0 && nb.x < n) orig = __ldg(sorted_indices + nb.x);
+    out_ids[i] = make_int2(orig, nb.y);
+    if (out_pdf) out_pdf[i] = __ldg(pdf_by_original + orig);
+  }
+}
+}  // namespace tfgpc
+
+extern "C" int tfgpc_original_neighbor_ids(void* stream, int64_t M, const int32_t* neighbors,
+                                           int64_t n, const int32_t* sorted_indices,
+                                           const float* pdf_by_original, int32_t* ids_out,
+                                           float* pdf_out) {
+  TFGPC_REQUIRE(M >= 0 && M <= (int64_t)INT32_MAX && n >= 0 && n < (int64_t)INT32_MAX,
+                "original_neighbor_ids expects 0 <= M, n < 2^31");
+  if (M == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(neighbors && sorted_indices && ids_out, "original_neighbor_ids got a null pointer");
+  TFGPC_REQUIRE((pdf_out == nullptr) == (pdf_by_original == nullptr),
+                "original_neighbor_ids expects both density pointers or none");
+  cudaStream_t st = (cudaStream_t)stream;
+  ProfScope prof(st, "original_neighbor_ids");
+  unsigned grid = min(blocks_for(M, 256), (unsigned)(sm_count() * 32));
+  original_ids_kernel<<<grid, 256, 0, st>>>(M, (const int2*)neighbors, sorted_indices,
+                                            pdf_by_original, n, (int2*)ids_out, pdf_out);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
 // ---- FindNeighbors count pass without caller scratch ---------------------------
 //
 // Scratch of tfgpc_find_neighbors_count_static: the tile sums of the device-wide

@@ -147,6 +147,23 @@ def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, 
   return ranges, neigh
 
 
+def original_neighbor_ids(neighbors, sorted_indices, pdf_by_original=None):
+  """(sorted_indices[neighbors[:, 0]], neighbors[:, 1]) and, optionally, the
+  density of every pair's neighbor point (tfgpc_original_neighbor_ids)."""
+  neighbors, sorted_indices = _i32(neighbors), _i32(sorted_indices)
+  _dev_check(neighbors, sorted_indices)
+  m = neighbors.shape[0]
+  ids = torch.empty((m, 2), dtype=torch.int32, device=neighbors.device)
+  pdf = None
+  if pdf_by_original is not None:
+    pdf_by_original = _f32(pdf_by_original)
+    pdf = torch.empty(m, dtype=torch.float32, device=neighbors.device)
+  _lib.check(_lib.lib().tfgpc_original_neighbor_ids(
+      _stream(), c_i64(m), ptr(neighbors), c_i64(sorted_indices.shape[0]), ptr(sorted_indices),
+      ptr(pdf_by_original), ptr(ids), ptr(pdf)))
+  return ids, pdf
+
+
 def _pdf_args(points, neighbors, sample_neigh_indices, inv_bandwidth, inv_radii, mode):
   points = _f32(points)
   neighbors, ranges = _i32(neighbors), _i32(sample_neigh_indices)

@@ -113,8 +113,7 @@ class Neighborhood:
     """Neighbor ids mapped back to the unsorted point order
     (Neighborhood.py:246-250), built on first use."""
     if self._orig_ids is None:
-      orig = self._grid._sorted_indices[self._neighbors[:, 0].to(torch.int64)]
-      self._orig_ids = torch.stack([orig, self._neighbors[:, 1]], dim=1).contiguous()
+      self._orig_ids, _ = ops.original_neighbor_ids(self._neighbors, self._grid._sorted_indices)
     return self._orig_ids
 
   def _samples_are_grid_points(self):
@@ -141,7 +140,8 @@ class Neighborhood:
           self._samples_neigh_ranges, inv_bw, inv_r, mode)
       # sample s is point s of the unsorted cloud: index by the neighbors' original ids
       self._point_pdf = sample_pdf[g._sorted_indices.to(torch.int64)]
-      self._pdf = sample_pdf[self._original_neigh_ids[:, 0].to(torch.int64)]
+      self._orig_ids, self._pdf = ops.original_neighbor_ids(self._neighbors, g._sorted_indices,
+                                                            sample_pdf)
     else:
       nb = Neighborhood(g, self._radii)
       self._point_pdf = ops.compute_pdf_with_pt_grads(
