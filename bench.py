@@ -110,9 +110,10 @@ def kernel_model(name, sizes):
   n, m = sizes["n"], sizes["m"]
   c, k, co = sizes["cin"], sizes["k"], sizes["cout"]
   ck = c * k
-  if name == "basis_proj_split":
+  if name in ("basis_proj_split", "basis_proj_split_mma"):
+    # basis rows + neighbor ids, every feature row once, ranges, the projection
     return "hbm", m * (4 * k + 8) + n * 4 * c + n * 4 + n * ck * 4
-  if name == "basis_proj_grads":
+  if name in ("basis_proj_grads", "basis_proj_grads_mma"):
     return "hbm", n * ck * 4 + m * (4 * k + 8) + n * 4 * c + n * 4 + m * 4 * k + n * 4 * c
   if name == "gemm_bf16x3_k_mn":      # out = X W
     return "tensor", 2.0 * n * ck * co

@@ -267,11 +267,14 @@ int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
  * Backward: out_grads [ns, Cout] -> dbasis_out [M, K], dfeat_out [n_in, C],
  * dweights_out [C*K, Cout] (all overwritten).  x_in_workspace != 0 tells it
  * that `ws` still holds the projection written by the forward call for the
- * same inputs (ws sized for backward); otherwise it is recomputed.
+ * same inputs (ws sized for backward); otherwise it is recomputed.  The
+ * workspace size depends on n_in as well: for K in {16, 32, 64} and C a multiple
+ * of 16 the projection and its gradients run on warp-level tensor-core MMAs
+ * over a bf16 hi/mid copy of the features kept in the workspace.
  * tfgpc_mcconv_status blocks on the stream and returns TFGPC_ETIMEOUT if a
  * bounded wait inside one of the GEMM kernels that used `ws` ran out. */
 size_t tfgpc_mcconv_workspace_bytes(int K, int C, int Cout, int64_t ns,
-                                    int backward);
+                                    int64_t n_in, int backward);
 int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_t ns,
                          int64_t n_in, int64_t M, const float* basis,
                          const float* features, const int32_t* neighbors,

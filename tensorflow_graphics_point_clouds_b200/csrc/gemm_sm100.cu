@@ -205,6 +205,9 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
       tc_fence_after();
       const int row0 = m * kBM + quarter * 32;
       for (int c0 = 0; c0 < bn; c0 += 32, ++box_iter) {
+        // boxes beyond the last column hold nothing to store; skipping them also
+        // keeps the staging buffer of a store still in flight from being reused
+        if ((int64_t)n * bn + c0 >= n_total) break;
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                (uint32_t)(buf * kBNMax + c0);

@@ -16,6 +16,15 @@ namespace tfgpc {
 int basis_proj_split(cudaStream_t st, int K, int C, int64_t ns, const float* basis,
                      const float* feat, const int32_t* neigh, const int32_t* ranges,
                      __nv_bfloat16* hi, __nv_bfloat16* mid);
+// basis_proj_mma.cu: the projection on warp-level tensor-core MMAs
+bool basis_proj_mma_supported(int K, int C);
+int split_features(cudaStream_t st, const float* feat, int64_t n, int C, __nv_bfloat16* fs);
+int basis_proj_mma_split(cudaStream_t st, int K, int C, int64_t ns, const float* basis,
+                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                         __nv_bfloat16* hi, __nv_bfloat16* mid);
+int basis_proj_grads_mma(cudaStream_t st, int K, int C, int64_t ns, int64_t M, const float* basis,
+                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                         const float* in_grads, float* dbasis, float* dfeat);
 
 namespace {
 
@@ -26,11 +35,12 @@ struct McWs {
   __nv_bfloat16 *g_hi, *g_mid;      // [ns, Cout]   (backward)
   float* dx;                        // [ns, C*K]    (backward)
   float* dw_part;                   // [splits, C*K, Cout] (backward)
+  __nv_bfloat16* fs;                // [n_in, 2, C] split features (tensor-core projection)
   int dw_splits;
   size_t bytes;
 };
 
-McWs carve(void* ws, int K, int C, int Cout, int64_t ns, bool backward) {
+McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool backward) {
   McWs w;
   char* p = (char*)ws;
   auto take = [&](size_t b) { char* r = p; p += align_up(b, 1024); return r; };
@@ -40,6 +50,10 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, bool backward) {
   w.x_mid = (__nv_bfloat16*)take((size_t)ns * ck * 2);
   w.w_hi = (__nv_bfloat16*)take(ck * Cout * 2);
   w.w_mid = (__nv_bfloat16*)take(ck * Cout * 2);
+  // ahead of the backward-only buffers, so that a forward and a backward carve
+  // of the same workspace agree on where it lies
+  w.fs = nullptr;
+  if (basis_proj_mma_supported(K, C)) w.fs = (__nv_bfloat16*)take((size_t)n_in * C * 4);
   w.dw_splits = 1;
   w.g_hi = w.g_mid = nullptr; w.dx = w.dw_part = nullptr;
   if (backward) {
@@ -69,9 +83,23 @@ int check_mc_args(const char* op, int K, int C, int Cout, int64_t ns, int64_t n_
 
 using namespace tfgpc;
 
-extern "C" size_t tfgpc_mcconv_workspace_bytes(int K, int C, int Cout, int64_t ns, int backward) {
-  if (K <= 0 || C <= 0 || Cout <= 0 || ns < 0) return 0;
-  return carve(nullptr, K, C, Cout, ns, backward != 0).bytes + 1024;
+extern "C" size_t tfgpc_mcconv_workspace_bytes(int K, int C, int Cout, int64_t ns, int64_t n_in,
+                                               int backward) {
+  if (K <= 0 || C <= 0 || Cout <= 0 || ns < 0 || n_in < 0) return 0;
+  return carve(nullptr, K, C, Cout, ns, n_in, backward != 0).bytes + 1024;
+}
+
+// The projection, written as the GEMM's bf16 operand pair: on tensor-core MMAs
+// where the shape allows it, else on the SIMT kernels.
+static int project(cudaStream_t st, int K, int C, int64_t ns, int64_t n_in, const float* basis,
+                   const float* features, const int32_t* neighbors, const int32_t* ranges,
+                   const McWs& w) {
+  if (w.fs && (uintptr_t)features % 16 == 0) {
+    int rc = split_features(st, features, n_in, C, w.fs);
+    if (rc) return rc;
+    return basis_proj_mma_split(st, K, C, ns, basis, w.fs, neighbors, ranges, w.x_hi, w.x_mid);
+  }
+  return basis_proj_split(st, K, C, ns, basis, features, neighbors, ranges, w.x_hi, w.x_mid);
 }
 
 extern "C" int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in,
@@ -85,14 +113,14 @@ extern "C" int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_
                 "MCConvForward got a null pointer");
   TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)ws % 256 == 0,
                 "MCConvForward expects 16-byte aligned buffers and a 256-byte aligned workspace");
-  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0))
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 0))
     return fail(TFGPC_ENOMEM, "MCConvForward workspace too small: %zu < %zu", ws_bytes,
-                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 0));
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 0));
   cudaStream_t st = (cudaStream_t)stream;
-  McWs w = carve(ws, K, C, Cout, ns, false);
+  McWs w = carve(ws, K, C, Cout, ns, n_in, false);
   const int64_t ck = (int64_t)C * K;
   TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
-  rc = basis_proj_split(st, K, C, ns, basis, features, neighbors, ranges, w.x_hi, w.x_mid);
+  rc = project(st, K, C, ns, n_in, basis, features, neighbors, ranges, w);
   if (rc) return rc;
   rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
   if (rc) return rc;
@@ -124,13 +152,13 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)out_grads % 16 == 0 &&
                 (uintptr_t)ws % 256 == 0,
                 "MCConvBackward expects 16-byte aligned buffers and a 256-byte aligned workspace");
-  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1))
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1))
     return fail(TFGPC_ENOMEM, "MCConvBackward workspace too small: %zu < %zu", ws_bytes,
-                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, 1));
-  McWs w = carve(ws, K, C, Cout, ns, true);
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1));
+  McWs w = carve(ws, K, C, Cout, ns, n_in, true);
   if (!x_in_workspace) {
     TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
-    rc = basis_proj_split(st, K, C, ns, basis, features, neighbors, ranges, w.x_hi, w.x_mid);
+    rc = project(st, K, C, ns, n_in, basis, features, neighbors, ranges, w);
     if (rc) return rc;
     rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
     if (rc) return rc;
@@ -142,8 +170,15 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   GemmOperand w_k{w.w_hi, w.w_mid, (int64_t)Cout, Major::K};
   rc = gemm_bf16x3(st, ns, ck, Cout, g_k, w_k, w.dx, ck, 1, 0, w.err);
   if (rc) return rc;
-  rc = tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges, w.dx,
-                              dbasis_out, dfeat_out);
+  if (w.fs && (uintptr_t)features % 16 == 0 && (uintptr_t)dbasis_out % 16 == 0 &&
+      (uintptr_t)dfeat_out % 16 == 0) {
+    TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+    rc = basis_proj_grads_mma(st, K, C, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
+                              dfeat_out);
+  } else {
+    rc = tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges,
+                                w.dx, dbasis_out, dfeat_out);
+  }
   if (rc) return rc;
   // dW[C*K, Cout] = X^T * dOut: both operands have the reduction (sample) index
   // as their row index, i.e. they are MN-major

@@ -38,20 +38,34 @@ def matmul_f32(a, b, a_transposed=False, b_transposed=False):
 
 class ProjectionGemm:
   """Holds the workspace of one (K, C, Cout, Ns) problem and runs the fused
-  forward / backward entry points on it."""
+  forward / backward entry points on it.  The workspace also depends on the
+  number of input points; it is allocated on first use (or up front when
+  `n_in` is given) and grown if a later call brings more points."""
 
-  def __init__(self, k, c, cout, ns, device, backward=True):
+  def __init__(self, k, c, cout, ns, device, backward=True, n_in=None):
     self.k, self.c, self.cout, self.ns = int(k), int(c), int(cout), int(ns)
     self.backward_ws = bool(backward)
+    self.device = device
+    self.n_in, self.nbytes, self.ws = -1, 0, None
+    self._x_valid = False
+    if n_in is not None:
+      self._ensure_workspace(int(n_in))
+
+  def _ensure_workspace(self, n_in):
+    if self.ws is not None and n_in <= self.n_in:
+      return
+    self.n_in = n_in
     self.nbytes = _lib.lib().tfgpc_mcconv_workspace_bytes(
-        c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns), c_int(int(backward)))
-    self.ws = _workspace(self.nbytes, device)
+        c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns), c_i64(n_in),
+        c_int(int(self.backward_ws)))
+    self.ws = _workspace(self.nbytes, self.device)
     self._x_valid = False
 
   def forward(self, basis, features, neighbors, ranges, weights):
     basis, features, weights = _f32(basis), _f32(features), _f32(weights)
     neighbors, ranges = _i32(neighbors), _i32(ranges)
     out = torch.empty((self.ns, self.cout), dtype=torch.float32, device=basis.device)
+    self._ensure_workspace(features.shape[0])
     _lib.check(_lib.lib().tfgpc_mcconv_forward(
         _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
         c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),
@@ -67,6 +81,7 @@ class ProjectionGemm:
     dbasis = torch.empty_like(basis)
     dfeat = torch.empty_like(features)
     dw = torch.empty_like(weights)
+    self._ensure_workspace(features.shape[0])
     _lib.check(_lib.lib().tfgpc_mcconv_backward(
         _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
         c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),

@@ -14,7 +14,8 @@ F32 = np.float32
 
 @pytest.mark.parametrize("at,bt", [(False, True), (False, False), (True, False), (True, True)])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (304, 64, 192), (1000, 256, 2048),
-                                   (256, 2048, 256), (2048, 256, 5000 // 8 * 8), (64, 16, 128)])
+                                   (256, 2048, 256), (2048, 256, 5000 // 8 * 8), (64, 16, 128),
+                                   (19144, 384, 200)])
 def test_matmul_f32_layouts(at, bt, m, n, k):
   rng = np.random.default_rng(m + n + k)
   a = rng.normal(size=(m, k)).astype(F32)
