@@ -35,4 +35,14 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bflo
   mid = __float2bfloat16_rn(x - __bfloat162float(hi));
 }
 
+// The same split for two values at once: packed bf16 pairs of the hi and mid
+// terms (x in the low half).
+__device__ __forceinline__ void split2_bf16(float x, float y, uint32_t& hi, uint32_t& mid) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  const float hx = __uint_as_float(hi << 16), hy = __uint_as_float(hi & 0xffff0000u);
+  const __nv_bfloat162 m = __floats2bfloat162_rn(x - hx, y - hy);
+  mid = *reinterpret_cast<const uint32_t*>(&m);
+}
+
 }  // namespace tfgpc

@@ -79,13 +79,8 @@ __device__ __forceinline__ void mma3(float* d, const uint32_t* a_hi, const uint3
   mma16816(d, a_hi, bh0, bh1);
 }
 
-// (x, y) -> packed bf16 pairs of the hi and mid terms (x in the low half)
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& mid) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
-  hi = *reinterpret_cast<const uint32_t*>(&h);
-  const float hx = __uint_as_float(hi << 16), hy = __uint_as_float(hi & 0xffff0000u);
-  const __nv_bfloat162 m = __floats2bfloat162_rn(x - hx, y - hy);
-  mid = *reinterpret_cast<const uint32_t*>(&m);
+  split2_bf16(x, y, hi, mid);
 }
 
 // 16-byte asynchronous copy; copies nothing and writes zeros when !valid

@@ -39,6 +39,13 @@ constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kOutStageBytes +
 
 using namespace tc;
 
+// One 32-byte store (sm_100: 256-bit vector access to global memory).
+__device__ __forceinline__ void st_global_256(void* p, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y),
+                 "r"(hi.z), "r"(hi.w) : "memory");
+}
+
 struct TileSchedule {
   int m_tiles, n_tiles, k_splits;
   int k_blocks;         // ring slots over the whole reduction
@@ -54,14 +61,19 @@ struct Barriers {
   int abort_flag;
 };
 
-template <bool A_MN, bool B_MN>
+// OUT = 0: C as fp32 through TMA stores.  OUT = 1: C is the gradient of a
+// [rows, channels, 16] projection and is written as the bf16 hi/mid operand
+// image the tensor-core gradient kernel loads with one bulk copy per group of
+// four rows (basis_proj_grads_tc.cu describes the layout).
+template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
                    const __grid_constant__ CUtensorMap tm_a_mid,
                    const __grid_constant__ CUtensorMap tm_b_hi,
                    const __grid_constant__ CUtensorMap tm_b_mid,
                    const __grid_constant__ CUtensorMap tm_c, int64_t m_total, int64_t n_total,
-                   int bn, uint32_t idesc, TileSchedule sch, int* err_flag) {
+                   int bn, uint32_t idesc, TileSchedule sch, int* err_flag, uint8_t* image,
+                   int image_channels) {
   extern __shared__ uint8_t smem_raw[];
   // the swizzled tiles need 1024-byte alignment
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -205,13 +217,46 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
       tc_fence_after();
       const int row0 = m * kBM + quarter * 32;
       for (int c0 = 0; c0 < bn; c0 += 32, ++box_iter) {
-        // boxes beyond the last column hold nothing to store; skipping them also
-        // keeps the staging buffer of a store still in flight from being reused
-        if ((int64_t)n * bn + c0 >= n_total) break;
+        // Boxes beyond the last column or row hold nothing to store.  They must
+        // not touch the staging buffers either: the wait below only covers the
+        // buffer's previous store if every box written here also issues one.
+        if ((int64_t)n * bn + c0 >= n_total || row0 >= m_total) break;
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                (uint32_t)(buf * kBNMax + c0);
         tmem_ld_32x32(taddr, r);
+        if (OUT == 1) {
+          // this thread holds 2 channels x 16 basis functions of row `row`
+          const int64_t row = (int64_t)row0 + lane;
+          if (row < m_total && !*abort_flag) {
+            const int64_t part = (int64_t)image_channels * 128;   // bytes of the hi (or mid) rows
+            uint8_t* group = image + (row >> 2) * (2 * part);
+            const int sl = (int)(row & 3);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int ch = (n * bn + c0) / 16 + u;
+              // The row's two chunks (k 0-7, k 8-15) of this channel share one
+              // 32-byte sector, in swapped order when the channel is odd: one
+              // 256-bit store per part, and four lanes fill a 128-byte line.
+              uint4 hv[2], mv[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int b = 16 * u + 8 * h;
+                split2_bf16(__uint_as_float(r[b]), __uint_as_float(r[b + 1]), hv[h].x, mv[h].x);
+                split2_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]), hv[h].y, mv[h].y);
+                split2_bf16(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5]), hv[h].z, mv[h].z);
+                split2_bf16(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]), hv[h].w, mv[h].w);
+              }
+              const bool swap = (ch & 1) != 0;
+              const uint4 h_lo = swap ? hv[1] : hv[0], h_hi = swap ? hv[0] : hv[1];
+              const uint4 m_lo = swap ? mv[1] : mv[0], m_hi = swap ? mv[0] : mv[1];
+              uint8_t* dst = group + (int64_t)ch * 128 + (((2 * sl) ^ (ch & 6)) << 4);
+              st_global_256(dst, h_lo, h_hi);
+              st_global_256(dst + part, m_lo, m_hi);
+            }
+          }
+          continue;
+        }
         uint8_t* box = my_stage + (size_t)(box_iter & 1) * kOutBoxBytes;
         if (lane == 0) tma_store_wait_read<1>();  // the store that last used this box has read it
         __syncwarp();
@@ -313,18 +358,20 @@ uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
   return d;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int OUT = 0>
 int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int bn,
-           TileSchedule sch, int* err_flag) {
-  auto kern = gemm_bf16x3_kernel<A_MN, B_MN>;
+           TileSchedule sch, int* err_flag, uint8_t* image = nullptr, int image_channels = 0) {
+  auto kern = gemm_bf16x3_kernel<A_MN, B_MN, OUT>;
   TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  ProfScope prof(st, A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
-                          : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
+  ProfScope prof(st, OUT == 1 ? "gemm_bf16x3_k_k_image"
+                              : A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
+                                     : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
-                                           make_idesc(kBM, bn, A_MN, B_MN), sch, err_flag);
+                                           make_idesc(kBM, bn, A_MN, B_MN), sch, err_flag, image,
+                                           image_channels);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -383,6 +430,31 @@ int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K) {
   if (splits < 1) splits = 1;
   if (splits > k_blocks) splits = k_blocks > 0 ? k_blocks : 1;
   return (int)splits;
+}
+
+int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t K,
+                           const GemmOperand& a, const GemmOperand& b, void* image,
+                           int* err_flag) {
+  const int64_t N = (int64_t)channels * 16;
+  TFGPC_REQUIRE(M > 0 && channels > 0 && K > 0 && M < (int64_t)INT32_MAX && K < (int64_t)INT32_MAX,
+                "GEMM expects positive sizes below 2^31");
+  TFGPC_REQUIRE(a.major == Major::K && b.major == Major::K && channels % 2 == 0 &&
+                (uintptr_t)image % 16 == 0, "gradient-image GEMM expects K-major operands");
+  int bn = (int)(N < kBNMax ? N : kBNMax);
+  bn = (bn + 31) / 32 * 32;
+  CUtensorMap maps[5] = {};
+  int rc;
+  if ((rc = make_map(&maps[0], a.hi, K, M, a.ld, kBK, kBM))) return rc;
+  if ((rc = make_map(&maps[1], a.mid, K, M, a.ld, kBK, kBM))) return rc;
+  if ((rc = make_map(&maps[2], b.hi, K, N, b.ld, kBK, bn))) return rc;
+  if ((rc = make_map(&maps[3], b.mid, K, N, b.ld, kBK, bn))) return rc;
+  TileSchedule sch;
+  sch.m_tiles = (int)((M + kBM - 1) / kBM);
+  sch.n_tiles = (int)((N + bn - 1) / bn);
+  sch.k_blocks = (int)((K + kBK - 1) / kBK);
+  sch.k_splits = 1;
+  sch.k_blocks_per_split = sch.k_blocks;
+  return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels);
 }
 
 int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,

@@ -26,6 +26,12 @@ int basis_proj_grads_mma(cudaStream_t st, int K, int C, int64_t ns, int64_t M, c
                          const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
                          const float* in_grads, float* dbasis, float* dfeat);
 
+// basis_proj_grads_tc.cu: the gradients on tcgen05 tensor cores
+bool basis_proj_grads_tc_supported(int K, int C);
+int basis_proj_grads_tc(cudaStream_t st, int64_t ns, int64_t M, const float* basis,
+                        const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                        const void* image, float* dbasis, float* dfeat, int* err_flag);
+
 namespace {
 
 struct McWs {
@@ -59,7 +65,9 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
-    w.dx = (float*)take((size_t)ns * ck * 4);
+    // rounded up to whole groups of four samples (operand image of the
+    // tensor-core gradient kernel)
+    w.dx = (float*)take((size_t)((ns + 3) / 4 * 4) * ck * 4);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
     w.dw_part = (float*)take((size_t)w.dw_splits * ck * Cout * 4);
   }
@@ -168,16 +176,31 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   // dX[ns, C*K] = dOut[ns, Cout] * W^T: B rows are W's rows, reduction over Cout
   GemmOperand g_k{w.g_hi, w.g_mid, (int64_t)Cout, Major::K};
   GemmOperand w_k{w.w_hi, w.w_mid, (int64_t)Cout, Major::K};
-  rc = gemm_bf16x3(st, ns, ck, Cout, g_k, w_k, w.dx, ck, 1, 0, w.err);
-  if (rc) return rc;
-  if (w.fs && (uintptr_t)features % 16 == 0 && (uintptr_t)dbasis_out % 16 == 0 &&
-      (uintptr_t)dfeat_out % 16 == 0) {
+  const bool fs_ok = w.fs && (uintptr_t)features % 16 == 0 && (uintptr_t)dbasis_out % 16 == 0 &&
+                     (uintptr_t)dfeat_out % 16 == 0;
+  if (fs_ok && basis_proj_grads_tc_supported(K, C)) {
+    // dX goes straight into the operand image of the tcgen05 gradient kernel
+    if (ns % 4 != 0) {
+      // columns of the samples that do not exist must read as finite values
+      char* last = (char*)w.dx + (size_t)(ns / 4) * 4 * ck * 4;
+      TFGPC_CUDA(cudaMemsetAsync(last, 0, (size_t)4 * ck * 4, st));
+    }
+    rc = gemm_bf16x3_grad_image(st, ns, C, Cout, g_k, w_k, w.dx, w.err);
+    if (rc) return rc;
     TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
-    rc = basis_proj_grads_mma(st, K, C, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
-                              dfeat_out);
+    rc = basis_proj_grads_tc(st, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
+                             dfeat_out, w.err);
   } else {
-    rc = tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges,
-                                w.dx, dbasis_out, dfeat_out);
+    rc = gemm_bf16x3(st, ns, ck, Cout, g_k, w_k, w.dx, ck, 1, 0, w.err);
+    if (rc) return rc;
+    if (fs_ok) {
+      TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+      rc = basis_proj_grads_mma(st, K, C, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
+                                dfeat_out);
+    } else {
+      rc = tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges,
+                                  w.dx, dbasis_out, dfeat_out);
+    }
   }
   if (rc) return rc;
   // dW[C*K, Cout] = X^T * dOut: both operands have the reduction (sample) index

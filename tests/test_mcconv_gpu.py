@@ -62,6 +62,32 @@ def test_mcconv_forward_backward(c, k, cout):
     close(df.cpu().numpy(), ref_df)
 
 
+@pytest.mark.parametrize("n_pts,n_smp,radius", [(3000, 701, 0.25), (3000, 702, 0.45),
+                                                (20000, 5003, 0.12), (500, 3, 0.5),
+                                                (3000, 700, 0.08), (40, 5, 0.9)])
+def test_mcconv_wide_layer_ragged_shapes(n_pts, n_smp, radius):
+  """C = 128, K = 16 (the tensor-core projection kernels) on sample counts that
+  are not multiples of four, samples with more pairs than one MMA block holds,
+  samples without neighbors, and more sample groups than the GPU has SMs."""
+  c, k, cout = 128, 16, 64
+  rng = np.random.default_rng(n_pts + n_smp)
+  nb_ref, nb, basis, feat, w = mc_case(rng, c, k, cout, n_pts=n_pts, n_smp=n_smp, radius=radius)
+  ref_out, ref_x = pr.mcconv_forward(feat, basis, nb_ref, w)
+  ns = len(nb_ref.ranges)
+  op = mcconv.ProjectionGemm(k, c, cout, ns, "cuda", backward=True)
+  out = op.forward(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges, t(w[0]))
+  op.check_status()
+  close(out.cpu().numpy(), ref_out)
+  d_out = rng.normal(size=ref_out.shape).astype(F32)
+  ref_dw, ref_db, ref_df, _ = pr.mcconv_backward(feat, basis, nb_ref, w, ref_x, d_out)
+  db, df, dw = op.backward(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges,
+                           t(w[0]), t(d_out))
+  op.check_status()
+  close(dw.cpu().numpy(), ref_dw[0])
+  close(db.cpu().numpy(), ref_db)
+  close(df.cpu().numpy(), ref_df)
+
+
 def test_dense_final_weights_matches_reference_layout():
   rng = np.random.default_rng(5)
   cin, g, h, co = 8, 4, 8, 16
