@@ -34,19 +34,15 @@
 // coalesced reductions.
 // Every mbarrier wait is bounded; a wait that runs out sets the error flag and
 // the kernel drains and frees its tensor memory.
-#include "basis_proj.cuh"
-#include "tc_common.cuh"
+#include "basis_proj_tc.cuh"
 
 namespace tfgpc {
 
 using namespace tc;
+using namespace bptc;
 
 namespace {
 
-constexpr int kC = 128;
-constexpr int kK = 16;
-constexpr int kGroup = 4;              // samples per tile
-constexpr int kRows = 128;             // pairs per MMA block
 constexpr int kProdWarps = 8;
 constexpr int kMmaWarp = 8;            // issues product (1); warp 9 issues product (2)
 constexpr int kDxWarp = 10;
@@ -69,74 +65,6 @@ struct Barriers {
   uint32_t tmem_base;
   int abort_flag;
 };
-
-// Pair range of a group of four samples and the ends of its first three.
-struct Tile {
-  int pa, e0, e1, e2, pe;
-  __device__ __forceinline__ int blocks() const { return (pe - pa + kRows - 1) / kRows; }
-  __device__ __forceinline__ int local_sample(int m) const {
-    return (m >= e0) + (m >= e1) + (m >= e2);
-  }
-};
-
-__device__ __forceinline__ Tile load_tile(const int32_t* __restrict__ ranges, int64_t ns, int64_t g) {
-  Tile t;
-  const int64_t s0 = g * kGroup;
-  if (s0 >= ns) { t.pa = t.e0 = t.e1 = t.e2 = t.pe = 0; return t; }
-  t.pa = s0 > 0 ? __ldg(ranges + s0 - 1) : 0;
-  t.e0 = __ldg(ranges + s0);
-  t.e1 = __ldg(ranges + min(s0 + 1, ns - 1));
-  t.e2 = __ldg(ranges + min(s0 + 2, ns - 1));
-  t.pe = __ldg(ranges + min(s0 + 3, ns - 1));
-  return t;
-}
-
-// Walk over the blocks (tile, 128-row block) of this CTA, with the next tile's
-// ranges already on their way.
-struct ItemWalk {
-  const int32_t* ranges;
-  int64_t ns, groups, g;
-  Tile t, tn;
-  int b;
-  bool valid;
-  __device__ __forceinline__ void settle() {
-    while (g < groups && b >= t.blocks()) {
-      g += gridDim.x;
-      t = tn;
-      tn = load_tile(ranges, ns, g + gridDim.x);
-      b = 0;
-    }
-    valid = g < groups;
-  }
-  __device__ __forceinline__ void init(const int32_t* r, int64_t n, int64_t gr) {
-    ranges = r; ns = n; groups = gr; g = blockIdx.x; b = 0;
-    t = load_tile(ranges, ns, g);
-    tn = load_tile(ranges, ns, g + gridDim.x);
-    settle();
-  }
-  __device__ __forceinline__ void advance() { ++b; settle(); }
-};
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32"
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basis,
@@ -436,17 +364,6 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
   }
 }
 
-uint32_t make_idesc(int m, int n, bool b_mn) {
-  uint32_t d = 0;
-  d |= 1u << 4;                       // D: f32
-  d |= 1u << 7;                       // A: bf16
-  d |= 1u << 10;                      // B: bf16
-  d |= (b_mn ? 1u : 0u) << 16;        // B major: 0 = K, 1 = MN
-  d |= (uint32_t)(n >> 3) << 17;
-  d |= (uint32_t)(m >> 4) << 24;
-  return d;
-}
-
 }  // namespace
 
 bool basis_proj_grads_tc_supported(int K, int C) { return K == kK && C == kC; }
@@ -468,7 +385,7 @@ int basis_proj_grads_tc(cudaStream_t st, int64_t ns, int64_t M, const float* bas
   ProfScope prof(st, "basis_proj_grads_tc");
   kern<<<grid, kThreads, kSmemBytes, st>>>(ns, M, basis, fs, (const int2*)neigh, ranges,
                                            (const uint8_t*)image, dbasis, dfeat,
-                                           make_idesc(kRows, 64, true), make_idesc(kRows, kC, false),
+                                           make_idesc(kRows, 64, false, true), make_idesc(kRows, kC, false, false),
                                            err_flag);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
