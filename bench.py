@@ -97,10 +97,14 @@ def measured_peaks():
 NCU_TRAFFIC_BYTES_PER_POINT = {
     # profiles/projection_and_gemm_kernels_16_clouds.md: bytes of one launch / 262144 points
     "basis_proj_split": (1.030125e9 + 2.100271e9) / 262144,
+    "basis_proj_split_mma": (1.318681e9 + 2.100419e9) / 262144,
     "basis_proj_grads": (4.091760e9 + 1.135269e9) / 262144,
-    "gemm_bf16x3_k_mn": (2.176671e9 + 0.255460e9) / 262144,
+    "basis_proj_grads_mma": (3.955412e9 + 1.121180e9) / 262144,
+    "basis_proj_grads_tc": (3.101795e9 + 0.680210e9) / 262144,
+    "gemm_bf16x3_k_mn": (2.176700e9 + 0.255623e9) / 262144,
     "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
-    "gemm_bf16x3_mn_mn": (2.415946e9 + 0.004173e9) / 262144,
+    "gemm_bf16x3_k_k_image": (2.149690e9 + 2.100168e9) / 262144,
+    "gemm_bf16x3_mn_mn": (2.415943e9 + 0.004868e9) / 262144,
 }
 
 
