@@ -227,6 +227,24 @@ int tfgpc_basis_proj_grads(void* stream, int K, int C, int64_t ns,
                            const float* features, const int32_t* neighbors,
                            const int32_t* ranges, const float* in_grads,
                            float* dbasis_out, float* dfeat_out);
+/* The same two ops with caller scratch (what the reference takes from
+ * IGPUDevice::getFloatTmpGPUBuffer, tf_gpu_device.cpp:122-142): for K in
+ * {16, 32, 64} and C a multiple of 16 they run on tensor-core MMAs over a bf16
+ * hi/mid copy of the features written into `ws` (three bf16 passes, fp32
+ * accumulate: results within 1e-4 of the fp32 kernels).  The query returns 0
+ * for shapes without such a path; with ws == NULL, too little scratch or a
+ * shape without it, the calls fall through to the entries above. */
+size_t tfgpc_basis_proj_workspace_bytes(int K, int C, int64_t n_in);
+int tfgpc_basis_proj_ws(void* stream, int K, int C, int64_t ns, int64_t n_in,
+                        int64_t M, const float* basis, const float* features,
+                        const int32_t* neighbors, const int32_t* ranges,
+                        float* out, void* ws, size_t ws_bytes);
+int tfgpc_basis_proj_grads_ws(void* stream, int K, int C, int64_t ns,
+                              int64_t n_in, int64_t M, const float* basis,
+                              const float* features, const int32_t* neighbors,
+                              const int32_t* ranges, const float* in_grads,
+                              float* dbasis_out, float* dfeat_out, void* ws,
+                              size_t ws_bytes);
 
 /* ---- Sampling ------------------------------------------------------------
  * Replaces SamplingOp::Compute (sampling/cc/ops/sampling_ops.cpp:81-195) and

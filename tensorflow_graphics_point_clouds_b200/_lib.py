@@ -45,6 +45,9 @@ SYMBOLS = {
     "tfgpc_compute_pdf_pt_grads": c_int,
     "tfgpc_basis_proj": c_int,
     "tfgpc_basis_proj_grads": c_int,
+    "tfgpc_basis_proj_workspace_bytes": c_sz,
+    "tfgpc_basis_proj_ws": c_int,
+    "tfgpc_basis_proj_grads_ws": c_int,
     "tfgpc_sampling_workspace_bytes": c_sz,
     "tfgpc_sampling_count": c_int,
     "tfgpc_sampling_store": c_int,

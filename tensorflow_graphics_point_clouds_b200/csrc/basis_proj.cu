@@ -359,6 +359,17 @@ static int launch_basis_proj_grads(cudaStream_t st, int C, int64_t ns, const flo
   return TFGPC_OK;
 }
 
+// basis_proj_mma.cu: the same contractions on warp-level tensor-core MMAs, over a
+// bf16 hi/mid copy of the features kept in caller scratch
+bool basis_proj_mma_supported(int K, int C);
+int split_features(cudaStream_t st, const float* feat, int64_t n, int C, __nv_bfloat16* fs);
+int basis_proj_mma_f32(cudaStream_t st, int K, int C, int64_t ns, const float* basis,
+                       const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                       float* out);
+int basis_proj_grads_mma(cudaStream_t st, int K, int C, int64_t ns, int64_t M, const float* basis,
+                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                         const float* in_grads, float* dbasis, float* dfeat);
+
 static int check_bp_args(const char* op, int K, int C, int64_t ns, int64_t n_in, int64_t M) {
   TFGPC_REQUIRE(valid_basis(K), "%s expects a valid number of basis functions.", op);
   TFGPC_REQUIRE(valid_features(C), "%s expects a valid number of input features, between 1 and 8 "
@@ -419,4 +430,56 @@ extern "C" int tfgpc_basis_proj_grads(void* stream, int K, int C, int64_t ns, in
     case 32: return launch_basis_proj_grads<32>(st, C, ns, basis, features, nb, ranges, in_grads, dbasis_out, dfeat_out);
     default: return launch_basis_proj_grads<64>(st, C, ns, basis, features, nb, ranges, in_grads, dbasis_out, dfeat_out);
   }
+}
+
+extern "C" size_t tfgpc_basis_proj_workspace_bytes(int K, int C, int64_t n_in) {
+  if (n_in <= 0 || !basis_proj_mma_supported(K, C)) return 0;
+  return (size_t)n_in * C * 4 + 256;
+}
+
+// True if `ws` can hold the split features of this call and everything is
+// aligned for the tensor-core kernels.
+static bool mma_path(int K, int C, int64_t n_in, const void* ws, size_t ws_bytes, const void* a,
+                     const void* b, const void* c) {
+  const size_t need = tfgpc_basis_proj_workspace_bytes(K, C, n_in);
+  return need > 0 && ws && ws_bytes >= need && (uintptr_t)ws % 16 == 0 && (uintptr_t)a % 16 == 0 &&
+         (uintptr_t)b % 16 == 0 && (uintptr_t)c % 16 == 0;
+}
+
+extern "C" int tfgpc_basis_proj_ws(void* stream, int K, int C, int64_t ns, int64_t n_in, int64_t M,
+                                   const float* basis, const float* features,
+                                   const int32_t* neighbors, const int32_t* ranges, float* out,
+                                   void* ws, size_t ws_bytes) {
+  if (ns == 0 || M == 0 || !mma_path(K, C, n_in, ws, ws_bytes, features, basis, out))
+    return tfgpc_basis_proj(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges, out);
+  int rc = check_bp_args("BasisProjOp", K, C, ns, n_in, M);
+  if (rc) return rc;
+  TFGPC_REQUIRE(ranges && out && basis && features && neighbors, "BasisProjOp got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  __nv_bfloat16* fs = (__nv_bfloat16*)ws;
+  rc = split_features(st, features, n_in, C, fs);
+  if (rc) return rc;
+  return basis_proj_mma_f32(st, K, C, ns, basis, fs, neighbors, ranges, out);
+}
+
+extern "C" int tfgpc_basis_proj_grads_ws(void* stream, int K, int C, int64_t ns, int64_t n_in,
+                                         int64_t M, const float* basis, const float* features,
+                                         const int32_t* neighbors, const int32_t* ranges,
+                                         const float* in_grads, float* dbasis_out,
+                                         float* dfeat_out, void* ws, size_t ws_bytes) {
+  if (ns == 0 || M == 0 || !mma_path(K, C, n_in, ws, ws_bytes, features, dbasis_out, dfeat_out) ||
+      (uintptr_t)basis % 16 != 0 || (uintptr_t)in_grads % 16 != 0)
+    return tfgpc_basis_proj_grads(stream, K, C, ns, n_in, M, basis, features, neighbors, ranges,
+                                  in_grads, dbasis_out, dfeat_out);
+  int rc = check_bp_args("BasisProjGradsOp", K, C, ns, n_in, M);
+  if (rc) return rc;
+  TFGPC_REQUIRE(basis && features && neighbors && ranges && in_grads && dbasis_out && dfeat_out,
+                "BasisProjGradsOp got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  __nv_bfloat16* fs = (__nv_bfloat16*)ws;
+  rc = split_features(st, features, n_in, C, fs);
+  if (rc) return rc;
+  TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+  return basis_proj_grads_mma(st, K, C, ns, M, basis, fs, neighbors, ranges, in_grads, dbasis_out,
+                              dfeat_out);
 }

@@ -38,15 +38,16 @@ int launch_persistent(Kern kern, int warp_bytes, int max_warps, int64_t ns, int*
   return TFGPC_OK;
 }
 
-template <int K>
+template <int K, int OUT>
 int launch_fwd(cudaStream_t st, int C, int64_t ns, const float* basis, const __nv_bfloat16* fs,
-               const int2* neigh, const int32_t* ranges, __nv_bfloat16* hi, __nv_bfloat16* mid) {
-  auto kern = bpm::basis_proj_mma_kernel<K>;
+               const int2* neigh, const int32_t* ranges, float* out, __nv_bfloat16* hi,
+               __nv_bfloat16* mid) {
+  auto kern = bpm::basis_proj_mma_kernel<K, OUT>;
   int grid, threads; size_t smem;
   int rc = launch_persistent(kern, bpm::Cfg<K>::kFwdWarpBytes, 11, ns, &grid, &threads, &smem);
   if (rc) return rc;
-  ProfScope prof(st, "basis_proj_split_mma");
-  kern<<<grid, threads, smem, st>>>(C, ns, basis, fs, neigh, ranges, hi, mid);
+  ProfScope prof(st, OUT == 0 ? "basis_proj_mma" : "basis_proj_split_mma");
+  kern<<<grid, threads, smem, st>>>(C, ns, basis, fs, neigh, ranges, out, hi, mid);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -86,9 +87,22 @@ int basis_proj_mma_split(cudaStream_t st, int K, int C, int64_t ns, const float*
                          __nv_bfloat16* hi, __nv_bfloat16* mid) {
   const int2* nb = (const int2*)neigh;
   switch (K) {
-    case 16: return launch_fwd<16>(st, C, ns, basis, fs, nb, ranges, hi, mid);
-    case 32: return launch_fwd<32>(st, C, ns, basis, fs, nb, ranges, hi, mid);
-    case 64: return launch_fwd<64>(st, C, ns, basis, fs, nb, ranges, hi, mid);
+    case 16: return launch_fwd<16, 1>(st, C, ns, basis, fs, nb, ranges, nullptr, hi, mid);
+    case 32: return launch_fwd<32, 1>(st, C, ns, basis, fs, nb, ranges, nullptr, hi, mid);
+    case 64: return launch_fwd<64, 1>(st, C, ns, basis, fs, nb, ranges, nullptr, hi, mid);
+  }
+  return fail(TFGPC_EINVAL, "tensor-core projection expects 16, 32 or 64 basis functions");
+}
+
+// The same projection as fp32 [ns, C, K] (the drop-in op's output).
+int basis_proj_mma_f32(cudaStream_t st, int K, int C, int64_t ns, const float* basis,
+                       const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                       float* out) {
+  const int2* nb = (const int2*)neigh;
+  switch (K) {
+    case 16: return launch_fwd<16, 0>(st, C, ns, basis, fs, nb, ranges, out, nullptr, nullptr);
+    case 32: return launch_fwd<32, 0>(st, C, ns, basis, fs, nb, ranges, out, nullptr, nullptr);
+    case 64: return launch_fwd<64, 0>(st, C, ns, basis, fs, nb, ranges, out, nullptr, nullptr);
   }
   return fail(TFGPC_EINVAL, "tensor-core projection expects 16, 32 or 64 basis functions");
 }

@@ -244,12 +244,14 @@ __device__ __forceinline__ void store_basis(uint8_t* tile, int lane, const float
 // the gathered feature rows (ldmatrix.trans), B transposed out of the staged
 // basis rows.  Features of chunk i+1 are in flight, and its basis rows and the
 // indices of chunk i+2 are on their way to registers, while chunk i is multiplied.
-template <int K>
+// OUT = 0: fp32 [ns, C, K] (the op's output).  OUT = 1: the same values split
+// into two bf16 arrays [ns, C*K] (left operand of the tensor-core GEMM).
+template <int K, int OUT>
 __global__ void __launch_bounds__(352, 1)
 basis_proj_mma_kernel(int C, int64_t ns, const float* __restrict__ basis,
                       const __nv_bfloat16* __restrict__ fs, const int2* __restrict__ neigh,
-                      const int32_t* __restrict__ ranges, __nv_bfloat16* __restrict__ out_hi,
-                      __nv_bfloat16* __restrict__ out_mid) {
+                      const int32_t* __restrict__ ranges, float* __restrict__ out,
+                      __nv_bfloat16* __restrict__ out_hi, __nv_bfloat16* __restrict__ out_mid) {
   typedef Cfg<K> cfg;
   extern __shared__ __align__(128) uint8_t bpm_smem[];
   const int lane = threadIdx.x & 31;
@@ -354,12 +356,18 @@ basis_proj_mma_kernel(int C, int64_t ns, const float* __restrict__ basis,
             for (int j = 0; j < cfg::kNTP; ++j) {
 #pragma unroll
               for (int h = 0; h < 2; ++h) {   // rows g and g + 8
-                uint2 hv, mv;
-                split2(acc[mt][2 * j][2 * h], acc[mt][2 * j][2 * h + 1], hv.x, mv.x);
-                split2(acc[mt][2 * j + 1][2 * h], acc[mt][2 * j + 1][2 * h + 1], hv.y, mv.y);
                 const int64_t o = obase + (int64_t)(16 * mt + 8 * h) * K + 16 * j;
-                *reinterpret_cast<uint2*>(out_hi + o) = hv;
-                *reinterpret_cast<uint2*>(out_mid + o) = mv;
+                if (OUT == 0) {
+                  *reinterpret_cast<float4*>(out + o) =
+                      make_float4(acc[mt][2 * j][2 * h], acc[mt][2 * j][2 * h + 1],
+                                  acc[mt][2 * j + 1][2 * h], acc[mt][2 * j + 1][2 * h + 1]);
+                } else {
+                  uint2 hv, mv;
+                  split2(acc[mt][2 * j][2 * h], acc[mt][2 * j][2 * h + 1], hv.x, mv.x);
+                  split2(acc[mt][2 * j + 1][2 * h], acc[mt][2 * j + 1][2 * h + 1], hv.y, mv.y);
+                  *reinterpret_cast<uint2*>(out_hi + o) = hv;
+                  *reinterpret_cast<uint2*>(out_mid + o) = mv;
+                }
               }
             }
           }

@@ -244,20 +244,30 @@ def _bp_args(basis, features, neighbors, ranges):
   return basis, features, neighbors, ranges
 
 
-def basis_proj(basis_neighbors, pt_features, neighbors, sample_neigh_indices):
-  """BasisProj (basis_proj/cc/ops/basis_proj_ops.cpp:25-39) -> [Ns, C, K]."""
+def _bp_scratch(k, c, feat):
+  """Scratch of the tensor-core BasisProj kernels (None where the shape has none)."""
+  nbytes = _lib.lib().tfgpc_basis_proj_workspace_bytes(c_int(k), c_int(c), c_i64(feat.shape[0]))
+  if nbytes == 0:
+    return None, 0
+  return torch.empty(nbytes, dtype=torch.uint8, device=feat.device), nbytes
+
+
+def basis_proj(basis_neighbors, pt_features, neighbors, sample_neigh_indices, scratch=True):
+  """BasisProj (basis_proj/cc/ops/basis_proj_ops.cpp:25-39) -> [Ns, C, K].
+  scratch=False keeps the call free of temporary device memory (fp32 kernels)."""
   basis, feat, neighbors, ranges = _bp_args(basis_neighbors, pt_features, neighbors,
                                             sample_neigh_indices)
   k, c, ns = basis.shape[1], feat.shape[1], ranges.shape[0]
   out = torch.empty((ns, c, k), dtype=torch.float32, device=basis.device)
-  _lib.check(_lib.lib().tfgpc_basis_proj(
+  ws, ws_bytes = _bp_scratch(k, c, feat) if scratch else (None, 0)
+  _lib.check(_lib.lib().tfgpc_basis_proj_ws(
       _stream(), c_int(k), c_int(c), c_i64(ns), c_i64(feat.shape[0]), c_i64(basis.shape[0]),
-      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(out)))
+      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(out), ptr(ws), c_sz(ws_bytes)))
   return out
 
 
 def basis_proj_grads(basis_neighbors, pt_features, neighbors, sample_neigh_indices,
-                     in_gradients):
+                     in_gradients, scratch=True):
   """BasisProjGrads (basis_proj/cc/ops/basis_proj_ops.cpp:41-53) ->
   (basis_gradients [M, K], feat_gradients [Nin, C])."""
   basis, feat, neighbors, ranges = _bp_args(basis_neighbors, pt_features, neighbors,
@@ -268,9 +278,11 @@ def basis_proj_grads(basis_neighbors, pt_features, neighbors, sample_neigh_indic
     raise _lib.TfgpcError(1, "BasisProjGradsOp expects gradients of shape [Ns, C, K]")
   dbasis = torch.empty_like(basis)
   dfeat = torch.empty_like(feat)
-  _lib.check(_lib.lib().tfgpc_basis_proj_grads(
+  ws, ws_bytes = _bp_scratch(k, c, feat) if scratch else (None, 0)
+  _lib.check(_lib.lib().tfgpc_basis_proj_grads_ws(
       _stream(), c_int(k), c_int(c), c_i64(ns), c_i64(feat.shape[0]), c_i64(basis.shape[0]),
-      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(grads), ptr(dbasis), ptr(dfeat)))
+      ptr(basis), ptr(feat), ptr(neighbors), ptr(ranges), ptr(grads), ptr(dbasis), ptr(dfeat),
+      ptr(ws), c_sz(ws_bytes)))
   return dbasis, dfeat
 
 

@@ -208,8 +208,11 @@ BP_CASES = [(1, 8, 2), (3, 16, 3), (7, 32, 3), (8, 64, 3), (16, 8, 4), (32, 16, 
             (64, 32, 3), (128, 16, 3), (136, 16, 3), (256, 16, 3), (64, 64, 3)]
 
 
+@pytest.mark.parametrize("scratch", [True, False])
 @pytest.mark.parametrize("c,k,d", BP_CASES)
-def test_basis_proj_and_grads(c, k, d):
+def test_basis_proj_and_grads(c, k, d, scratch):
+  """scratch=True: tensor-core kernels where the shape has them (K in 16/32/64,
+  C % 16 == 0), fp32 kernels elsewhere; scratch=False: fp32 kernels only."""
   rng = np.random.default_rng(400 + c + k)
   b = 3
   pts, bid = random_cloud(rng, b, 1200, d)
@@ -221,12 +224,13 @@ def test_basis_proj_and_grads(c, k, d):
   basis = rng.normal(size=(m, k)).astype(F32)
   feat = rng.normal(size=(len(pts), c)).astype(F32)
   ref = orc.basis_proj(basis, feat, nb_ref.original_neigh_ids, nb_ref.ranges)
-  got = ops.basis_proj(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges)
+  got = ops.basis_proj(t(basis), t(feat), nb._original_neigh_ids, nb._samples_neigh_ranges,
+                       scratch=scratch)
   close(got.cpu().numpy(), ref)
   gin = rng.normal(size=ref.shape).astype(F32)
   ref_db, ref_df = orc.basis_proj_grads(basis, feat, nb_ref.original_neigh_ids, nb_ref.ranges, gin)
   got_db, got_df = ops.basis_proj_grads(t(basis), t(feat), nb._original_neigh_ids,
-                                        nb._samples_neigh_ranges, t(gin))
+                                        nb._samples_neigh_ranges, t(gin), scratch=scratch)
   close(got_db.cpu().numpy(), ref_db)
   close(got_df.cpu().numpy(), ref_df)
 
