@@ -4,17 +4,18 @@
 //   dbasis[m, k]  = sum_c feat[j, c] * dX[s, c, k]
 //   dfeat[j, c]  += sum_k basis[m, k] * dX[s, c, k]
 // Per sample these products have only ~32 rows, too few for a 128-row tensor
-// core tile.  The kernel therefore works on groups of four consecutive samples
-// whose pairs (contiguous in the neighbor list) are cut into blocks of 128 rows,
-// and writes both gradients as block-sparse products against the group's
-// concatenated gradient dXcat[c, (s_local, k)] (128 x 64):
-//   (1) D1[128 pairs, 64]  = F[128 pairs, 128 c] * dXcat          -> a pair's own
+// core tile.  The kernel therefore works on groups of G consecutive samples (G =
+// 4, or 3 where four samples would mostly overflow one block) whose pairs
+// (contiguous in the neighbor list) are cut into blocks of 128 rows, and writes
+// both gradients as block-sparse products against the group's concatenated
+// gradient dXcat[c, (s_local, k)] (128 x 16 G):
+//   (1) D1[128 pairs, 16 G] = F[128 pairs, 128 c] * dXcat         -> a pair's own
 //       sample block of 16 columns is its dbasis row, the rest is discarded;
-//   (2) D2[128 c, 128 pairs] = dXcat * Bx^T, where Bx[128 pairs, 64] holds the
+//   (2) D2[128 c, 128 pairs] = dXcat * Bx^T, where Bx[128 pairs, 16 G] holds the
 //       pair's basis row in the 16 columns of its own sample and zeros elsewhere
 //       (channels on the accumulator rows, so that a warp of the epilogue adds 32
 //       consecutive channels of one neighbor's gradient row per instruction).
-// 3/4 of the MMA work multiplies zeros or is thrown away, which is cheap next to
+// Most of the MMA work multiplies zeros or is thrown away, which is cheap next to
 // what it saves: no per-sample staging, no warp-level bookkeeping per 16 pairs.
 // fp32 accuracy comes from the 3-pass bf16 split of both operands (hi*mid +
 // mid*hi + hi*hi into fp32 tensor memory), as in gemm_sm100.cu.
@@ -66,6 +67,7 @@ struct Barriers {
   int abort_flag;
 };
 
+template <int G>
 __global__ void __launch_bounds__(kThreads, 1)
 basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basis,
                            const __nv_bfloat16* __restrict__ fs, const int2* __restrict__ neigh,
@@ -80,7 +82,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
   Barriers* bars = (Barriers*)(dx + 2 * kDxBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int64_t groups = (ns + kGroup - 1) / kGroup;
+  const int64_t groups = (ns + G - 1) / G;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kSlots; ++i) {
@@ -120,8 +122,14 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     // blocks only when the ring has no free slot.
     const int row_base = warp * 16;
     const int brow = lane >> 1, bh = lane & 1;     // basis: two lanes per row
+    // gather: lanes 0-15 take row `it`, lanes 16-31 row `it + 8` of the warp's 16;
+    // within a row, lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
+    const int l4 = lane >> 4, part = (lane >> 3) & 1, j = lane & 7;
+    const int idx_row = (lane & 7) + 8 * l4;
+    const __nv_bfloat16* const fs_lane = fs + part * kC + j * 8;
+    const uint32_t dst_lane = part * kPart + (row_base + 8 * l4) * 128;
     uint32_t unit = 0, item = 0;
-    ItemWalk walk;
+    ItemWalk<G> walk;
     walk.init(ranges, ns, groups);
     // registers of the block being prefetched
     Tile t_n = walk.t;
@@ -130,7 +138,9 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     auto prefetch = [&]() {
       t_n = walk.t;
       m0_n = walk.t.pa + walk.b * kRows + row_base;
-      idx_n = (lane < 16 && m0_n + lane < t_n.pe) ? __ldg(&neigh[m0_n + lane].x) : 0;
+      // ids of rows 0-7 in lanes 0-7, of rows 8-15 in lanes 16-23: a shuffle within
+      // half warps then hands row it + 8 * (lane / 16) to every lane
+      idx_n = ((lane & 8) == 0 && m0_n + idx_row < t_n.pe) ? __ldg(&neigh[m0_n + idx_row].x) : 0;
       b0_n = b1_n = make_float4(0.f, 0.f, 0.f, 0.f);
       if (m0_n + brow < t_n.pe) {
         const float4* src =
@@ -151,16 +161,14 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
       for (int kb = 0; kb < 2; ++kb, ++unit) {
         const uint32_t slot = unit % kSlots;
         mbar_wait(smem_u32(&bars->f_empty[slot]), ((unit / kSlots) & 1) ^ 1, abort_flag, err_flag);
-        const uint32_t base = smem_u32(f_ring + (size_t)slot * kSlotBytes);
-        const int part = (lane >> 3) & 1, j = lane & 7;
+        const uint32_t base = smem_u32(f_ring + (size_t)slot * kSlotBytes) + dst_lane;
+        const int nv = t.pe - m0 - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-          const int rl = 2 * it + (lane >> 4);
-          const int idx = __shfl_sync(0xffffffffu, my_idx, rl);
-          const int r = row_base + rl;
-          if (m0 + rl < t.pe)
-            cp_async16(base + part * kPart + r * 128 + ((j ^ (r & 7)) << 4),
-                       fs + (int64_t)idx * 2 * kC + part * kC + kb * 64 + j * 8);
+          const int idx = __shfl_sync(0xffffffffu, my_idx, it, 16);
+          // row row_base + 8 * l4 + it: (row % 8) == it, the swizzle is a constant
+          if (it < nv)
+            cp_async16(base + it * 128 + ((j ^ it) << 4), fs_lane + (int64_t)idx * 2 * kC + kb * 64);
         }
         // arrives on the slot's barrier once this thread's copies have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
@@ -181,7 +189,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         uint8_t* rowp = bx + (size_t)stage * kBxBytes + r * 128;
         const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int q = 0; q < kGroup; ++q) {
+        for (int q = 0; q < G; ++q) {
           const int pos = ((2 * q + bh) ^ (r & 7)) << 4;
           *reinterpret_cast<uint4*>(rowp + pos) = (q == sl) ? hv : zero;
           *reinterpret_cast<uint4*>(rowp + kPart + pos) = (q == sl) ? mv : zero;
@@ -199,10 +207,10 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     const bool first = warp == kMmaWarp;
     if (lane == 0) {
       uint32_t unit = 0, item = 0, tile_i = 0;
-      Tile next = load_tile(ranges, ns, blockIdx.x);
+      Tile next = load_tile<G>(ranges, ns, blockIdx.x);
       for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
         const Tile t = next;
-        next = load_tile(ranges, ns, g + gridDim.x);
+        next = load_tile<G>(ranges, ns, g + gridDim.x);
         const int nb = t.blocks();
         if (nb == 0) continue;
         const uint32_t dbuf = tile_i & 1;
@@ -212,7 +220,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
           const uint32_t abuf = item & 1;
           mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
           tc_fence_after();
-          const uint32_t d1 = tmem_base + abuf * kAccCols, d2 = d1 + 64;
+          const uint32_t d1 = tmem_base + abuf * kAccCols, d2 = d1 + 64;   // D1 uses 16 G columns
           if (first) {
             // (1) D1 = F * dXcat: reduction over the 128 channels, two ring slots
             uint32_t accumulate = 0;
@@ -246,7 +254,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
             const uint32_t bx_hi = smem_u32(bx + (size_t)abuf * kBxBytes), bx_mid = bx_hi + kPart;
             uint32_t accumulate = 0;
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < G; ++kk) {   // one step of 16 columns per sample of the group
               const uint64_t da_hi = make_desc(dx_hi + kk * 32, 16, 1024);
               const uint64_t da_mid = make_desc(dx_mid + kk * 32, 16, 1024);
               const uint64_t db_hi = make_desc(bx_hi + kk * 32, 16, 1024);
@@ -268,10 +276,10 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     // ------------------------------------------------------- dXcat loader
     if (lane == 0) {
       uint32_t tile_i = 0;
-      Tile next = load_tile(ranges, ns, blockIdx.x);
+      Tile next = load_tile<G>(ranges, ns, blockIdx.x);
       for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
         const Tile t = next;
-        next = load_tile(ranges, ns, g + gridDim.x);
+        next = load_tile<G>(ranges, ns, g + gridDim.x);
         if (t.blocks() == 0) continue;
         const uint32_t dbuf = tile_i & 1;
         mbar_wait(smem_u32(&bars->dx_empty[dbuf]), ((tile_i >> 1) & 1) ^ 1, abort_flag, err_flag);
@@ -292,7 +300,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     const int half = (warp - kEpiWarp0) >> 2;
     const int r = quarter * 32 + lane;        // this thread's accumulator row
     float* const dcol = dfeat + r;            // channel r of every gradient row
-    ItemWalk walk;
+    ItemWalk<G> walk;
     walk.init(ranges, ns, groups);
     uint32_t item = 0;
     for (; walk.valid; walk.advance(), ++item) {
@@ -316,7 +324,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         const bool live = ok && m < t.pe;
         const int sl = live ? t.local_sample(m) : -1;
 #pragma unroll
-        for (int q = 0; q < kGroup; ++q) {
+        for (int q = 0; q < G; ++q) {
           if (__any_sync(0xffffffffu, sl == q)) {
             uint32_t v[16];
             tmem_ld_x16(taddr + 16 * q, v);
@@ -368,27 +376,45 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
 
 bool basis_proj_grads_tc_supported(int K, int C) { return K == kK && C == kC; }
 
+// Samples per group for a neighbor list of M pairs over ns samples: four while a
+// group's pairs mostly fit one block of 128 rows, else three (whose second block,
+// when there is one, is no emptier than any other remainder).
+int basis_proj_grads_tc_group(int64_t ns, int64_t M) {
+  return (ns > 0 && M * 4 <= ns * 112) ? 4 : 3;
+}
+
+template <int G>
+static int launch_grads_tc(cudaStream_t st, int64_t ns, int64_t M, const float* basis,
+                           const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
+                           const void* image, float* dbasis, float* dfeat, int* err_flag) {
+  auto kern = basis_proj_grads_tc_kernel<G>;
+  TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kSmemBytes));
+  const int64_t groups = (ns + G - 1) / G;
+  const int grid = (int)(groups < sm_count() ? groups : sm_count());
+  ProfScope prof(st, "basis_proj_grads_tc");
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ns, M, basis, fs, (const int2*)neigh, ranges,
+                                           (const uint8_t*)image, dbasis, dfeat,
+                                           make_idesc(kRows, 16 * G, false, true),
+                                           make_idesc(kRows, kC, false, false), err_flag);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
 // `image`: the dX operand image written by gemm_bf16x3_grad_image for these ns
-// samples (ceil(ns / 4) groups of 32 KB; the columns of samples beyond ns must
-// be finite).  dfeat must be zero on entry; dbasis is overwritten.
-int basis_proj_grads_tc(cudaStream_t st, int64_t ns, int64_t M, const float* basis,
+// samples in groups of `group` (ceil(ns / group) groups of 32 KB; the columns of
+// the samples beyond ns in the last group must be finite).  dfeat must be zero
+// on entry; dbasis is overwritten.
+int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const float* basis,
                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
                         const void* image, float* dbasis, float* dfeat, int* err_flag) {
   TFGPC_REQUIRE((uintptr_t)image % 16 == 0 && (uintptr_t)fs % 16 == 0 && (uintptr_t)basis % 16 == 0 &&
                 (uintptr_t)dbasis % 16 == 0 && (uintptr_t)dfeat % 16 == 0,
                 "tensor-core projection gradients expect 16-byte aligned buffers");
-  auto kern = basis_proj_grads_tc_kernel;
-  TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)kSmemBytes));
-  const int64_t groups = (ns + kGroup - 1) / kGroup;
-  const int grid = (int)(groups < sm_count() ? groups : sm_count());
-  ProfScope prof(st, "basis_proj_grads_tc");
-  kern<<<grid, kThreads, kSmemBytes, st>>>(ns, M, basis, fs, (const int2*)neigh, ranges,
-                                           (const uint8_t*)image, dbasis, dfeat,
-                                           make_idesc(kRows, 64, false, true), make_idesc(kRows, kC, false, false),
-                                           err_flag);
-  TFGPC_LAUNCH_CHECK();
-  return TFGPC_OK;
+  if (group == 4)
+    return launch_grads_tc<4>(st, ns, M, basis, fs, neigh, ranges, image, dbasis, dfeat, err_flag);
+  TFGPC_REQUIRE(group == 3, "tensor-core projection gradients work on groups of 3 or 4 samples");
+  return launch_grads_tc<3>(st, ns, M, basis, fs, neigh, ranges, image, dbasis, dfeat, err_flag);
 }
 
 }  // namespace tfgpc

@@ -1,6 +1,6 @@
 // Pieces shared by the tcgen05 basis-projection kernels (forward and
-// gradients): both work on groups of four consecutive samples, whose pairs are
-// contiguous in the neighbor list.
+// gradients): both work on groups of three or four consecutive samples, whose
+// pairs are contiguous in the neighbor list.
 #pragma once
 
 #include "basis_proj.cuh"
@@ -13,32 +13,35 @@ using namespace tc;
 
 constexpr int kC = 128;        // channels
 constexpr int kK = 16;         // basis functions
-constexpr int kGroup = 4;      // samples per tile
 constexpr int kRows = 128;     // pairs per 128-row block of the gradient kernel
 
-// Pair range of a group of four samples and the ends of its first three.
+// Pair range of a group of G consecutive samples (G = 3 or 4) and the ends of
+// all but its last sample.
 struct Tile {
   int pa, e0, e1, e2, pe;
   __device__ __forceinline__ int blocks() const { return (pe - pa + kRows - 1) / kRows; }
+  // (e2 == pe for groups of three, so the third comparison is then always false)
   __device__ __forceinline__ int local_sample(int m) const {
     return (m >= e0) + (m >= e1) + (m >= e2);
   }
 };
 
+template <int G>
 __device__ __forceinline__ Tile load_tile(const int32_t* __restrict__ ranges, int64_t ns, int64_t g) {
   Tile t;
-  const int64_t s0 = g * kGroup;
+  const int64_t s0 = g * G;
   if (s0 >= ns) { t.pa = t.e0 = t.e1 = t.e2 = t.pe = 0; return t; }
   t.pa = s0 > 0 ? __ldg(ranges + s0 - 1) : 0;
   t.e0 = __ldg(ranges + s0);
   t.e1 = __ldg(ranges + min(s0 + 1, ns - 1));
   t.e2 = __ldg(ranges + min(s0 + 2, ns - 1));
-  t.pe = __ldg(ranges + min(s0 + 3, ns - 1));
+  t.pe = G == 4 ? __ldg(ranges + min(s0 + 3, ns - 1)) : t.e2;
   return t;
 }
 
 // Walk over the blocks (tile, 128-row block) of this CTA, with the next tile's
 // ranges already on their way.
+template <int G>
 struct ItemWalk {
   const int32_t* ranges;
   int64_t ns, groups, g;
@@ -49,15 +52,15 @@ struct ItemWalk {
     while (g < groups && b >= t.blocks()) {
       g += gridDim.x;
       t = tn;
-      tn = load_tile(ranges, ns, g + gridDim.x);
+      tn = load_tile<G>(ranges, ns, g + gridDim.x);
       b = 0;
     }
     valid = g < groups;
   }
   __device__ __forceinline__ void init(const int32_t* r, int64_t n, int64_t gr) {
     ranges = r; ns = n; groups = gr; g = blockIdx.x; b = 0;
-    t = load_tile(ranges, ns, g);
-    tn = load_tile(ranges, ns, g + gridDim.x);
+    t = load_tile<G>(ranges, ns, g);
+    tn = load_tile<G>(ranges, ns, g + gridDim.x);
     settle();
   }
   __device__ __forceinline__ void advance() { ++b; settle(); }

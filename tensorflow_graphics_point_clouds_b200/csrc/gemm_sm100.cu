@@ -73,7 +73,7 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
                    const __grid_constant__ CUtensorMap tm_b_mid,
                    const __grid_constant__ CUtensorMap tm_c, int64_t m_total, int64_t n_total,
                    int bn, uint32_t idesc, TileSchedule sch, int* err_flag, uint8_t* image,
-                   int image_channels) {
+                   int image_channels, int image_group) {
   extern __shared__ uint8_t smem_raw[];
   // the swizzled tiles need 1024-byte alignment
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -230,8 +230,9 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
           const int64_t row = (int64_t)row0 + lane;
           if (row < m_total && !*abort_flag) {
             const int64_t part = (int64_t)image_channels * 128;   // bytes of the hi (or mid) rows
-            uint8_t* group = image + (row >> 2) * (2 * part);
-            const int sl = (int)(row & 3);
+            const int64_t gi = row / image_group;
+            uint8_t* group = image + gi * (2 * part);
+            const int sl = (int)(row - gi * image_group);
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const int ch = (n * bn + c0) / 16 + u;
@@ -360,7 +361,8 @@ uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
 
 template <bool A_MN, bool B_MN, int OUT = 0>
 int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int bn,
-           TileSchedule sch, int* err_flag, uint8_t* image = nullptr, int image_channels = 0) {
+           TileSchedule sch, int* err_flag, uint8_t* image = nullptr, int image_channels = 0,
+           int image_group = 4) {
   auto kern = gemm_bf16x3_kernel<A_MN, B_MN, OUT>;
   TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)kSmemBytes));
@@ -371,7 +373,7 @@ int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int b
                                      : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
                                            make_idesc(kBM, bn, A_MN, B_MN), sch, err_flag, image,
-                                           image_channels);
+                                           image_channels, image_group);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -433,13 +435,14 @@ int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K) {
 }
 
 int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t K,
-                           const GemmOperand& a, const GemmOperand& b, void* image,
+                           const GemmOperand& a, const GemmOperand& b, void* image, int group,
                            int* err_flag) {
   const int64_t N = (int64_t)channels * 16;
   TFGPC_REQUIRE(M > 0 && channels > 0 && K > 0 && M < (int64_t)INT32_MAX && K < (int64_t)INT32_MAX,
                 "GEMM expects positive sizes below 2^31");
   TFGPC_REQUIRE(a.major == Major::K && b.major == Major::K && channels % 2 == 0 &&
-                (uintptr_t)image % 16 == 0, "gradient-image GEMM expects K-major operands");
+                (uintptr_t)image % 32 == 0 && group >= 1 && group <= 4,
+                "gradient-image GEMM expects K-major operands and groups of 1 to 4 rows");
   int bn = (int)(N < kBNMax ? N : kBNMax);
   bn = (bn + 31) / 32 * 32;
   CUtensorMap maps[5] = {};
@@ -454,7 +457,8 @@ int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t
   sch.k_blocks = (int)((K + kBK - 1) / kBK);
   sch.k_splits = 1;
   sch.k_blocks_per_split = sch.k_blocks;
-  return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels);
+  return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
+                                 group);
 }
 
 int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,

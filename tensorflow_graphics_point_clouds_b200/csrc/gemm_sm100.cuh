@@ -38,11 +38,11 @@ int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const Gemm
 
 // The same product for C = [M, channels * 16] (K-major operands), written not as
 // fp32 but as the bf16 hi/mid operand image of the tensor-core projection
-// gradients: per group of four rows, [hi | mid][channel][128 bytes], where the
-// 16-byte chunk 2 * (row % 4) + (k / 8) of a channel's line sits at position
-// chunk ^ (channel % 8).  `image` holds ceil(M / 4) groups.
+// gradients: per group of `group` rows (1 to 4), [hi | mid][channel][128 bytes],
+// where the 16-byte chunk 2 * (row % group) + (k / 8) of a channel's line sits at
+// position chunk ^ (channel % 8).  `image` holds ceil(M / group) groups.
 int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t K,
-                           const GemmOperand& a, const GemmOperand& b, void* image,
+                           const GemmOperand& a, const GemmOperand& b, void* image, int group,
                            int* err_flag);
 
 // Number of k slices that fills the GPU for an [M,N] output with reduction K.

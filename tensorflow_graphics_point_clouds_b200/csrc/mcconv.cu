@@ -28,7 +28,8 @@ int basis_proj_grads_mma(cudaStream_t st, int K, int C, int64_t ns, int64_t M, c
 
 // basis_proj_grads_tc.cu: the gradients on tcgen05 tensor cores
 bool basis_proj_grads_tc_supported(int K, int C);
-int basis_proj_grads_tc(cudaStream_t st, int64_t ns, int64_t M, const float* basis,
+int basis_proj_grads_tc_group(int64_t ns, int64_t M);
+int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const float* basis,
                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
                         const void* image, float* dbasis, float* dfeat, int* err_flag);
 
@@ -65,9 +66,9 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
-    // rounded up to whole groups of four samples (operand image of the
-    // tensor-core gradient kernel)
-    w.dx = (float*)take((size_t)((ns + 3) / 4 * 4) * ck * 4);
+    // as operand image of the tensor-core gradient kernel: one slot of 4*ck floats
+    // per group of three (or four) samples
+    w.dx = (float*)take((size_t)((ns + 2) / 3) * 4 * ck * 4);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
     w.dw_part = (float*)take((size_t)w.dw_splits * ck * Cout * 4);
   }
@@ -180,15 +181,16 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
                      (uintptr_t)dfeat_out % 16 == 0;
   if (fs_ok && basis_proj_grads_tc_supported(K, C)) {
     // dX goes straight into the operand image of the tcgen05 gradient kernel
-    if (ns % 4 != 0) {
+    const int group = basis_proj_grads_tc_group(ns, M);
+    if (ns % group != 0) {
       // columns of the samples that do not exist must read as finite values
-      char* last = (char*)w.dx + (size_t)(ns / 4) * 4 * ck * 4;
+      char* last = (char*)w.dx + (size_t)(ns / group) * 4 * ck * 4;
       TFGPC_CUDA(cudaMemsetAsync(last, 0, (size_t)4 * ck * 4, st));
     }
-    rc = gemm_bf16x3_grad_image(st, ns, C, Cout, g_k, w_k, w.dx, w.err);
+    rc = gemm_bf16x3_grad_image(st, ns, C, Cout, g_k, w_k, w.dx, group, w.err);
     if (rc) return rc;
     TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
-    rc = basis_proj_grads_tc(st, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
+    rc = basis_proj_grads_tc(st, group, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
                              dfeat_out, w.err);
   } else {
     rc = gemm_bf16x3(st, ns, ck, Cout, g_k, w_k, w.dx, ck, 1, 0, w.err);
