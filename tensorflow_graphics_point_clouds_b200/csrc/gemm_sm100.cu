@@ -368,7 +368,7 @@ int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int b
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  ProfScope prof(st, OUT == 1 ? "gemm_bf16x3_k_k_image"
+  ProfScope prof(st, OUT == 1 ? (B_MN ? "gemm_bf16x3_k_mn_image" : "gemm_bf16x3_k_k_image")
                               : A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
                                      : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
@@ -440,23 +440,32 @@ int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t
   const int64_t N = (int64_t)channels * 16;
   TFGPC_REQUIRE(M > 0 && channels > 0 && K > 0 && M < (int64_t)INT32_MAX && K < (int64_t)INT32_MAX,
                 "GEMM expects positive sizes below 2^31");
-  TFGPC_REQUIRE(a.major == Major::K && b.major == Major::K && channels % 2 == 0 &&
-                (uintptr_t)image % 32 == 0 && group >= 1 && group <= 4,
-                "gradient-image GEMM expects K-major operands and groups of 1 to 4 rows");
+  TFGPC_REQUIRE(a.major == Major::K && channels % 2 == 0 && (uintptr_t)image % 32 == 0 &&
+                group >= 1 && group <= 4,
+                "gradient-image GEMM expects a K-major left operand and groups of 1 to 4 rows");
+  const bool b_mn = b.major == Major::MN;
   int bn = (int)(N < kBNMax ? N : kBNMax);
-  bn = (bn + 31) / 32 * 32;
+  const int gran = b_mn ? 64 : 32;
+  bn = (bn + gran - 1) / gran * gran;
   CUtensorMap maps[5] = {};
   int rc;
   if ((rc = make_map(&maps[0], a.hi, K, M, a.ld, kBK, kBM))) return rc;
   if ((rc = make_map(&maps[1], a.mid, K, M, a.ld, kBK, kBM))) return rc;
-  if ((rc = make_map(&maps[2], b.hi, K, N, b.ld, kBK, bn))) return rc;
-  if ((rc = make_map(&maps[3], b.mid, K, N, b.ld, kBK, bn))) return rc;
+  const __nv_bfloat16* bp[2] = {b.hi, b.mid};
+  for (int i = 0; i < 2; ++i) {
+    rc = b_mn ? make_map(&maps[2 + i], bp[i], N, K, b.ld, 64, kBK)
+              : make_map(&maps[2 + i], bp[i], K, N, b.ld, kBK, bn);
+    if (rc) return rc;
+  }
   TileSchedule sch;
   sch.m_tiles = (int)((M + kBM - 1) / kBM);
   sch.n_tiles = (int)((N + bn - 1) / bn);
   sch.k_blocks = (int)((K + kBK - 1) / kBK);
   sch.k_splits = 1;
   sch.k_blocks_per_split = sch.k_blocks;
+  if (b_mn)
+    return launch<false, true, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
+                                  group);
   return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
                                  group);
 }

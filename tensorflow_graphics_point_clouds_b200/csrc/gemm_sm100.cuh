@@ -36,7 +36,7 @@ int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const Gemm
                 const GemmOperand& b, float* c, int64_t ldc, int k_splits, int64_t split_stride,
                 int* err_flag);
 
-// The same product for C = [M, channels * 16] (K-major operands), written not as
+// The same product for C = [M, channels * 16] (K-major left operand), written not as
 // fp32 but as the bf16 hi/mid operand image of the tensor-core projection
 // gradients: per group of `group` rows (1 to 4), [hi | mid][channel][128 bytes],
 // where the 16-byte chunk 2 * (row % group) + (k / 8) of a channel's line sits at
