@@ -100,7 +100,7 @@ NCU_TRAFFIC_BYTES_PER_POINT = {
     "basis_proj_split_mma": (1.318681e9 + 2.100419e9) / 262144,
     "basis_proj_grads": (4.091760e9 + 1.135269e9) / 262144,
     "basis_proj_grads_mma": (3.955412e9 + 1.121180e9) / 262144,
-    "basis_proj_grads_tc": (3.101795e9 + 0.680210e9) / 262144,
+    "basis_proj_grads_tc": (3.792681e9 + 0.670124e9) / 262144,
     "gemm_bf16x3_k_mn": (2.176700e9 + 0.255623e9) / 262144,
     "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
     "gemm_bf16x3_k_k_image": (2.149690e9 + 2.100168e9) / 262144,
