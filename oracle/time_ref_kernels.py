@@ -82,7 +82,7 @@ def main():
   out, _, _, ms = twice(lambda: ref.basis_proj(basis, feat, nb, rg))
   tb, tf = t(basis), t(feat)
   mine = ours(lambda: ops.basis_proj(tb, tf, neigh._neighbors, neigh._samples_neigh_ranges),
-              ("basis_proj",))
+              ("basis_proj", "split_features"))
   rows.append(("BasisProj [%d,%d,%d]" % (n, cin, k), ms, mine))
   _, _, _, ms = twice(lambda: ref.sampling(g_np["sp"], g_np["sb"], g_np["sk"], g_np["nc"], nb, rg, 0))
   mine = ours(lambda: pc.sample(neigh, "poisson"), ("sampling", "scan_i32"))
