@@ -102,6 +102,7 @@ NCU_TRAFFIC_BYTES_PER_POINT = {
     "basis_proj_grads_mma": (3.955412e9 + 1.121180e9) / 262144,
     "basis_proj_grads_tc": (3.792681e9 + 0.670124e9) / 262144,
     "gemm_bf16x3_k_mn": (2.176700e9 + 0.255623e9) / 262144,
+    "gemm_bf16x3_mn_k_t": (2.176700e9 + 0.255623e9) / 262144,
     "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
     "gemm_bf16x3_k_k_image": (2.149690e9 + 2.100168e9) / 262144,
     "gemm_bf16x3_k_mn_image": (2.149690e9 + 2.100168e9) / 262144,
@@ -120,7 +121,7 @@ def kernel_model(name, sizes):
     return "hbm", m * (4 * k + 8) + n * 4 * c + n * 4 + n * ck * 4
   if name in ("basis_proj_grads", "basis_proj_grads_mma", "basis_proj_grads_tc"):
     return "hbm", n * ck * 4 + m * (4 * k + 8) + n * 4 * c + n * 4 + m * 4 * k + n * 4 * c
-  if name == "gemm_bf16x3_k_mn":      # out = X W
+  if name in ("gemm_bf16x3_k_mn", "gemm_bf16x3_mn_k_t"):      # out = X W
     return "tensor", 2.0 * n * ck * co
   if name in ("gemm_bf16x3_k_k", "gemm_bf16x3_k_k_image", "gemm_bf16x3_k_mn_image"):  # dX = dOut W^T (4-byte output dominates)
     return "hbm", n * co * 4 + ck * co * 4 + n * ck * 4

@@ -64,7 +64,9 @@ struct Barriers {
 // OUT = 0: C as fp32 through TMA stores.  OUT = 1: C is the gradient of a
 // [rows, channels, 16] projection and is written as the bf16 hi/mid operand
 // image the tensor-core gradient kernel loads with one bulk copy per group of
-// four rows (basis_proj_grads_tc.cu describes the layout).
+// four rows (basis_proj_grads_tc.cu describes the layout).  OUT = 2: the map of C
+// describes C^T ([N, M] row-major): boxes are transposed on their way through
+// shared memory, for products whose natural left operand is the small matrix.
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
@@ -261,17 +263,30 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
         uint8_t* box = my_stage + (size_t)(box_iter & 1) * kOutBoxBytes;
         if (lane == 0) tma_store_wait_read<1>();  // the store that last used this box has read it
         __syncwarp();
-        float4* rowp = reinterpret_cast<float4*>(box + lane * 128);
+        if (OUT == 2) {
+          // box row i = column c0 + i of the tile, box column = this lane's row:
+          // a warp store fills one (swizzled) 128-byte row, no bank conflicts
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          rowp[q ^ (lane & 7)] =
-              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          for (int i = 0; i < 32; ++i)
+            *reinterpret_cast<uint32_t*>(box + i * 128 + ((((lane >> 2) ^ (i & 7))) << 4) +
+                                         (lane & 3) * 4) = r[i];
+        } else {
+          float4* rowp = reinterpret_cast<float4*>(box + lane * 128);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            rowp[q ^ (lane & 7)] =
+                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        }
         fence_proxy_async();
         __syncwarp();
         const int col0 = n * bn + c0;
-        if (lane == 0 && row0 < m_total && col0 < n_total && !*abort_flag)
-          tma_store_3d(&tm_c, smem_u32(box), col0, row0, sp);
+        if (lane == 0 && row0 < m_total && col0 < n_total && !*abort_flag) {
+          if (OUT == 2)
+            tma_store_3d(&tm_c, smem_u32(box), row0, col0, sp);
+          else
+            tma_store_3d(&tm_c, smem_u32(box), col0, row0, sp);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -368,7 +383,8 @@ int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int b
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  ProfScope prof(st, OUT == 1 ? (B_MN ? "gemm_bf16x3_k_mn_image" : "gemm_bf16x3_k_k_image")
+  ProfScope prof(st, OUT == 2 ? "gemm_bf16x3_mn_k_t"
+                     : OUT == 1 ? (B_MN ? "gemm_bf16x3_k_mn_image" : "gemm_bf16x3_k_k_image")
                               : A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
                                      : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
@@ -468,6 +484,31 @@ int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t
                                   group);
   return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
                                  group);
+}
+
+int gemm_bf16x3_tn(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,
+                   const GemmOperand& b, float* ct, int64_t ldct, int* err_flag) {
+  TFGPC_REQUIRE(M > 0 && N > 0 && K > 0 && M < (int64_t)INT32_MAX && N < (int64_t)INT32_MAX &&
+                K < (int64_t)INT32_MAX, "GEMM expects positive sizes below 2^31");
+  TFGPC_REQUIRE(a.major == Major::MN && b.major == Major::K,
+                "transposed-output GEMM expects an MN-major left and a K-major right operand");
+  int bn = (int)(N < kBNMax ? N : kBNMax);
+  bn = (bn + 31) / 32 * 32;
+  CUtensorMap maps[5];
+  int rc;
+  if ((rc = make_map(&maps[0], a.hi, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[1], a.mid, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[2], b.hi, K, N, b.ld, kBK, bn))) return rc;
+  if ((rc = make_map(&maps[3], b.mid, K, N, b.ld, kBK, bn))) return rc;
+  // C^T: N rows of M columns
+  if ((rc = make_map_c(&maps[4], ct, M, N, 1, ldct, 0))) return rc;
+  TileSchedule sch;
+  sch.m_tiles = (int)((M + kBM - 1) / kBM);
+  sch.n_tiles = (int)((N + bn - 1) / bn);
+  sch.k_blocks = (int)((K + kBK - 1) / kBK);
+  sch.k_splits = 1;
+  sch.k_blocks_per_split = sch.k_blocks;
+  return launch<true, false, 2>(stream, maps, M, N, bn, sch, err_flag);
 }
 
 int gemm_bf16x3(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,

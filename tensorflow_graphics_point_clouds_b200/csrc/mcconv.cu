@@ -135,6 +135,10 @@ extern "C" int tfgpc_mcconv_forward(void* stream, int K, int C, int Cout, int64_
   if (rc) return rc;
   GemmOperand a{w.x_hi, w.x_mid, ck, Major::K};
   GemmOperand b{w.w_hi, w.w_mid, (int64_t)Cout, Major::MN};  // W is [C*K, Cout]: N contiguous
+  // With at least one full tile of output features the roles are swapped,
+  // out^T = W^T * X^T with W as the (MN-major) left operand, and the tiles are
+  // transposed on their way out.
+  if (Cout >= 128) return gemm_bf16x3_tn(st, Cout, ns, ck, b, a, out, Cout, w.err);
   return gemm_bf16x3(st, ns, Cout, ck, a, b, out, Cout, 1, 0, w.err);
 }
 
