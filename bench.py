@@ -106,6 +106,7 @@ NCU_TRAFFIC_BYTES_PER_POINT = {
     "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
     "gemm_bf16x3_k_k_image": (2.149690e9 + 2.100168e9) / 262144,
     "gemm_bf16x3_k_mn_image": (2.149690e9 + 2.100168e9) / 262144,
+    "gemm_bf16x3_mn_k_image": (2.149690e9 + 2.100168e9) / 262144,
     "gemm_bf16x3_mn_mn": (2.415943e9 + 0.004868e9) / 262144,
 }
 
@@ -123,7 +124,8 @@ def kernel_model(name, sizes):
     return "hbm", n * ck * 4 + m * (4 * k + 8) + n * 4 * c + n * 4 + m * 4 * k + n * 4 * c
   if name in ("gemm_bf16x3_k_mn", "gemm_bf16x3_mn_k_t"):      # out = X W
     return "tensor", 2.0 * n * ck * co
-  if name in ("gemm_bf16x3_k_k", "gemm_bf16x3_k_k_image", "gemm_bf16x3_k_mn_image"):  # dX = dOut W^T (4-byte output dominates)
+  if name in ("gemm_bf16x3_k_k", "gemm_bf16x3_k_k_image", "gemm_bf16x3_k_mn_image",
+              "gemm_bf16x3_mn_k_image"):  # dX = dOut W^T (4-byte output dominates)
     return "hbm", n * co * 4 + ck * co * 4 + n * ck * 4
   if name == "gemm_bf16x3_mn_mn":     # dW = X^T dOut
     return "tensor", 2.0 * n * ck * co

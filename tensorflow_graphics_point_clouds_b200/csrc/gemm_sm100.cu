@@ -46,6 +46,38 @@ __device__ __forceinline__ void st_global_256(void* p, const uint4& lo, const ui
                  "r"(hi.z), "r"(hi.w) : "memory");
 }
 
+// Writes 2 channels x 16 basis functions (v[0..31]) of sample `row` into the
+// operand image of the tensor-core gradient kernel (basis_proj_grads_tc.cu).
+// The row's two chunks (k 0-7, k 8-15) of a channel share one 32-byte sector,
+// in swapped order when the channel is odd: one 256-bit store per part, and the
+// lanes of neighboring samples fill whole 128-byte lines.
+__device__ __forceinline__ void store_image_row(uint8_t* image, int channels, int group_size,
+                                                int64_t row, int ch0, const uint32_t* v) {
+  const int64_t part = (int64_t)channels * 128;   // bytes of the hi (or mid) rows of a group
+  const int64_t gi = row / group_size;
+  uint8_t* group = image + gi * (2 * part);
+  const int sl = (int)(row - gi * group_size);
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int ch = ch0 + u;
+    uint4 hv[2], mv[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int b = 16 * u + 8 * h;
+      split2_bf16(__uint_as_float(v[b]), __uint_as_float(v[b + 1]), hv[h].x, mv[h].x);
+      split2_bf16(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]), hv[h].y, mv[h].y);
+      split2_bf16(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]), hv[h].z, mv[h].z);
+      split2_bf16(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]), hv[h].w, mv[h].w);
+    }
+    const bool swap = (ch & 1) != 0;
+    const uint4 h_lo = swap ? hv[1] : hv[0], h_hi = swap ? hv[0] : hv[1];
+    const uint4 m_lo = swap ? mv[1] : mv[0], m_hi = swap ? mv[0] : mv[1];
+    uint8_t* dst = group + (int64_t)ch * 128 + (((2 * sl) ^ (ch & 6)) << 4);
+    st_global_256(dst, h_lo, h_hi);
+    st_global_256(dst + part, m_lo, m_hi);
+  }
+}
+
 struct TileSchedule {
   int m_tiles, n_tiles, k_splits;
   int k_blocks;         // ring slots over the whole reduction
@@ -230,34 +262,30 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
         if (OUT == 1) {
           // this thread holds 2 channels x 16 basis functions of row `row`
           const int64_t row = (int64_t)row0 + lane;
-          if (row < m_total && !*abort_flag) {
-            const int64_t part = (int64_t)image_channels * 128;   // bytes of the hi (or mid) rows
-            const int64_t gi = row / image_group;
-            uint8_t* group = image + gi * (2 * part);
-            const int sl = (int)(row - gi * image_group);
+          if (row < m_total && !*abort_flag)
+            store_image_row(image, image_channels, image_group, row, (n * bn + c0) / 16, r);
+          continue;
+        }
+        if (OUT == 3) {
+          // C^T tile: this thread holds 32 rows (samples c0 .. c0+31 of the tile)
+          // of column row0 + lane.  Transposed through the warp's staging box, it
+          // holds 32 consecutive columns (2 channels x 16) of sample c0 + lane.
+          uint8_t* box = my_stage;
+          __syncwarp();
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int ch = (n * bn + c0) / 16 + u;
-              // The row's two chunks (k 0-7, k 8-15) of this channel share one
-              // 32-byte sector, in swapped order when the channel is odd: one
-              // 256-bit store per part, and four lanes fill a 128-byte line.
-              uint4 hv[2], mv[2];
+          for (int i = 0; i < 32; ++i)
+            *reinterpret_cast<uint32_t*>(box + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) +
+                                         (lane & 3) * 4) = r[i];
+          __syncwarp();
+          uint32_t v[32];
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int b = 16 * u + 8 * h;
-                split2_bf16(__uint_as_float(r[b]), __uint_as_float(r[b + 1]), hv[h].x, mv[h].x);
-                split2_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]), hv[h].y, mv[h].y);
-                split2_bf16(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5]), hv[h].z, mv[h].z);
-                split2_bf16(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]), hv[h].w, mv[h].w);
-              }
-              const bool swap = (ch & 1) != 0;
-              const uint4 h_lo = swap ? hv[1] : hv[0], h_hi = swap ? hv[0] : hv[1];
-              const uint4 m_lo = swap ? mv[1] : mv[0], m_hi = swap ? mv[0] : mv[1];
-              uint8_t* dst = group + (int64_t)ch * 128 + (((2 * sl) ^ (ch & 6)) << 4);
-              st_global_256(dst, h_lo, h_hi);
-              st_global_256(dst + part, m_lo, m_hi);
-            }
+          for (int q = 0; q < 8; ++q) {
+            const uint4 t4 = *reinterpret_cast<const uint4*>(box + lane * 128 + ((q ^ (lane & 7)) << 4));
+            v[4 * q] = t4.x; v[4 * q + 1] = t4.y; v[4 * q + 2] = t4.z; v[4 * q + 3] = t4.w;
           }
+          const int64_t sample = (int64_t)n * bn + c0 + lane;
+          if (sample < n_total && !*abort_flag)
+            store_image_row(image, image_channels, image_group, sample, row0 / 16, v);
           continue;
         }
         uint8_t* box = my_stage + (size_t)(box_iter & 1) * kOutBoxBytes;
@@ -383,7 +411,7 @@ int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int b
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  ProfScope prof(st, OUT == 2 ? "gemm_bf16x3_mn_k_t"
+  ProfScope prof(st, OUT == 3 ? "gemm_bf16x3_mn_k_image" : OUT == 2 ? "gemm_bf16x3_mn_k_t"
                      : OUT == 1 ? (B_MN ? "gemm_bf16x3_k_mn_image" : "gemm_bf16x3_k_k_image")
                               : A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
                                      : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
@@ -484,6 +512,34 @@ int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t
                                   group);
   return launch<false, false, 1>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
                                  group);
+}
+
+int gemm_bf16x3_grad_image_tn(cudaStream_t stream, int channels, int64_t N, int64_t K,
+                              const GemmOperand& a, const GemmOperand& b, void* image, int group,
+                              int* err_flag) {
+  const int64_t M = (int64_t)channels * 16;
+  TFGPC_REQUIRE(channels > 0 && N > 0 && K > 0 && N < (int64_t)INT32_MAX && K < (int64_t)INT32_MAX,
+                "GEMM expects positive sizes below 2^31");
+  TFGPC_REQUIRE(a.major == Major::MN && b.major == Major::K && channels % 2 == 0 &&
+                (uintptr_t)image % 32 == 0 && group >= 1 && group <= 4,
+                "gradient-image GEMM (transposed form) expects an MN-major left and a K-major "
+                "right operand and groups of 1 to 4 rows");
+  int bn = (int)(N < kBNMax ? N : kBNMax);
+  bn = (bn + 31) / 32 * 32;
+  CUtensorMap maps[5] = {};
+  int rc;
+  if ((rc = make_map(&maps[0], a.hi, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[1], a.mid, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[2], b.hi, K, N, b.ld, kBK, bn))) return rc;
+  if ((rc = make_map(&maps[3], b.mid, K, N, b.ld, kBK, bn))) return rc;
+  TileSchedule sch;
+  sch.m_tiles = (int)((M + kBM - 1) / kBM);
+  sch.n_tiles = (int)((N + bn - 1) / bn);
+  sch.k_blocks = (int)((K + kBK - 1) / kBK);
+  sch.k_splits = 1;
+  sch.k_blocks_per_split = sch.k_blocks;
+  return launch<true, false, 3>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
+                                group);
 }
 
 int gemm_bf16x3_tn(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,

@@ -45,6 +45,13 @@ int gemm_bf16x3_grad_image(cudaStream_t stream, int64_t M, int channels, int64_t
                            const GemmOperand& a, const GemmOperand& b, void* image, int group,
                            int* err_flag);
 
+// The gradient image of C^T = (A * B^T)^T, A MN-major with M = channels * 16 rows,
+// B K-major with one row per sample: the same image as gemm_bf16x3_grad_image
+// for the product written with the roles swapped (see gemm_bf16x3_tn).
+int gemm_bf16x3_grad_image_tn(cudaStream_t stream, int channels, int64_t N, int64_t K,
+                              const GemmOperand& a, const GemmOperand& b, void* image, int group,
+                              int* err_flag);
+
 // C^T[N, M] (row-major, ldct elements per row) = (A * B^T)^T for an MN-major A
 // ([K, M] row-major) and a K-major B ([N, K] row-major): the form to use when the
 // small matrix is the natural left operand -- the tensor pipe reads an MN-major

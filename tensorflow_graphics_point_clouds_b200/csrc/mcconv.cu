@@ -43,6 +43,7 @@ struct McWs {
   float* dx;                        // [ns, C*K]    (backward)
   float* dw_part;                   // [splits, C*K, Cout] (backward)
   __nv_bfloat16* fs;                // [n_in, 2, C] split features (tensor-core projection)
+  __nv_bfloat16 *wt_hi, *wt_mid;    // [Cout, C*K]: W transposed (backward)
   int dw_splits;
   size_t bytes;
 };
@@ -62,13 +63,15 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   w.fs = nullptr;
   if (basis_proj_mma_supported(K, C)) w.fs = (__nv_bfloat16*)take((size_t)n_in * C * 4);
   w.dw_splits = 1;
-  w.g_hi = w.g_mid = nullptr; w.dx = w.dw_part = nullptr;
+  w.g_hi = w.g_mid = nullptr; w.dx = w.dw_part = nullptr; w.wt_hi = w.wt_mid = nullptr;
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     // as operand image of the tensor-core gradient kernel: one slot of 4*ck floats
     // per group of three (or four) samples
     w.dx = (float*)take((size_t)((ns + 2) / 3) * 4 * ck * 4);
+    w.wt_hi = (__nv_bfloat16*)take(ck * Cout * 2);
+    w.wt_mid = (__nv_bfloat16*)take(ck * Cout * 2);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
     w.dw_part = (float*)take((size_t)w.dw_splits * ck * Cout * 4);
   }
@@ -191,7 +194,13 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
       char* last = (char*)w.dx + (size_t)(ns / group) * 4 * ck * 4;
       TFGPC_CUDA(cudaMemsetAsync(last, 0, (size_t)4 * ck * 4, st));
     }
-    rc = gemm_bf16x3_grad_image(st, ns, C, Cout, g_k, w_k, w.dx, group, w.err);
+    // dX^T = W * dOut^T with W^T [Cout, C*K] as the MN-major left operand (the
+    // tensor pipe reads it faster than a K-major one; transposing 2 MB is free),
+    // tiles transposed back on their way into the image
+    rc = split_transpose_to_bf16(st, weights, ck, Cout, w.wt_hi, w.wt_mid);
+    if (rc) return rc;
+    GemmOperand wt_mn{w.wt_hi, w.wt_mid, ck, Major::MN};
+    rc = gemm_bf16x3_grad_image_tn(st, C, ns, Cout, wt_mn, g_k, w.dx, group, w.err);
     if (rc) return rc;
     TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
     rc = basis_proj_grads_tc(st, group, ns, M, basis, w.fs, neighbors, ranges, w.dx, dbasis_out,
