@@ -102,11 +102,11 @@ NCU_TRAFFIC_BYTES_PER_POINT = {
     "basis_proj_grads_mma": (3.955412e9 + 1.121180e9) / 262144,
     "basis_proj_grads_tc": (3.792681e9 + 0.670124e9) / 262144,
     "gemm_bf16x3_k_mn": (2.176700e9 + 0.255623e9) / 262144,
-    "gemm_bf16x3_mn_k_t": (2.176700e9 + 0.255623e9) / 262144,
+    "gemm_bf16x3_mn_k_t": (2.172271e9 + 0.255117e9) / 262144,
     "gemm_bf16x3_k_k": (2.150015e9 + 2.098627e9) / 262144,
     "gemm_bf16x3_k_k_image": (2.149690e9 + 2.100168e9) / 262144,
     "gemm_bf16x3_k_mn_image": (2.149690e9 + 2.100168e9) / 262144,
-    "gemm_bf16x3_mn_k_image": (2.149690e9 + 2.100168e9) / 262144,
+    "gemm_bf16x3_mn_k_image": (0.270630e9 + 2.103353e9) / 262144,
     "gemm_bf16x3_mn_mn": (2.415943e9 + 0.004868e9) / 262144,
 }
 
