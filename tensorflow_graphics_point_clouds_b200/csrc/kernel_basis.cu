@@ -29,6 +29,20 @@ __device__ __forceinline__ float act_bwd(float x, int act, float alpha) {
   return x > 0.0f ? 1.0f : alpha;
 }
 
+// 256-bit accesses to global memory (sm_100): a thread that owns a 64-byte row
+// then reads or writes whole 32-byte sectors instead of halves of them.
+__device__ __forceinline__ void st_global_256(float* p, const float* v) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]),
+                 "f"(v[6]), "f"(v[7]) : "memory");
+}
+
+__device__ __forceinline__ void ld_global_256(const float* p, float* v) {
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]),
+                 "=f"(v[6]), "=f"(v[7]) : "l"(p));
+}
+
 template <int D>
 __device__ __forceinline__ void pair_diff(const float* __restrict__ p_in,
                                           const float* __restrict__ p_out, int2 nb,
@@ -38,7 +52,8 @@ __device__ __forceinline__ void pair_diff(const float* __restrict__ p_in,
     diff[d] = (__ldg(p_in + (int64_t)nb.x * D + d) - __ldg(p_out + (int64_t)nb.y * D + d)) * inv_radius;
 }
 
-template <int D, int K>
+// WIDE: rows are 32-byte aligned, 256-bit accesses are allowed.
+template <int D, int K, bool WIDE>
 __global__ void __launch_bounds__(kKbThreads)
 kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __restrict__ p_out,
                     const int2* __restrict__ neigh, const float* __restrict__ pdf,
@@ -54,24 +69,29 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
     float diff[D];
     pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
     const float inv_pdf = 1.0f / __ldg(pdf + m);
-    float4* dst = reinterpret_cast<float4*>(basis + m * K);
+    float* dst = basis + m * K;
 #pragma unroll
-    for (int q = 0; q < K / 4; ++q) {
-      float v[4];
+    for (int q = 0; q < K / 8; ++q) {
+      float v[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = 4 * q + i;
+      for (int i = 0; i < 8; ++i) {
+        const int k = 8 * q + i;
         float pre = w_s[D * K + k];
 #pragma unroll
         for (int d = 0; d < D; ++d) pre = fmaf(diff[d], w_s[d * K + k], pre);
         v[i] = act_fwd(pre, act, alpha) * inv_pdf;
       }
-      dst[q] = make_float4(v[0], v[1], v[2], v[3]);
+      if (WIDE) {
+        st_global_256(dst + 8 * q, v);
+      } else {
+        reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[2 * q + 1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
     }
   }
 }
 
-template <int D, int K>
+template <int D, int K, bool WIDE>
 __global__ void __launch_bounds__(kKbThreads)
 kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
                           const float* __restrict__ p_out, const int2* __restrict__ neigh,
@@ -100,14 +120,21 @@ kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
     float diff[D];
     pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
     const float inv_pdf = 1.0f / __ldg(pdf + m);
-    const float4* src = reinterpret_cast<const float4*>(dbasis + m * K + k0);
+    const float* src = dbasis + m * K + k0;
 #pragma unroll
-    for (int q = 0; q < KT / 4; ++q) {
-      const float4 g4 = __ldg(src + q);
-      const float g[4] = {g4.x, g4.y, g4.z, g4.w};
+    for (int q = 0; q < KT / 8; ++q) {
+      float g[8];
+      if (WIDE) {
+        ld_global_256(src + 8 * q, g);
+      } else {
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(src) + 2 * q);
+        const float4 g1 = __ldg(reinterpret_cast<const float4*>(src) + 2 * q + 1);
+        g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w;
+        g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+      }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = 4 * q + i;
+      for (int i = 0; i < 8; ++i) {
+        const int k = 8 * q + i;
         float pre = w_s[D * K + k0 + k];
 #pragma unroll
         for (int d = 0; d < D; ++d) pre = fmaf(diff[d], w_s[d * K + k0 + k], pre);
@@ -173,9 +200,15 @@ extern "C" int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M, const f
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(M, kKbThreads), (unsigned)(sm_count() * 16));
   ProfScope prof(st, "kernel_basis");
-  TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK><<<grid, kKbThreads, 0, st>>>(
-      M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation, alpha,
-      basis_out)));
+  if ((uintptr_t)basis_out % 32 == 0) {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
+        M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
+        alpha, basis_out)));
+  } else {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
+        M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
+        alpha, basis_out)));
+  }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -200,9 +233,15 @@ extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
   const int kt = K < kKTile ? K : kKTile;
   dim3 grid(min(blocks_for(M, kKbThreads), (unsigned)(sm_count() * 8)), (unsigned)(K / kt));
   ProfScope prof(st, "kernel_basis_grads");
-  TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_grads_kernel<kD, kK><<<grid, kKbThreads, 0, st>>>(
-      M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation, alpha,
-      basis_grads, dw1_out, db1_out)));
+  if ((uintptr_t)basis_grads % 32 == 0) {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_grads_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
+        M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
+        alpha, basis_grads, dw1_out, db1_out)));
+  } else {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_grads_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
+        M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
+        alpha, basis_grads, dw1_out, db1_out)));
+  }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
