@@ -329,11 +329,14 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
             uint32_t v[16];
             tmem_ld_x16(taddr + 16 * q, v);
             if (sl == q) {
-              float4* dst = reinterpret_cast<float4*>(dbasis + (int64_t)m * kK);
+              // the row's 64 bytes as two whole 32-byte sectors
+              float* dst = dbasis + (int64_t)m * kK;
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              for (int i = 0; i < 2; ++i)
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             ::"l"(dst + 8 * i), "r"(v[8 * i]), "r"(v[8 * i + 1]), "r"(v[8 * i + 2]),
+                               "r"(v[8 * i + 3]), "r"(v[8 * i + 4]), "r"(v[8 * i + 5]),
+                               "r"(v[8 * i + 6]), "r"(v[8 * i + 7]) : "memory");
             }
           }
         }
@@ -409,8 +412,8 @@ int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const
                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
                         const void* image, float* dbasis, float* dfeat, int* err_flag) {
   TFGPC_REQUIRE((uintptr_t)image % 16 == 0 && (uintptr_t)fs % 16 == 0 && (uintptr_t)basis % 16 == 0 &&
-                (uintptr_t)dbasis % 16 == 0 && (uintptr_t)dfeat % 16 == 0,
-                "tensor-core projection gradients expect 16-byte aligned buffers");
+                (uintptr_t)dbasis % 32 == 0 && (uintptr_t)dfeat % 16 == 0,
+                "tensor-core projection gradients expect 16-byte aligned buffers (dbasis: 32)");
   if (group == 4)
     return launch_grads_tc<4>(st, ns, M, basis, fs, neigh, ranges, image, dbasis, dfeat, err_flag);
   TFGPC_REQUIRE(group == 3, "tensor-core projection gradients work on groups of 3 or 4 samples");

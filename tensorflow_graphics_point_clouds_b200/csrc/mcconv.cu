@@ -184,7 +184,7 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   // dX[ns, C*K] = dOut[ns, Cout] * W^T: B rows are W's rows, reduction over Cout
   GemmOperand g_k{w.g_hi, w.g_mid, (int64_t)Cout, Major::K};
   GemmOperand w_k{w.w_hi, w.w_mid, (int64_t)Cout, Major::K};
-  const bool fs_ok = w.fs && (uintptr_t)features % 16 == 0 && (uintptr_t)dbasis_out % 16 == 0 &&
+  const bool fs_ok = w.fs && (uintptr_t)features % 16 == 0 && (uintptr_t)dbasis_out % 32 == 0 &&
                      (uintptr_t)dfeat_out % 16 == 0;
   if (fs_ok && basis_proj_grads_tc_supported(K, C)) {
     // dX goes straight into the operand image of the tcgen05 gradient kernel
