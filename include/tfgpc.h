@@ -342,6 +342,20 @@ int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K,
                      const float* a, int a_transposed, const float* b,
                      int b_transposed, float* c, void* ws, size_t ws_bytes);
 
+/* ---- small blocking reads -------------------------------------------------
+ * No counterpart in the reference (it reads its counts with cudaMemcpy behind
+ * cudaEventSynchronize, scan_alg_kernels.cu.cc:259-265).  Copies `bytes`
+ * (4 .. 4096, a multiple of 4) from device memory to host_dst [host] and
+ * blocks on the stream.  The values travel through a page of mapped pinned
+ * host memory written by a kernel, not through a copy engine, so the read
+ * does not queue behind bulk transfers that other streams have in flight.
+ * The blocking entries (tfgpc_find_neighbors_count, tfgpc_sampling_count,
+ * tfgpc_mcconv_status) read their results the same way; the first such call
+ * of a host thread on a device allocates that page (4 KB) and keeps it.
+ * tfgpc_find_neighbors_count_static allocates nothing and uses cudaMemcpy. */
+int tfgpc_read_device(void* stream, const void* device_src, size_t bytes,
+                      void* host_dst);
+
 /* ---- per-launch timing ---------------------------------------------------
  * No counterpart in the reference (its DEBUG_INFO timing blocks do not
  * compile, store_neighbors_kernels.cu.cc:256-269).  While enabled on the

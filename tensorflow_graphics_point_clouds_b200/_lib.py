@@ -59,6 +59,7 @@ SYMBOLS = {
     "tfgpc_kernel_basis_grads": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
+    "tfgpc_read_device": c_int,
     "tfgpc_profile_enable": c_int,
     "tfgpc_profile_collect": c_int,
 }

@@ -57,6 +57,11 @@ struct ProfScope {
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Blocking read of a few values (4 .. 4096 bytes, a multiple of 4) from device
+// memory, through mapped pinned host memory instead of a copy engine: it does
+// not queue behind bulk transfers on other streams.
+int read_small(cudaStream_t st, const void* dev_src, size_t bytes, void* host_dst);
+
 inline unsigned blocks_for(int64_t work, int per_block) {
   int64_t b = (work + per_block - 1) / per_block;
   return (unsigned)(b < 1 ? 1 : b);

@@ -230,8 +230,8 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
 extern "C" int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out) {
   TFGPC_REQUIRE(ws && status_out, "mcconv_status got a null pointer");
   int flag = 0;
-  TFGPC_CUDA(cudaMemcpyAsync(&flag, ws, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-  TFGPC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  int rc = read_small((cudaStream_t)stream, ws, sizeof(int), &flag);
+  if (rc) return rc;
   *status_out = flag ? TFGPC_ETIMEOUT : TFGPC_OK;
   if (flag) return fail(TFGPC_ETIMEOUT, "a bounded wait inside the tensor-core GEMM ran out");
   return TFGPC_OK;

@@ -171,7 +171,7 @@ extern "C" size_t tfgpc_find_neighbors_workspace_bytes(int64_t ns) {
   return align_up((size_t)(scan_block_sums_elems(ns) + 1) * sizeof(int64_t), 256) + 256;
 }
 
-extern "C" int tfgpc_find_neighbors_count(
+static int find_neighbors_count_impl(bool mapped_read,
     void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
@@ -203,13 +203,32 @@ extern "C" int tfgpc_find_neighbors_count(
   rc = inclusive_scan_i32(st, ranges_out, ranges_out, ns, block_sums, total_dev);
   if (rc) return rc;
   int64_t total = 0;
-  TFGPC_CUDA(cudaMemcpyAsync(&total, total_dev, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-  TFGPC_CUDA(cudaStreamSynchronize(st));
+  if (mapped_read) {
+    rc = read_small(st, total_dev, sizeof(int64_t), &total);
+    if (rc) return rc;
+  } else {
+    // the entry that must not allocate: a plain copy, which may queue behind
+    // bulk transfers of other streams
+    TFGPC_CUDA(cudaMemcpyAsync(&total, total_dev, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    TFGPC_CUDA(cudaStreamSynchronize(st));
+  }
   if (total > (int64_t)INT32_MAX)
     return fail(TFGPC_EINVAL, "FindNeighbors found %lld pairs; the int32 ranges of the op "
                 "contract hold at most 2^31-1", (long long)total);
   *total_out = total;
   return TFGPC_OK;
+}
+
+extern "C" int tfgpc_find_neighbors_count(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
+    void* ws, size_t ws_bytes, int64_t* total_out) {
+  return find_neighbors_count_impl(true, stream, D, ns, samples, samples_batch_ids, n, points,
+                                  point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                  inv_cell_sizes, inv_radii, max_neighs, ranges_out, ws, ws_bytes,
+                                  total_out);
 }
 
 extern "C" int tfgpc_find_neighbors_fill(
@@ -340,8 +359,8 @@ extern "C" int tfgpc_find_neighbors_count_static(
                 kStaticScratchBytes, (long long)ns);
   // Nothing in the scratch has to start at zero: the scan overwrites every tile
   // sum and the total before it reads them, so stale contents are harmless.
-  return tfgpc_find_neighbors_count(stream, D, ns, samples, samples_batch_ids, n, points,
-                                    point_keys, ds, batch_size, num_cells, scaled_aabb_min,
-                                    inv_cell_sizes, inv_radii, max_neighs, ranges_out, scratch,
-                                    kStaticScratchBytes, total_out);
+  return find_neighbors_count_impl(false, stream, D, ns, samples, samples_batch_ids, n, points,
+                                  point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                  inv_cell_sizes, inv_radii, max_neighs, ranges_out, scratch,
+                                  kStaticScratchBytes, total_out);
 }

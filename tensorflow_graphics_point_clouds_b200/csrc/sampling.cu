@@ -227,8 +227,8 @@ extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, co
     if (rc) return rc;
   }
   int64_t totals[2] = {0, 0};
-  TFGPC_CUDA(cudaMemcpyAsync(totals, w.totals, sizeof(totals), cudaMemcpyDeviceToHost, st));
-  TFGPC_CUDA(cudaStreamSynchronize(st));
+  rc = read_small(st, w.totals, sizeof(totals), totals);
+  if (rc) return rc;
   *num_samples_out = mode == 0 ? totals[1] : totals[0];
   return TFGPC_OK;
 }

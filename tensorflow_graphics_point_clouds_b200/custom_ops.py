@@ -244,6 +244,22 @@ def _bp_args(basis, features, neighbors, ranges):
   return basis, features, neighbors, ranges
 
 
+def read_device(values):
+  """Blocking read of a small device tensor (at most 4096 bytes of int32,
+  int64 or float32) into a CPU tensor, through mapped host memory instead of a
+  copy engine: it does not wait behind bulk transfers on other streams."""
+  v = values.contiguous()
+  if not v.is_cuda:
+    return v.clone()
+  nbytes = v.numel() * v.element_size()
+  if nbytes == 0 or nbytes > 4096 or nbytes % 4 != 0:
+    return v.cpu()
+  out = torch.empty(v.shape, dtype=v.dtype)
+  _lib.check(_lib.lib().tfgpc_read_device(_stream(), ptr(v), c_sz(nbytes),
+                                          ctypes.c_void_p(out.data_ptr())))
+  return out
+
+
 def _bp_scratch(k, c, feat):
   """Scratch of the tensor-core BasisProj kernels (None where the shape has none)."""
   nbytes = _lib.lib().tfgpc_basis_proj_workspace_bytes(c_int(k), c_int(c), c_i64(feat.shape[0]))

@@ -36,7 +36,7 @@ class PointCloud:
     self._batch_ids = torch.as_tensor(batch_ids, device=self._points.device).to(
         torch.int32).contiguous()
     if batch_size is None:
-      batch_size = int(self._batch_ids.max().item()) + 1
+      batch_size = int(ops.read_device(self._batch_ids.max().reshape(1))[0]) + 1
     self._batch_size = int(batch_size)
     self._dimension = self._points.shape[1]
     self._aabb = None
@@ -62,7 +62,7 @@ class Grid:
     sizes = self._aabb_max - self._aabb_min
     batch_num_cells = torch.ceil(sizes / self._cell_sizes).to(torch.int32)
     self._num_cells = torch.clamp(batch_num_cells.max(dim=0).values, min=1).to(torch.int32)
-    self._num_cells_host = self._num_cells.cpu()
+    self._num_cells_host = ops.read_device(self._num_cells)
     # custom_ops_wrapper.py:37-43
     self._scaled_aabb_min = self._aabb_min / self._cell_sizes
     self._inv_cell_sizes = torch.reciprocal(self._cell_sizes)
