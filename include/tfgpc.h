@@ -266,6 +266,21 @@ int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n,
                          const int32_t* neighbors, int64_t M,
                          const int32_t* ranges, void* ws, size_t ws_bytes,
                          int64_t* num_samples_out);
+/* tfgpc_sampling_count for SYMMETRIC neighbor lists: point j is listed for
+ * point i exactly when i is listed for j, which holds for every self
+ * neighborhood that tfgpc_find_neighbors_* builds with max_neighs = 0 (the
+ * only input pylib/pc/sampling.py:123-150 and PointHierarchy.py:83-93 give
+ * the op).  Same arguments and same result; the Poisson passes then walk only
+ * the lists of the points they take.  With lists that are not symmetric the
+ * selection differs from the reference's and may vary from run to run. */
+int tfgpc_sampling_count_symmetric(void* stream, int D, int mode, int64_t n,
+                                   const float* points,
+                                   const int32_t* batch_ids,
+                                   const int64_t* point_keys,
+                                   const int32_t* num_cells,
+                                   const int32_t* neighbors, int64_t M,
+                                   const int32_t* ranges, void* ws,
+                                   size_t ws_bytes, int64_t* num_samples_out);
 int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
                          const float* points, const int32_t* batch_ids,
                          const int64_t* point_keys, const int32_t* num_cells,

@@ -50,6 +50,7 @@ SYMBOLS = {
     "tfgpc_basis_proj_grads_ws": c_int,
     "tfgpc_sampling_workspace_bytes": c_sz,
     "tfgpc_sampling_count": c_int,
+    "tfgpc_sampling_count_symmetric": c_int,
     "tfgpc_sampling_store": c_int,
     "tfgpc_mcconv_workspace_bytes": c_sz,
     "tfgpc_mcconv_forward": c_int,

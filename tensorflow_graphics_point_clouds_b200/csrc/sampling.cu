@@ -126,6 +126,68 @@ poisson_pass_kernel(int pass, int64_t n, const int64_t* __restrict__ num_runs,
   }
 }
 
+// The same pass for SYMMETRIC neighbor lists (j is listed for i exactly when i
+// is listed for j, as in every self neighborhood found without a neighbor
+// limit).  "None of my neighbors is taken" then equals "no taken point lists
+// me", so a taken point marks its whole list as blocked and every other point
+// costs one flag read instead of a walk over its list: the work drops from the
+// sum of all list lengths to the lists of the taken points, and the
+// point-after-point chain inside a crowded cell to one flag read per 32 points.
+// During a pass only the warp that owns a cell writes flags of that cell's
+// points (cells of equal parity are never neighbors), so the flags of the 32
+// points in flight are kept in a register mask and patched from the marks the
+// warp itself makes.
+template <int D>
+__global__ void __launch_bounds__(kSmpThreads)
+poisson_pass_symmetric_kernel(int pass, int64_t n, const int64_t* __restrict__ num_runs,
+                              const int32_t* __restrict__ starts,
+                              const int64_t* __restrict__ keys,
+                              const int32_t* __restrict__ num_cells,
+                              const int2* __restrict__ neigh, const int32_t* __restrict__ ranges,
+                              int32_t* __restrict__ used, int32_t* blocked) {
+  const int64_t runs = *num_runs;
+  const int lane = lane_id();
+  int nc[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) nc[d] = __ldg(num_cells + d);
+  const int64_t warps = ((int64_t)gridDim.x * kSmpThreads) >> 5;
+  for (int64_t r = ((int64_t)blockIdx.x * kSmpThreads + threadIdx.x) >> 5; r < runs; r += warps) {
+    const int begin = __ldg(starts + r);
+    const int end = (r + 1 < runs) ? __ldg(starts + r + 1) : (int)n;
+    int64_t aux = __ldg(keys + begin);
+    bool mine = true;
+#pragma unroll
+    for (int d = D - 1; d >= 0; --d) {  // grid_utils.h:110-125
+      int c = (int)(aux % nc[d]);
+      aux /= nc[d];
+      mine = mine && ((c & 1) == ((pass >> d) & 1));
+    }
+    if (!mine) continue;
+    for (int q0 = begin; q0 < end; q0 += 32) {
+      const int q = q0 + lane;
+      unsigned open = __ballot_sync(0xffffffffu, q < end && __ldcg(blocked + q) == 0);
+      while (open) {
+        const int t = __ffs(open) - 1;
+        const int taken = q0 + t;
+        open &= open - 1u;
+        if (lane == 0) used[taken] = 1;
+        const int a = taken ? __ldg(ranges + taken - 1) : 0;
+        const int e = __ldg(ranges + taken);
+        unsigned marked = 0u;
+        for (int m = a + lane; m < e; m += 32) {
+          const int j = __ldg(&neigh[m].x);
+          if (j >= 0 && j < n && j != taken) {
+            __stcg(blocked + j, 1);
+            if (j >= q0 && j < q0 + 32) marked |= 1u << (j - q0);
+          }
+        }
+        open &= ~__reduce_or_sync(0xffffffffu, marked);
+      }
+      __syncwarp();  // the marks of this group are visible to the next group's reads
+    }
+  }
+}
+
 template <int D>
 __global__ void store_poisson_kernel(int64_t n, const int32_t* __restrict__ used,
                                      const int32_t* __restrict__ used_scan,
@@ -183,11 +245,11 @@ using namespace tfgpc;
 
 extern "C" size_t tfgpc_sampling_workspace_bytes(int64_t n) { return sampling_ws_bytes(n); }
 
-extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, const float* points,
-                                    const int32_t* batch_ids, const int64_t* point_keys,
-                                    const int32_t* num_cells, const int32_t* neighbors, int64_t M,
-                                    const int32_t* ranges, void* ws, size_t ws_bytes,
-                                    int64_t* num_samples_out) {
+static int sampling_count_impl(bool symmetric, void* stream, int D, int mode, int64_t n,
+                               const float* points, const int32_t* batch_ids,
+                               const int64_t* point_keys, const int32_t* num_cells,
+                               const int32_t* neighbors, int64_t M, const int32_t* ranges,
+                               void* ws, size_t ws_bytes, int64_t* num_samples_out) {
   int rc = check_smp_args(D, mode, n, M);
   if (rc) return rc;
   TFGPC_REQUIRE(num_samples_out, "SamplingOp got a null pointer");
@@ -216,11 +278,20 @@ extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, co
   if (mode == 0) {
     TFGPC_CUDA(cudaMemsetAsync(w.used, 0, sizeof(int32_t) * (size_t)n, st));
     unsigned grid = min(blocks_for(n, kSmpThreads / 32), (unsigned)(sm_count() * 32));
+    // the blocked flags of the symmetric variant live in used_scan, which
+    // nothing else touches before the scan below overwrites it
+    if (symmetric) TFGPC_CUDA(cudaMemsetAsync(w.used_scan, 0, sizeof(int32_t) * (size_t)n, st));
     for (int pass = 0; pass < (1 << D); ++pass) {
       ProfScope prof(st, "sampling_poisson_pass");
-      TFGPC_DIM_SWITCH(D, poisson_pass_kernel<kD><<<grid, kSmpThreads, 0, st>>>(
-          pass, n, w.totals, w.starts, point_keys, num_cells, (const int2*)neighbors, ranges,
-          w.used));
+      if (symmetric) {
+        TFGPC_DIM_SWITCH(D, poisson_pass_symmetric_kernel<kD><<<grid, kSmpThreads, 0, st>>>(
+            pass, n, w.totals, w.starts, point_keys, num_cells, (const int2*)neighbors, ranges,
+            w.used, w.used_scan));
+      } else {
+        TFGPC_DIM_SWITCH(D, poisson_pass_kernel<kD><<<grid, kSmpThreads, 0, st>>>(
+            pass, n, w.totals, w.starts, point_keys, num_cells, (const int2*)neighbors, ranges,
+            w.used));
+      }
       TFGPC_LAUNCH_CHECK();
     }
     rc = inclusive_scan_i32(st, w.used, w.used_scan, n, w.block_sums, w.totals + 1);
@@ -231,6 +302,25 @@ extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, co
   if (rc) return rc;
   *num_samples_out = mode == 0 ? totals[1] : totals[0];
   return TFGPC_OK;
+}
+
+extern "C" int tfgpc_sampling_count(void* stream, int D, int mode, int64_t n, const float* points,
+                                    const int32_t* batch_ids, const int64_t* point_keys,
+                                    const int32_t* num_cells, const int32_t* neighbors, int64_t M,
+                                    const int32_t* ranges, void* ws, size_t ws_bytes,
+                                    int64_t* num_samples_out) {
+  return sampling_count_impl(false, stream, D, mode, n, points, batch_ids, point_keys, num_cells,
+                             neighbors, M, ranges, ws, ws_bytes, num_samples_out);
+}
+
+extern "C" int tfgpc_sampling_count_symmetric(void* stream, int D, int mode, int64_t n,
+                                              const float* points, const int32_t* batch_ids,
+                                              const int64_t* point_keys,
+                                              const int32_t* num_cells, const int32_t* neighbors,
+                                              int64_t M, const int32_t* ranges, void* ws,
+                                              size_t ws_bytes, int64_t* num_samples_out) {
+  return sampling_count_impl(true, stream, D, mode, n, points, batch_ids, point_keys, num_cells,
+                             neighbors, M, ranges, ws, ws_bytes, num_samples_out);
 }
 
 extern "C" int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n, const float* points,

@@ -302,10 +302,14 @@ def basis_proj_grads(basis_neighbors, pt_features, neighbors, sample_neigh_indic
   return dbasis, dfeat
 
 
-def sampling(points, batch_ids, point_keys, num_cells, neighbors, sample_neigh_indices, mode):
+def sampling(points, batch_ids, point_keys, num_cells, neighbors, sample_neigh_indices, mode,
+             symmetric=False):
   """Sampling (sampling/cc/ops/sampling_ops.cpp:33-53).  mode 0 = Poisson disk,
   1 = cell average.  Returns (sample_pts [S, D], sample_batch_ids [S],
-  sample_indices [S] or an unwritten [1] tensor for mode 1)."""
+  sample_indices [S] or an unwritten [1] tensor for mode 1).  symmetric=True
+  promises that point j is listed for point i exactly when i is listed for j
+  (a self neighborhood found without a neighbor limit): same result, and the
+  Poisson passes only walk the lists of the points they take."""
   points, batch_ids, nc = _f32(points), _i32(batch_ids), _i32(num_cells)
   keys = point_keys.contiguous()
   neighbors, ranges = _i32(neighbors), _i32(sample_neigh_indices)
@@ -328,7 +332,9 @@ def sampling(points, batch_ids, point_keys, num_cells, neighbors, sample_neigh_i
   total = c_i64(0)
   common = (_stream(), c_int(d), c_int(int(mode)), c_i64(n), ptr(points), ptr(batch_ids),
             ptr(keys), ptr(nc))
-  _lib.check(_lib.lib().tfgpc_sampling_count(
+  count = (_lib.lib().tfgpc_sampling_count_symmetric if symmetric
+           else _lib.lib().tfgpc_sampling_count)
+  _lib.check(count(
       *common, ptr(neighbors), c_i64(neighbors.shape[0]), ptr(ranges), ptr(ws), c_sz(nbytes),
       ctypes.byref(total)))
   s = int(total.value)

@@ -160,7 +160,9 @@ def sample(neighborhood, sample_mode='poisson'):
   g = neighborhood._grid
   pts, bids, idx = ops.sampling(g._sorted_points, g._sorted_batch_ids, g._sorted_keys,
                                 g._num_cells, neighborhood._neighbors,
-                                neighborhood._samples_neigh_ranges, mode)
+                                neighborhood._samples_neigh_ranges, mode,
+                                symmetric=(neighborhood._equal_samples
+                                           and neighborhood.max_neighbors == 0))
   if mode == 0:
     idx = g._sorted_indices[idx.to(torch.int64)]
   else:

@@ -265,6 +265,44 @@ def test_sampling_poisson_and_average(d, cell):
     else:
       assert idx is None
       close(cloud._points.cpu().numpy(), rp)
+  # pc.sample takes the symmetric-list entry for a self neighborhood; the entry
+  # that assumes nothing about the lists must select the same points
+  for symmetric in (False, True):
+    p2, b2, i2 = ops.sampling(g._sorted_points, g._sorted_batch_ids, g._sorted_keys, g._num_cells,
+                              nb._neighbors, nb._samples_neigh_ranges, 0, symmetric=symmetric)
+    rp, rb, ri = pr.sample(nb_ref, 0)
+    assert np.array_equal(g._sorted_indices[i2.long()].cpu().numpy(), ri)
+    assert np.array_equal(p2.cpu().numpy(), rp)
+    assert np.array_equal(b2.cpu().numpy(), rb)
+
+
+def test_sampling_poisson_truncated_lists():
+  """Lists cut by a neighbor limit are not symmetric: pc.sample must then select
+  like the reference kernel, which looks only at a point's own list
+  (count_sampling_pd_kernels.cu.cc:59-106)."""
+  rng = np.random.default_rng(77)
+  pts, bid = random_cloud(rng, 3, 5000, 3)
+  g_ref, g = grid_pair(pts, bid, 3, 0.15)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.15, max_neighbors=6)
+  rp, rb, ri = pr.sample(nb_ref, 0)
+  cloud, idx = pc.sample(nb, 'poisson')
+  assert np.array_equal(idx.cpu().numpy(), ri)
+  assert np.array_equal(cloud._points.cpu().numpy(), rp)
+
+
+def test_sampling_poisson_crowded_cells():
+  """Cells holding thousands of points with thousands of neighbors each: the
+  case where the symmetric-list passes and the general ones differ most in
+  the work they do."""
+  pts, bid = synthetic.gaussian_mixture_clouds(2, 12000, seed=11)
+  g_ref, g = grid_pair(pts, bid, 2, 0.1)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.1)
+  rp, rb, ri = pr.sample(nb_ref, 0)
+  for symmetric in (False, True):
+    p2, b2, i2 = ops.sampling(g._sorted_points, g._sorted_batch_ids, g._sorted_keys, g._num_cells,
+                              nb._neighbors, nb._samples_neigh_ranges, 0, symmetric=symmetric)
+    assert np.array_equal(g._sorted_indices[i2.long()].cpu().numpy(), ri)
+    assert np.array_equal(b2.cpu().numpy(), rb)
 
 
 @pytest.mark.parametrize("n,scale", [(6, 1), (100, 5)])
