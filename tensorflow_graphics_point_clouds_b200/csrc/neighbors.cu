@@ -18,6 +18,7 @@
 namespace tfgpc {
 
 constexpr int kFnThreads = 256;
+constexpr int kFnSpan = 8;  // consecutive samples one warp takes at a time
 
 template <int D>
 __host__ __device__ constexpr int num_offsets() {
@@ -107,7 +108,14 @@ find_neighbors_kernel(int64_t ns, const float* __restrict__ samples,
   const int lane = lane_id();
   const unsigned lt_mask = (1u << lane) - 1u;
   const int64_t warps = ((int64_t)gridDim.x * kFnThreads) >> 5;
-  for (int64_t s = ((int64_t)blockIdx.x * kFnThreads + threadIdx.x) >> 5; s < ns; s += warps) {
+  // A warp takes kFnSpan consecutive samples at a time.  Samples that follow one
+  // another in memory mostly share their cell (always, when the samples are
+  // the sorted points themselves), and then the candidate ranges of the
+  // previous sample are kept instead of being searched again.
+  int prev_cell[D], prev_b = -1;
+  int2 my_range[kChunks];
+  for (int64_t s = (((int64_t)blockIdx.x * kFnThreads + threadIdx.x) >> 5) * kFnSpan; s < ns;
+       s += ((s + 1) % kFnSpan) ? 1 : (warps - 1) * kFnSpan + 1) {
     float sp[D], smin[D];
     int cell[D];
     const int b = __ldg(sbatch + s);
@@ -119,12 +127,19 @@ find_neighbors_kernel(int64_t ns, const float* __restrict__ samples,
       smin[d] = __ldg(smin_all + (int64_t)bs * D + d);
     }
     cell_of<D>(sp, smin, g, cell);
-    int2 my_range[kChunks];
+    bool same = b_ok && b == prev_b;
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      int code = c * 32 + lane;
-      my_range[c] = (b_ok && code < kOff) ? candidate_range<D>(code, cell, b, g, keys, ds)
-                                          : make_int2(0, 0);
+    for (int d = 0; d < D; ++d) same = same && cell[d] == prev_cell[d];
+    if (!same) {
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        int code = c * 32 + lane;
+        my_range[c] = (b_ok && code < kOff) ? candidate_range<D>(code, cell, b, g, keys, ds)
+                                            : make_int2(0, 0);
+      }
+      prev_b = b_ok ? b : -1;
+#pragma unroll
+      for (int d = 0; d < D; ++d) prev_cell[d] = cell[d];
     }
     int count = 0;
     int64_t out_base = 0;
@@ -191,7 +206,8 @@ static int find_neighbors_count_impl(bool mapped_read,
   cudaStream_t st = (cudaStream_t)stream;
   int64_t* block_sums = (int64_t*)ws;
   int64_t* total_dev = block_sums + scan_block_sums_elems(ns);
-  unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  unsigned grid = min(blocks_for((ns + kFnSpan - 1) / kFnSpan, kFnThreads / 32),
+                      (unsigned)(sm_count() * 32));
   {
   ProfScope prof(st, "find_neighbors_count");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, false><<<grid, kFnThreads, 0, st>>>(
@@ -245,7 +261,8 @@ extern "C" int tfgpc_find_neighbors_fill(
                 scaled_aabb_min && inv_cell_sizes && inv_radii && ranges && neigh_out,
                 "FindNeighbors got a null pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  unsigned grid = min(blocks_for(ns, kFnThreads / 32), (unsigned)(sm_count() * 32));
+  unsigned grid = min(blocks_for((ns + kFnSpan - 1) / kFnSpan, kFnThreads / 32),
+                      (unsigned)(sm_count() * 32));
   ProfScope prof(st, "find_neighbors_fill");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, true><<<grid, kFnThreads, 0, st>>>(
       ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
