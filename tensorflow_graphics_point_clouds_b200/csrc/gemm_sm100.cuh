@@ -28,7 +28,9 @@ struct GemmOperand {
 
 // C = A * B^T over k in [0, K).  With k_splits > 1 the reduction range is cut
 // into k_splits slices and slice s writes its partial result to
-// C + s * split_stride (the caller sums the slices).  M, N, K are the logical
+// C + s * split_stride (the caller sums the slices); with split_stride 0 the
+// slices are added into the one C instead (zeroed first; the order of the
+// additions is not fixed).  M, N, K are the logical
 // sizes; edges are handled by TMA zero fill and masked stores.
 // err_flag (device int, zero-initialised by the caller) is set to 1 if a
 // bounded wait inside the kernel ran out.

@@ -41,7 +41,6 @@ struct McWs {
   __nv_bfloat16 *w_hi, *w_mid;      // [C*K, Cout]
   __nv_bfloat16 *g_hi, *g_mid;      // [ns, Cout]   (backward)
   float* dx;                        // [ns, C*K]    (backward)
-  float* dw_part;                   // [splits, C*K, Cout] (backward)
   __nv_bfloat16* fs;                // [n_in, 2, C] split features (tensor-core projection)
   __nv_bfloat16 *wt_hi, *wt_mid;    // [Cout, C*K]: W transposed (backward)
   int dw_splits;
@@ -63,7 +62,7 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   w.fs = nullptr;
   if (basis_proj_mma_supported(K, C)) w.fs = (__nv_bfloat16*)take((size_t)n_in * C * 4);
   w.dw_splits = 1;
-  w.g_hi = w.g_mid = nullptr; w.dx = w.dw_part = nullptr; w.wt_hi = w.wt_mid = nullptr;
+  w.g_hi = w.g_mid = nullptr; w.dx = nullptr; w.wt_hi = w.wt_mid = nullptr;
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
@@ -73,7 +72,6 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
     w.wt_hi = (__nv_bfloat16*)take(ck * Cout * 2);
     w.wt_mid = (__nv_bfloat16*)take(ck * Cout * 2);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
-    w.dw_part = (float*)take((size_t)w.dw_splits * ck * Cout * 4);
   }
   w.bytes = (size_t)(p - (char*)ws);
   return w;
@@ -222,9 +220,9 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   // as their row index, i.e. they are MN-major
   GemmOperand x_mn{w.x_hi, w.x_mid, ck, Major::MN};
   GemmOperand g_mn{w.g_hi, w.g_mid, (int64_t)Cout, Major::MN};
-  rc = gemm_bf16x3(st, ck, Cout, ns, x_mn, g_mn, w.dw_part, Cout, w.dw_splits, ck * Cout, w.err);
-  if (rc) return rc;
-  return reduce_splits(st, w.dw_part, w.dw_splits, ck * Cout, ck * Cout, dweights_out);
+  // the reduction over the samples is cut into slices (see gemm_pick_k_splits)
+  // that the GEMM adds into dweights_out
+  return gemm_bf16x3(st, ck, Cout, ns, x_mn, g_mn, dweights_out, Cout, w.dw_splits, 0, w.err);
 }
 
 extern "C" int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out) {
@@ -241,9 +239,8 @@ extern "C" int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out
 
 extern "C" size_t tfgpc_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 1024;
-  const int splits = gemm_pick_k_splits(M, N, K);
   return 1024 + 2 * align_up((size_t)M * K * 2, 1024) + 2 * align_up((size_t)N * K * 2, 1024) +
-         (splits > 1 ? align_up((size_t)splits * M * N * 4, 1024) : 0) + 1024;
+         1024;
 }
 
 extern "C" int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K, const float* a,
@@ -264,7 +261,6 @@ extern "C" int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K, c
   __nv_bfloat16* a_mid = (__nv_bfloat16*)p; p += align_up((size_t)M * K * 2, 1024);
   __nv_bfloat16* b_hi = (__nv_bfloat16*)p; p += align_up((size_t)N * K * 2, 1024);
   __nv_bfloat16* b_mid = (__nv_bfloat16*)p; p += align_up((size_t)N * K * 2, 1024);
-  float* part = (float*)p;
   TFGPC_CUDA(cudaMemsetAsync(err, 0, sizeof(int), st));
   int rc = split_to_bf16(st, a, M * K, a_hi, a_mid);
   if (rc) return rc;
@@ -274,9 +270,6 @@ extern "C" int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K, c
   // or, transposed, [N,K] (K-major)
   GemmOperand ao{a_hi, a_mid, a_transposed ? M : K, a_transposed ? Major::MN : Major::K};
   GemmOperand bo{b_hi, b_mid, b_transposed ? K : N, b_transposed ? Major::K : Major::MN};
-  const int splits = gemm_pick_k_splits(M, N, K);
-  if (splits <= 1) return gemm_bf16x3(st, M, N, K, ao, bo, c, N, 1, 0, err);
-  rc = gemm_bf16x3(st, M, N, K, ao, bo, part, N, splits, M * N, err);
-  if (rc) return rc;
-  return reduce_splits(st, part, splits, M * N, M * N, c);
+  // several slices of the reduction are added into c by the GEMM itself
+  return gemm_bf16x3(st, M, N, K, ao, bo, c, N, gemm_pick_k_splits(M, N, K), 0, err);
 }

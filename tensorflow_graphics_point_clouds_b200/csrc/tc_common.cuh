@@ -82,6 +82,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// The same box added (fp32, round to nearest) to what the tensor holds.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int x,
+                                                  int y, int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");

@@ -27,6 +27,24 @@ def test_matmul_f32_layouts(at, bt, m, n, k):
   close(got.cpu().numpy(), ref, rel=1e-4)
 
 
+def test_matmul_f32_long_reduction():
+  """The shape of the layer's weight-gradient product at full batch size: the
+  reduction runs over 2^19 samples.  Tensor cores accumulate by truncation, so
+  the error of one accumulator grows with the number of terms it takes (7e-4
+  when the reduction was cut into 9 slices); the library cuts it into slices of
+  2048 terms.  Checked against fp64 on the device."""
+  import torch
+  gen = torch.Generator(device="cuda").manual_seed(5)
+  m, n, k = 256, 128, 1 << 19
+  a = torch.randn((k, m), generator=gen, device="cuda")           # [K, M]: a transposed
+  b = torch.randn((k, n), generator=gen, device="cuda")           # [K, N]
+  got = mcconv.matmul_f32(a, b, a_transposed=True, b_transposed=False)
+  ref = torch.zeros((m, n), dtype=torch.float64, device="cuda")
+  for i in range(0, k, 1 << 16):
+    ref += a[i:i + (1 << 16)].double().T @ b[i:i + (1 << 16)].double()
+  close(got.cpu().numpy(), ref.cpu().numpy(), rel=1e-4)
+
+
 def mc_case(rng, c, k, cout, n_pts=3000, n_smp=700, radius=0.25, b=3):
   pts, bid = random_cloud(rng, b, n_pts, 3)
   smp, sbid = random_cloud(rng, b, n_smp, 3)
