@@ -296,7 +296,8 @@ int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
  * pair of a tcgen05 tensor-core GEMM (three bf16 passes, fp32 accumulate).
  * weights [C*K, Cout] row-major in the projection's own reduction order
  * (row c*K + k; for num_mlps == 1 this is MCConv's final weight matrix as
- * stored), out [ns, Cout].  Cout must be a multiple of 4.
+ * stored), out [ns, Cout].  Cout must be a multiple of 8
+ * (16-byte rows of the bf16 weight operand).
  * Backward: out_grads [ns, Cout] -> dbasis_out [M, K], dfeat_out [n_in, C],
  * dweights_out [C*K, Cout] (all overwritten).  x_in_workspace != 0 tells it
  * that `ws` still holds the projection written by the forward call for the
@@ -345,6 +346,33 @@ int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
                              int activation, float alpha,
                              const float* basis_grads, float* dw1_out,
                              float* db1_out);
+
+/* ---- KPConv and PointConv bases --------------------------------------------
+ * The per-pair basis values of the other two convolutions of pylib/pc/layers,
+ * which feed the same BasisProj (+ weight product) as the MCConv basis.
+ *
+ * tfgpc_kp_basis replaces the op chain of KPConv.py:194-212 (rigid kernel
+ * points): diff as above, basis[m, k] = weighting(|diff - kernel_points[k]|,
+ * sigma) for k < num_kernel_points and 0 for the padding columns up to K
+ * (the tf.pad of KPConv.py:199-212).  interpolation 0 = linear,
+ * max(0, 1 - dist / sigma) (KPConv.py:28-40); 1 = gaussian,
+ * exp(-(dist / (sigma / 3))^2) (:43-56).  kernel_points [num_kernel_points, D]
+ * as the layer holds them (already scaled by 0.75, KPConv.py:129).
+ *
+ * tfgpc_pointconv_pdf replaces PointConv.py:168-183: per sample the largest
+ * density among its pairs (pairs of sample s end at ranges[s]), then per pair
+ * out[m] = relu(pdf[m] / max * w1 + b1) . w2 + b2 with w1, b1, w2 [16], b2 [1].
+ * The PointConv basis is then tfgpc_kernel_basis with inv_radius 1, pdf_out as
+ * its density and the layer's non-linearity (PointConv.py:160-166, 186). */
+int tfgpc_kp_basis(void* stream, int D, int K, int num_kernel_points, int64_t M,
+                   const float* points_in, const float* points_out,
+                   const int32_t* neighbors, const float* kernel_points,
+                   float inv_radius, float sigma, int interpolation,
+                   float* basis_out);
+int tfgpc_pointconv_pdf(void* stream, int64_t ns, int64_t M,
+                        const int32_t* ranges, const float* pdf,
+                        const float* w1, const float* b1, const float* w2,
+                        const float* b2, float* pdf_out);
 
 /* ---- fp32 matrix product on the tensor cores -----------------------------
  * c[M,N] = op(a) * op(b) in fp32 accuracy (three bf16 passes), the tf.matmul

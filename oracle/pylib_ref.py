@@ -188,3 +188,72 @@ def mcconv_backward(features, basis, neigh, wf, x, d_out):
                                          neigh.original_neigh_ids, neigh.ranges,
                                          dx.astype(F32))
   return d_wf, d_basis, d_feat, dx.astype(F32)
+
+
+# ---- KPConv and PointConv (test infrastructure like the rest of this file) ----
+
+def _projected_conv(basis, features, neigh, weights):
+  """basis_proj followed by the [Ns, Cin*K] x [Cin*K, Cout] product both layers
+  end with (KPConv.py:218-230, PointConv.py:189-200)."""
+  x = orc.basis_proj(basis, features, neigh.original_neigh_ids, neigh.ranges)
+  ns = x.shape[0]
+  return (x.reshape(ns, -1).astype(np.float64) @ weights.astype(np.float64)).astype(F32), x
+
+
+def kpconv_basis(points_in, points_out, neigh, kernel_points, radius, sigma=1.0,
+                 interpolation='linear'):
+  """KPConv.py:194-197 with the weightings of :28-56.  kernel_points are the
+  layer's points after the 0.75 scaling of :129.  Returns [M, K] unpadded."""
+  ids = neigh.original_neigh_ids
+  diff = ((points_in[ids[:, 0]] - points_out[ids[:, 1]]) / F32(radius)).astype(F32)
+  dist = np.linalg.norm(diff[:, None, :] - kernel_points[None, :, :].astype(F32),
+                        axis=2).astype(F32)
+  if interpolation == 'linear':
+    return np.maximum(F32(1) - dist / F32(sigma), F32(0)).astype(F32)
+  s = F32(sigma) / F32(3)
+  return np.exp(-(dist / s) ** 2).astype(F32)
+
+
+def kpconv_forward(features, points_in, points_out, neigh, kernel_points, weights, radius,
+                   sigma=1.0, interpolation='linear'):
+  """Rigid KPConv (KPConv.py:171-230): the zero padding of the basis and its
+  removal (:199-221) cancel, so the unpadded basis is projected directly."""
+  k = kernel_points.shape[0]
+  basis = kpconv_basis(points_in, points_out, neigh, kernel_points, radius, sigma,
+                       interpolation)
+  pad = next(c for c in (8, 16, 32, 64) if k <= c)
+  padded = np.zeros((basis.shape[0], pad), F32)
+  padded[:, :k] = basis
+  x = orc.basis_proj(padded, features, neigh.original_neigh_ids, neigh.ranges)[:, :, :k]
+  ns = x.shape[0]
+  return (x.reshape(ns, -1).astype(np.float64) @ weights.astype(np.float64)).astype(F32)
+
+
+def pointconv_pdf(pdf, neigh, w1, b1, w2, b2):
+  """PointConv.py:173-183: density over the largest density of the sample's
+  pairs, then relu(x w1 + b1) w2 + b2."""
+  sample = neigh.original_neigh_ids[:, 1]
+  mx = np.full(len(neigh.ranges), -np.inf, F32)
+  np.maximum.at(mx, sample, pdf.astype(F32))
+  cur = (pdf / mx[sample]).astype(F32).reshape(-1, 1)
+  hid = np.maximum(cur @ w1.reshape(1, 16).astype(F32) + b1.reshape(1, 16), 0).astype(F32)
+  return (hid @ w2.reshape(16, 1).astype(F32) + b2.reshape(1, 1)).astype(F32).reshape(-1)
+
+
+def pointconv_forward(features, points_in, points_out, neigh, pdf, hidden_w, hidden_b, weights,
+                      pdf_weights, pdf_biases, non_linearity='relu'):
+  """PointConv.py:160-200 with the kernel inputs of :266-272 (differences not
+  divided by the radius)."""
+  ids = neigh.original_neigh_ids
+  diff = (points_in[ids[:, 0]] - points_out[ids[:, 1]]).astype(F32)
+  hid = (diff @ hidden_w.astype(F32) + hidden_b.reshape(1, -1)).astype(F32)
+  if non_linearity == 'relu':
+    hid = np.maximum(hid, 0)
+  elif non_linearity == 'elu':
+    hid = np.where(hid > 0, hid, np.expm1(hid)).astype(F32)
+  else:
+    hid = leaky_relu(hid)
+  scale = pointconv_pdf(pdf, neigh, pdf_weights[0], pdf_biases[0], pdf_weights[1],
+                        pdf_biases[1])
+  basis = (hid / scale.reshape(-1, 1)).astype(F32)
+  return _projected_conv(basis, features, neigh, weights)[0], basis

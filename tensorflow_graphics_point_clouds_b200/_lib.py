@@ -58,6 +58,8 @@ SYMBOLS = {
     "tfgpc_mcconv_status": c_int,
     "tfgpc_kernel_basis": c_int,
     "tfgpc_kernel_basis_grads": c_int,
+    "tfgpc_kp_basis": c_int,
+    "tfgpc_pointconv_pdf": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
     "tfgpc_read_device": c_int,

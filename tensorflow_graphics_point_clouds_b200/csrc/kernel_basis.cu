@@ -164,6 +164,101 @@ kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
   }
 }
 
+// Kernel-point correlation of KPConv (KPConv.py:194-212): per neighbor pair
+//   basis[m, k] = weighting(|diff - kp[k]|, sigma)   for k < num_kp, 0 above
+// with weighting = max(0, 1 - dist / sigma) (linear, KPConv.py:28-40) or
+// exp(-(dist / (sigma / 3))^2) (gaussian, :43-56).  The columns from num_kp up to
+// K are the zero padding the reference adds with tf.pad to reach a basis count
+// the projection accepts.
+constexpr int kMaxKernelPoints = 64;
+
+template <int D, int K, bool WIDE>
+__global__ void __launch_bounds__(kKbThreads)
+kp_basis_kernel(int64_t M, int num_kp, const float* __restrict__ p_in,
+                const float* __restrict__ p_out, const int2* __restrict__ neigh,
+                const float* __restrict__ kernel_points, float inv_radius, float sigma,
+                int interpolation, float* __restrict__ basis) {
+  __shared__ float kp_s[kMaxKernelPoints * D];
+  for (int i = threadIdx.x; i < num_kp * D; i += kKbThreads) kp_s[i] = __ldg(kernel_points + i);
+  __syncthreads();
+  const float gauss_sigma = sigma / 3.0f;
+  for (int64_t m = (int64_t)blockIdx.x * kKbThreads + threadIdx.x; m < M;
+       m += (int64_t)gridDim.x * kKbThreads) {
+    const int2 nb = __ldg(neigh + m);
+    float diff[D];
+    pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
+    float* dst = basis + m * K;
+#pragma unroll
+    for (int q = 0; q < K / 8; ++q) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = 8 * q + i;
+        float w = 0.0f;
+        if (k < num_kp) {
+          float d2 = 0.0f;
+#pragma unroll
+          for (int d = 0; d < D; ++d) {
+            const float t = diff[d] - kp_s[k * D + d];
+            d2 = fmaf(t, t, d2);
+          }
+          const float dist = sqrtf(d2);
+          if (interpolation == 0) {
+            w = fmaxf(1.0f - dist / sigma, 0.0f);
+          } else {
+            const float r = dist / gauss_sigma;
+            w = expf(-(r * r));
+          }
+        }
+        v[i] = w;
+      }
+      if (WIDE) {
+        st_global_256(dst + 8 * q, v);
+      } else {
+        reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[2 * q + 1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    }
+  }
+}
+
+// Density transform of PointConv (PointConv.py:168-183): per sample the largest
+// density among its neighbor pairs, then per pair
+//   out[m] = sum_j relu(pdf[m] / max * w1[j] + b1[j]) * w2[j] + b2      (j < 16)
+// One warp owns one sample; its pairs are contiguous (ranges holds their end).
+constexpr int kPdfHidden = 16;
+
+__global__ void __launch_bounds__(kKbThreads)
+pointconv_pdf_kernel(int64_t ns, const int32_t* __restrict__ ranges,
+                     const float* __restrict__ pdf, const float* __restrict__ w1,
+                     const float* __restrict__ b1, const float* __restrict__ w2,
+                     const float* __restrict__ b2, float* __restrict__ out) {
+  __shared__ float par[3 * kPdfHidden + 1];
+  for (int i = threadIdx.x; i < 3 * kPdfHidden + 1; i += kKbThreads)
+    par[i] = i < kPdfHidden ? __ldg(w1 + i)
+             : i < 2 * kPdfHidden ? __ldg(b1 + i - kPdfHidden)
+             : i < 3 * kPdfHidden ? __ldg(w2 + i - 2 * kPdfHidden) : __ldg(b2);
+  __syncthreads();
+  const int lane = lane_id();
+  const int64_t warps = ((int64_t)gridDim.x * kKbThreads) >> 5;
+  for (int64_t s = ((int64_t)blockIdx.x * kKbThreads + threadIdx.x) >> 5; s < ns; s += warps) {
+    const int a = s ? __ldg(ranges + s - 1) : 0;
+    const int e = __ldg(ranges + s);
+    float mx = -INFINITY;
+    for (int m = a + lane; m < e; m += 32) mx = fmaxf(mx, __ldg(pdf + m));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int m = a + lane; m < e; m += 32) {
+      const float x = __ldg(pdf + m) / mx;
+      float acc = 0.0f;
+#pragma unroll
+      for (int j = 0; j < kPdfHidden; ++j)
+        acc = fmaf(fmaxf(fmaf(x, par[j], par[kPdfHidden + j]), 0.0f), par[2 * kPdfHidden + j], acc);
+      out[m] = acc + par[3 * kPdfHidden];
+    }
+  }
+}
+
 int check_kb_args(const char* op, int D, int K, int64_t M, int act) {
   TFGPC_REQUIRE(valid_dims(D), "%s expects a valid number of dimension (got %d)", op, D);
   TFGPC_REQUIRE(K == 8 || K == 16 || K == 32 || K == 64,
@@ -242,6 +337,54 @@ extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
         alpha, basis_grads, dw1_out, db1_out)));
   }
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_kp_basis(void* stream, int D, int K, int num_kernel_points, int64_t M,
+                              const float* points_in, const float* points_out,
+                              const int32_t* neighbors, const float* kernel_points,
+                              float inv_radius, float sigma, int interpolation,
+                              float* basis_out) {
+  int rc = check_kb_args("KPBasis", D, K, M, 0);
+  if (rc) return rc;
+  TFGPC_REQUIRE(num_kernel_points >= 1 && num_kernel_points <= K,
+                "KPBasis expects 1 <= kernel points <= basis functions");
+  TFGPC_REQUIRE(interpolation == 0 || interpolation == 1,
+                "KPBasis expects interpolation 0 (linear) or 1 (gaussian)");
+  TFGPC_REQUIRE(sigma > 0.0f && inv_radius > 0.0f, "KPBasis expects a positive sigma and radius");
+  if (M == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(points_in && points_out && neighbors && kernel_points && basis_out,
+                "KPBasis got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0, "KPBasis expects a 16-byte aligned output");
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned grid = min(blocks_for(M, kKbThreads), (unsigned)(sm_count() * 16));
+  ProfScope prof(st, "kp_basis");
+  if ((uintptr_t)basis_out % 32 == 0) {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kp_basis_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
+        M, num_kernel_points, points_in, points_out, (const int2*)neighbors, kernel_points,
+        inv_radius, sigma, interpolation, basis_out)));
+  } else {
+    TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kp_basis_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
+        M, num_kernel_points, points_in, points_out, (const int2*)neighbors, kernel_points,
+        inv_radius, sigma, interpolation, basis_out)));
+  }
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_pointconv_pdf(void* stream, int64_t ns, int64_t M, const int32_t* ranges,
+                                   const float* pdf, const float* w1, const float* b1,
+                                   const float* w2, const float* b2, float* pdf_out) {
+  TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && M >= 0 && M <= (int64_t)INT32_MAX,
+                "PointConvPdf expects 0 <= ns, M < 2^31");
+  if (ns == 0 || M == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(ranges && pdf && w1 && b1 && w2 && b2 && pdf_out,
+                "PointConvPdf got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned grid = min(blocks_for(ns, kKbThreads / 32), (unsigned)(sm_count() * 16));
+  ProfScope prof(st, "pointconv_pdf");
+  pointconv_pdf_kernel<<<grid, kKbThreads, 0, st>>>(ns, ranges, pdf, w1, b1, w2, b2, pdf_out);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

@@ -81,8 +81,8 @@ int check_mc_args(const char* op, int K, int C, int Cout, int64_t ns, int64_t n_
   TFGPC_REQUIRE(valid_basis(K), "%s expects a valid number of basis functions.", op);
   TFGPC_REQUIRE(valid_features(C), "%s expects a valid number of input features, between 1 and 8 "
                 "or multiple of 8", op);
-  TFGPC_REQUIRE(Cout > 0 && Cout % 4 == 0, "%s expects a number of output features that is a "
-                "multiple of 4", op);
+  TFGPC_REQUIRE(Cout > 0 && Cout % 8 == 0, "%s expects a number of output features that is a "
+                "multiple of 8", op);
   TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && n_in >= 0 && n_in < (int64_t)INT32_MAX &&
                 M >= 0 && M <= (int64_t)INT32_MAX, "%s expects 0 <= ns, n_in, M < 2^31", op);
   return TFGPC_OK;

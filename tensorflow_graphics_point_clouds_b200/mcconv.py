@@ -217,3 +217,176 @@ class MCConv:
     dwf = (dwd.unsqueeze(0) if self.num_mlps == 1
            else blocks_of_dense_grad(dwd, self.num_mlps, self.cin, self.hidden))
     return dfeat, dw1, db1, dwf
+
+
+# ---- KPConv and PointConv: other bases on the same projection + weight product
+
+def _basis_count(k):
+  """Smallest basis count the projection accepts that holds k functions
+  (the padding rule of KPConv.py:199-212)."""
+  for cand in (8, 16, 32, 64):
+    if k <= cand:
+      return cand
+  raise _lib.TfgpcError(1, "at most 64 basis functions are supported")
+
+
+def _pad_weights(w, cin, k, k_pad, cout_pad):
+  """[cin*k, cout] -> [cin*k_pad, cout_pad] with zero rows for the padding
+  basis functions and zero columns up to a multiple of 8."""
+  cout = w.shape[1]
+  wp = torch.zeros((cin, k_pad, cout_pad), dtype=torch.float32, device=w.device)
+  wp[:, :k, :cout] = w.reshape(cin, k, cout)
+  return wp.reshape(cin * k_pad, cout_pad)
+
+
+def kp_basis(points_in, points_out, neighbors, kernel_points, radius, sigma, k_pad,
+             interpolation='linear'):
+  """basis[m, k] = weighting(|diff_m - kernel_points[k]|, sigma), zero for the
+  padding columns (tfgpc_kp_basis; KPConv.py:194-212)."""
+  points_in, points_out = _f32(points_in), _f32(points_out)
+  kernel_points, neighbors = _f32(kernel_points), _i32(neighbors)
+  num_kp, d = kernel_points.shape
+  m = neighbors.shape[0]
+  basis = torch.empty((m, k_pad), dtype=torch.float32, device=points_in.device)
+  _lib.check(_lib.lib().tfgpc_kp_basis(
+      _stream(), c_int(d), c_int(k_pad), c_int(num_kp), c_i64(m), ptr(points_in),
+      ptr(points_out), ptr(neighbors), ptr(kernel_points), ctypes.c_float(1.0 / float(radius)),
+      ctypes.c_float(float(sigma)), c_int({'linear': 0, 'gaussian': 1}[interpolation]),
+      ptr(basis)))
+  return basis
+
+
+def pointconv_pdf(pdf, ranges, w1, b1, w2, b2):
+  """Per pair relu(pdf / max over the sample * w1 + b1) . w2 + b2
+  (tfgpc_pointconv_pdf; PointConv.py:168-183)."""
+  pdf, ranges = _f32(pdf), _i32(ranges)
+  w1, b1 = _f32(w1).reshape(-1), _f32(b1).reshape(-1)
+  w2, b2 = _f32(w2).reshape(-1), _f32(b2).reshape(-1)
+  if w1.numel() != 16 or b1.numel() != 16 or w2.numel() != 16 or b2.numel() != 1:
+    raise _lib.TfgpcError(1, "PointConv's density transform has 16 hidden units")
+  out = torch.empty_like(pdf)
+  _lib.check(_lib.lib().tfgpc_pointconv_pdf(
+      _stream(), c_i64(ranges.shape[0]), c_i64(pdf.shape[0]), ptr(ranges), ptr(pdf), ptr(w1),
+      ptr(b1), ptr(w2), ptr(b2), ptr(out)))
+  return out
+
+
+class _ProjectedConv:
+  """Shared part of the layers below: neighborhood, projection + weight
+  product on a padded weight matrix, explicit backward for features and
+  weights."""
+
+  def _setup(self, cin, k, cout):
+    self.cin, self.k, self.cout = int(cin), int(k), int(cout)
+    self.k_pad = _basis_count(self.k)
+    self.cout_pad = (self.cout + 7) // 8 * 8
+    self._op = None
+    self._saved = None
+
+  def _neighborhood(self, point_cloud_in, point_cloud_out, radius, neighborhood):
+    if neighborhood is not None:
+      return neighborhood
+    from . import pc
+    grid = pc.Grid(point_cloud_in, radius)
+    return pc.Neighborhood(grid, radius, point_cloud_out)
+
+  def _project(self, basis, features, neigh, weights, ns, keep_for_backward):
+    if self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward:
+      self._op = ProjectionGemm(self.k_pad, self.cin, self.cout_pad, ns, features.device,
+                                backward=keep_for_backward)
+    wp = _pad_weights(_f32(weights), self.cin, self.k, self.k_pad, self.cout_pad)
+    out = self._op.forward(basis, _f32(features), neigh._original_neigh_ids,
+                           neigh._samples_neigh_ranges, wp)
+    if keep_for_backward:
+      self._saved = (neigh, basis, _f32(features), wp)
+    return out[:, :self.cout] if self.cout_pad != self.cout else out
+
+  def _backward(self, out_grads):
+    neigh, basis, features, wp = self._saved
+    g = _f32(out_grads)
+    if self.cout_pad != self.cout:
+      g = torch.nn.functional.pad(g, (0, self.cout_pad - self.cout))
+    dbasis, dfeat, dwp = self._op.backward(basis, features, neigh._original_neigh_ids,
+                                           neigh._samples_neigh_ranges, wp, g)
+    dw = dwp.reshape(self.cin, self.k_pad, self.cout_pad)[:, :self.k, :self.cout]
+    return dbasis, dfeat, dw.reshape(self.cin * self.k, self.cout).contiguous()
+
+
+class KPConv(_ProjectedConv):
+  """Rigid kernel-point convolution (KPConv.py:59-296).  kernel_points [K, D]
+  are the layer's points before the 0.75 scaling of KPConv.py:129; weights
+  [K * C_in, C_out] in the reference's layout (row c * K + k)."""
+
+  def __init__(self, kernel_points, weights, num_features_in, kp_interpolation='linear'):
+    self.kernel_points = _f32(kernel_points) * 0.75
+    self.weights = _f32(weights)
+    self.interpolation = kp_interpolation
+    self._setup(num_features_in, self.kernel_points.shape[0], self.weights.shape[1])
+
+  def forward(self, features, point_cloud_in, point_cloud_out, conv_radius, neighborhood=None,
+              kernel_influence_dist=None, keep_for_backward=True):
+    neigh = self._neighborhood(point_cloud_in, point_cloud_out, conv_radius, neighborhood)
+    # KPConv.py:283-288: sigma is 1 unless an influence distance is given
+    sigma = 1.0 if kernel_influence_dist is None else kernel_influence_dist / conv_radius
+    basis = kp_basis(point_cloud_in._points, point_cloud_out._points, neigh._original_neigh_ids,
+                     self.kernel_points, conv_radius, sigma, self.k_pad, self.interpolation)
+    return self._project(basis, features, neigh, self.weights,
+                         point_cloud_out._points.shape[0], keep_for_backward)
+
+  def backward(self, out_grads):
+    """(d_features, d_weights) of the last forward call; the kernel points of the
+    rigid layer are not trained."""
+    _, dfeat, dw = self._backward(out_grads)
+    return dfeat, dw
+
+
+# PointConv.py:27-31: name -> (activation code, slope) of tfgpc_kernel_basis
+NON_LINEARITIES = {'relu': (0, 0.0), 'lrelu': (0, 0.2), 'leakyrelu': (0, 0.2),
+                   'leaky_relu': (0, 0.2), 'elu': (1, 0.0)}
+
+
+class PointConv(_ProjectedConv):
+  """PointConv layer (PointConv.py:37-281): one hidden layer on the unscaled
+  point differences, divided by a learned transform of the normalised density.
+  hidden_w [D, H], hidden_b [1, H] or [H], weights [H * C_in, C_out];
+  pdf_weights = (w1 [1, 16], w2 [16, 1]), pdf_biases = (b1 [1, 16], b2 [1, 1])."""
+
+  def __init__(self, hidden_w, hidden_b, weights, pdf_weights, pdf_biases, num_features_in,
+               non_linearity_type='relu'):
+    self.hidden_w, self.hidden_b = _f32(hidden_w), _f32(hidden_b).reshape(-1)
+    self.weights = _f32(weights)
+    self.pdf_weights = [_f32(w) for w in pdf_weights]
+    self.pdf_biases = [_f32(b) for b in pdf_biases]
+    self.activation, self.alpha = NON_LINEARITIES[non_linearity_type.lower()]
+    hidden = self.hidden_w.shape[1]
+    if hidden not in (8, 16, 32, 64):
+      # BasisProj accepts these sizes only (basis_proj_ops.cpp:99-103)
+      raise _lib.TfgpcError(1, "BasisProjOp expects a valid number of basis functions.")
+    self._setup(num_features_in, hidden, self.weights.shape[1])
+
+  def forward(self, features, point_cloud_in, point_cloud_out, radius, neighborhood=None,
+              bandwidth=0.2, keep_for_backward=True):
+    neigh = self._neighborhood(point_cloud_in, point_cloud_out, radius, neighborhood)
+    pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
+    scale = pointconv_pdf(pdf, neigh._samples_neigh_ranges, self.pdf_weights[0],
+                          self.pdf_biases[0], self.pdf_weights[1], self.pdf_biases[1])
+    # PointConv.py:272: the kernel input is the point difference itself (radius 1)
+    basis = kernel_basis(point_cloud_in._points, point_cloud_out._points,
+                         neigh._original_neigh_ids, scale, self.hidden_w, self.hidden_b, 1.0,
+                         self.activation, self.alpha)
+    out = self._project(basis, features, neigh, self.weights,
+                        point_cloud_out._points.shape[0], keep_for_backward)
+    if keep_for_backward:
+      self._kernel_inputs = (point_cloud_in, point_cloud_out, scale)
+    return out
+
+  def backward(self, out_grads):
+    """(d_features, d_hidden_w, d_hidden_b, d_weights) of the last forward call.
+    The 50 parameters of the density transform get no gradient here."""
+    dbasis, dfeat, dw = self._backward(out_grads)
+    neigh = self._saved[0]
+    pc_in, pc_out, scale = self._kernel_inputs
+    dhw, dhb = kernel_basis_grads(pc_in._points, pc_out._points, neigh._original_neigh_ids,
+                                  scale, self.hidden_w, self.hidden_b, 1.0, dbasis,
+                                  self.activation, self.alpha)
+    return dfeat, dhw, dhb, dw

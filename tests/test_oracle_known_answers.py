@@ -255,3 +255,71 @@ def test_cell_average_matches_running_mean(cell, b):
   ref.append(cur / cnt); refb.append(g.sorted_batch_ids[-1])
   np.testing.assert_allclose(p, np.array(ref), atol=1e-4)
   assert np.array_equal(pb, np.array(refb))
+
+
+def _layer_case(rng, d, n_pts, n_smp, b, radius):
+  pts, bid = random_cloud(rng, b, n_pts, d)
+  smp, sbid = random_cloud(rng, b, n_smp, d)
+  r = np.repeat(F32(radius), d)
+  g = pr.Grid(pts, bid, b, r)
+  nb = pr.Neighborhood(g, r, smp, sbid)
+  return pts, smp, nb
+
+
+def _sum_per_sample(per_pair, ranges):
+  """The reference tests' integration loop: rows of a sample are contiguous."""
+  ends = np.concatenate(([0], ranges))
+  return np.stack([per_pair[ends[i]:ends[i + 1]].sum(axis=0) for i in range(len(ranges))])
+
+
+@pytest.mark.parametrize("n_pts,n_smp,feats,b,radius,num_kp,interp",
+                         [(200, 20, (1, 3), 16, 0.7, 5, 'linear'),
+                          (400, 40, (3, 3), 8, 0.7, 5, 'linear'),
+                          (400, 10, (3, 1), 1, np.sqrt(3), 5, 'linear'),
+                          (400, 40, (8, 4), 4, 0.7, 15, 'gaussian')])
+def test_kpconv_matches_numpy_layer(n_pts, n_smp, feats, b, radius, num_kp, interp):
+  """kernel_point_conv_test.py:53-99 (sizes from its parameter list): distances
+  to the kernel points, linear weights, per-sample sums, product with the
+  weights, all in float64."""
+  rng = np.random.default_rng(n_pts + num_kp)
+  pts, smp, nb = _layer_case(rng, 3, n_pts, n_smp, b, radius)
+  feat = rng.uniform(size=(n_pts, feats[0])).astype(F32)
+  kp = (rng.normal(size=(num_kp, 3)) * 0.4).astype(F32)
+  w = rng.normal(size=(num_kp * feats[0], feats[1])).astype(F32)
+  out = pr.kpconv_forward(feat, pts, smp, nb, kp, w, radius, 1.0, interp)
+  ids = nb.original_neigh_ids
+  diff = (pts[ids[:, 0]].astype(np.float64) - smp[ids[:, 1]]) / radius
+  dist = np.linalg.norm(diff[:, None, :] - kp[None].astype(np.float64), axis=2)
+  kw = np.maximum(1 - dist, 0) if interp == 'linear' else np.exp(-(dist / (1 / 3)) ** 2)
+  per_pair = feat[ids[:, 0]][:, :, None].astype(np.float64) * kw[:, None, :]
+  x = _sum_per_sample(per_pair, nb.ranges)
+  ref = x.reshape(n_smp, -1) @ w.astype(np.float64)
+  np.testing.assert_allclose(out, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("n_pts,n_smp,feats,b,radius,hidden,d",
+                         [(2000, 200, (3, 3), 16, 0.7, 8, 2), (2000, 200, (1, 3), 16, 0.7, 8, 3),
+                          (4000, 100, (3, 1), 1, np.sqrt(3), 16, 3),
+                          (2000, 200, (3, 3), 16, 0.7, 8, 4)])
+def test_pointconv_matches_numpy_layer(n_pts, n_smp, feats, b, radius, hidden, d):
+  """point_conv_test.py:38-113 (sizes from its parameter list)."""
+  rng = np.random.default_rng(n_pts + hidden + d)
+  pts, smp, nb = _layer_case(rng, d, n_pts, n_smp, b, radius)
+  feat = rng.uniform(size=(n_pts, feats[0])).astype(F32)
+  pdf = nb.get_pdf()
+  hw = rng.normal(size=(d, hidden)).astype(F32)
+  hb = (rng.normal(size=(1, hidden)) * 0.1).astype(F32)
+  w = rng.normal(size=(hidden * feats[0], feats[1])).astype(F32)
+  pw = [rng.normal(size=(1, 16)).astype(F32), np.abs(rng.normal(size=(16, 1))).astype(F32)]
+  pb = [np.abs(rng.normal(size=(1, 16))).astype(F32), np.ones((1, 1), F32)]
+  out, _ = pr.pointconv_forward(feat, pts, smp, nb, pdf, hw, hb, w, pw, pb, 'relu')
+  ids = nb.original_neigh_ids
+  mx = np.array([pdf[ids[:, 1] == s].max() if (ids[:, 1] == s).any() else 1.0
+                 for s in range(n_smp)])
+  cur = (pdf.astype(np.float64) / mx[ids[:, 1]]).reshape(-1, 1)
+  cur = np.maximum(cur @ pw[0] + pb[0], 0) @ pw[1] + pb[1]
+  latent = np.maximum((pts[ids[:, 0]].astype(np.float64) - smp[ids[:, 1]]) @ hw + hb, 0) / cur
+  per_pair = feat[ids[:, 0]][:, :, None].astype(np.float64) * latent[:, None, :]
+  x = _sum_per_sample(per_pair, nb.ranges)
+  ref = x.reshape(n_smp, -1) @ w.astype(np.float64)
+  np.testing.assert_allclose(out, ref, rtol=1e-3, atol=1e-3)
