@@ -374,6 +374,28 @@ int tfgpc_pointconv_pdf(void* stream, int64_t ns, int64_t M,
                         const float* w1, const float* b1, const float* w2,
                         const float* b2, float* pdf_out);
 
+/* ---- pooling and the bias of Conv1x1 ----------------------------------------
+ * tfgpc_neighborhood_pool replaces the gather + unsorted_segment_max / _mean
+ * of pylib/pc/layers/Pooling.py:148-162 (MaxPooling, AveragePooling):
+ * out[s, c] = max or mean over the pairs of sample s of features[nbr.x, c];
+ * features [n_in,C], neighbors [M,2], ranges [ns] (end offsets), out [ns,C].
+ * tfgpc_global_pool replaces the segment ops over the batch ids of
+ * Pooling.py:51-57 (GlobalMaxPooling) and :90-96 (GlobalAveragePooling):
+ * features [n,C], batch_ids [n], out [batch_size,C].  mode 0 = max, 1 = mean;
+ * an empty segment gives the lowest float (max), as TensorFlow does, or 0 (mean).
+ * tfgpc_add_bias adds bias [C] to every row of x [n,C] in place: with
+ * tfgpc_matmul_f32 it is Conv1x1.py:97. */
+int tfgpc_neighborhood_pool(void* stream, int mode, int C, int64_t ns,
+                            int64_t n_in, int64_t M, const float* features,
+                            const int32_t* neighbors, const int32_t* ranges,
+                            float* out);
+size_t tfgpc_global_pool_workspace_bytes(int64_t batch_size);
+int tfgpc_global_pool(void* stream, int mode, int C, int64_t n,
+                      int64_t batch_size, const float* features,
+                      const int32_t* batch_ids, float* out, void* ws,
+                      size_t ws_bytes);
+int tfgpc_add_bias(void* stream, int64_t n, int C, float* x, const float* bias);
+
 /* ---- fp32 matrix product on the tensor cores -----------------------------
  * c[M,N] = op(a) * op(b) in fp32 accuracy (three bf16 passes), the tf.matmul
  * of MCConv.py:187-191 as a stand-alone call.  a is [M,K] row-major, or

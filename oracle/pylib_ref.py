@@ -257,3 +257,39 @@ def pointconv_forward(features, points_in, points_out, neigh, pdf, hidden_w, hid
                         pdf_biases[1])
   basis = (hid / scale.reshape(-1, 1)).astype(F32)
   return _projected_conv(basis, features, neigh, weights)[0], basis
+
+
+# ---- pooling and 1x1 convolution ------------------------------------------------
+
+LOWEST = np.finfo(F32).min   # what unsorted_segment_max writes for an empty segment
+
+
+def segment_pool(data, segment_ids, num_segments, mode):
+  """tf.math.unsorted_segment_max / _mean as the pooling layers call them
+  (Pooling.py:54-57, 93-96, 155-158): mode 'max' or 'avg'."""
+  data = np.asarray(data, F32)
+  if mode == 'max':
+    out = np.full((num_segments, data.shape[1]), LOWEST, F32)
+    np.maximum.at(out, segment_ids, data)
+    return out
+  out = np.zeros((num_segments, data.shape[1]), np.float64)
+  np.add.at(out, segment_ids, data)
+  cnt = np.bincount(segment_ids, minlength=num_segments).astype(np.float64)
+  return (out / np.maximum(cnt, 1)[:, None]).astype(F32)
+
+
+def neighborhood_pool(features, neigh, mode):
+  """Pooling.py:148-158: gather the neighbors' rows, pool them per sample."""
+  ids = neigh.original_neigh_ids
+  return segment_pool(features[ids[:, 0]], ids[:, 1], len(neigh.ranges), mode)
+
+
+def global_pool(features, batch_ids, batch_size, mode):
+  """Pooling.py:51-57 and :90-96."""
+  return segment_pool(features, batch_ids, batch_size, mode)
+
+
+def conv1x1(features, weights, bias):
+  """Conv1x1.py:97."""
+  return (features.astype(np.float64) @ weights.astype(np.float64)
+          + bias.reshape(1, -1)).astype(F32)

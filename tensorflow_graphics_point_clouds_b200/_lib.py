@@ -60,6 +60,10 @@ SYMBOLS = {
     "tfgpc_kernel_basis_grads": c_int,
     "tfgpc_kp_basis": c_int,
     "tfgpc_pointconv_pdf": c_int,
+    "tfgpc_neighborhood_pool": c_int,
+    "tfgpc_global_pool_workspace_bytes": c_sz,
+    "tfgpc_global_pool": c_int,
+    "tfgpc_add_bias": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
     "tfgpc_read_device": c_int,

@@ -390,3 +390,62 @@ class PointConv(_ProjectedConv):
                                   scale, self.hidden_w, self.hidden_b, 1.0, dbasis,
                                   self.activation, self.alpha)
     return dfeat, dhw, dhb, dw
+
+
+# ---- pooling and 1x1 convolution (Pooling.py, Conv1x1.py) ----------------------
+
+POOL_MODES = {'max': 0, 'avg': 1, 'average': 1, 'mean': 1}
+
+
+def neighborhood_pool(features, neighborhood, mode='max'):
+  """MaxPooling / AveragePooling over a neighborhood (Pooling.py:148-162):
+  [N_in, C] -> [N_out, C]."""
+  features = _f32(features)
+  nb, ranges = _i32(neighborhood._original_neigh_ids), _i32(neighborhood._samples_neigh_ranges)
+  ns, c = ranges.shape[0], features.shape[1]
+  out = torch.empty((ns, c), dtype=torch.float32, device=features.device)
+  _lib.check(_lib.lib().tfgpc_neighborhood_pool(
+      _stream(), c_int(POOL_MODES[mode]), c_int(c), c_i64(ns), c_i64(features.shape[0]),
+      c_i64(nb.shape[0]), ptr(features), ptr(nb), ptr(ranges), ptr(out)))
+  return out
+
+
+def local_pool(features, point_cloud_in, point_cloud_out, pooling_radius, mode='max'):
+  """Pooling.py:140-162: grid of the input cloud, neighborhood around the output
+  points, pooled features."""
+  from . import pc
+  grid = pc.Grid(point_cloud_in, pooling_radius)
+  return neighborhood_pool(features, pc.Neighborhood(grid, pooling_radius, point_cloud_out), mode)
+
+
+def global_pool(features, point_cloud, mode='max'):
+  """GlobalMaxPooling / GlobalAveragePooling (Pooling.py:51-57, 90-96):
+  [N, C] -> [batch_size, C]."""
+  features, bids = _f32(features), _i32(point_cloud._batch_ids)
+  n, c = features.shape
+  b = int(point_cloud._batch_size)
+  out = torch.empty((b, c), dtype=torch.float32, device=features.device)
+  nbytes = _lib.lib().tfgpc_global_pool_workspace_bytes(c_i64(b))
+  ws = _workspace(nbytes, features.device)
+  _lib.check(_lib.lib().tfgpc_global_pool(
+      _stream(), c_int(POOL_MODES[mode]), c_int(c), c_i64(n), c_i64(b), ptr(features), ptr(bids),
+      ptr(out), ptr(ws), c_sz(nbytes)))
+  return out
+
+
+def conv1x1(features, weights, bias):
+  """Conv1x1.py:97: features [N, C_in] @ weights [C_in, C_out] + bias [1, C_out].
+  The product runs on the tensor cores; channel counts that are not multiples
+  of 8 are zero padded for it."""
+  features, weights, bias = _f32(features), _f32(weights), _f32(bias).reshape(-1)
+  n, cin = features.shape
+  cout = weights.shape[1]
+  cin_p, cout_p = (cin + 7) // 8 * 8, (cout + 7) // 8 * 8
+  if cin_p != cin:
+    features = torch.nn.functional.pad(features, (0, cin_p - cin))
+  if cin_p != cin or cout_p != cout:
+    weights = torch.nn.functional.pad(weights, (0, cout_p - cout, 0, cin_p - cin))
+    bias = torch.nn.functional.pad(bias, (0, cout_p - cout))
+  out = matmul_f32(features, weights)
+  _lib.check(_lib.lib().tfgpc_add_bias(_stream(), c_i64(n), c_int(cout_p), ptr(out), ptr(bias)))
+  return out[:, :cout] if cout_p != cout else out

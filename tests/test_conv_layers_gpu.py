@@ -90,3 +90,39 @@ def test_pointconv_forward_backward(n_pts, n_smp, cin, cout, b, radius, hidden, 
   np.add.at(ref_df, ids[:, 0], np.einsum('mck,mk->mc', dx[ids[:, 1]], basis))
   close(dfeat.cpu().numpy(), ref_df)
   assert dhw.shape == (d, hidden) and dhb.reshape(-1).shape == (hidden,)
+
+
+@pytest.mark.parametrize("c", [1, 6, 64, 129])
+@pytest.mark.parametrize("mode", ['max', 'avg'])
+def test_pooling_layers(c, mode):
+  rng = np.random.default_rng(c + len(mode))
+  pts, smp, nb_ref, nb, (cloud_in, cloud_out) = layer_case(rng, 3, 4000, 700, 4, 0.12)
+  feat = rng.normal(size=(4000, c)).astype(F32)
+  out = mcconv.neighborhood_pool(t(feat), nb, mode).cpu().numpy()
+  ref = pr.neighborhood_pool(feat, nb_ref, mode)
+  assert (np.diff(np.concatenate(([0], nb_ref.ranges))) == 0).any()   # empty samples occur
+  if mode == 'max':
+    assert np.array_equal(out, ref)
+  else:
+    close(out, ref)
+  out2 = mcconv.local_pool(t(feat), cloud_in, cloud_out, 0.12, mode).cpu().numpy()
+  assert np.array_equal(out2, out)
+  # global pooling, with one cloud of the batch left empty
+  cloud = pc.PointCloud(cloud_in._points, cloud_in._batch_ids, 6)
+  g = mcconv.global_pool(t(feat), cloud, mode).cpu().numpy()
+  g_ref = pr.global_pool(feat, cloud_in._batch_ids.cpu().numpy(), 6, mode)
+  if mode == 'max':
+    assert np.array_equal(g, g_ref)
+  else:
+    close(g, g_ref)
+
+
+@pytest.mark.parametrize("n,cin,cout", [(1000, 8, 16), (3000, 1, 128), (5000, 128, 40),
+                                        (777, 20, 3), (4096, 1024, 40)])
+def test_conv1x1(n, cin, cout):
+  rng = np.random.default_rng(n + cin)
+  feat = rng.normal(size=(n, cin)).astype(F32)
+  w = (rng.normal(size=(cin, cout)) / np.sqrt(cin)).astype(F32)
+  bias = rng.normal(size=(1, cout)).astype(F32)
+  out = mcconv.conv1x1(t(feat), t(w), t(bias))
+  close(out.cpu().numpy(), pr.conv1x1(feat, w, bias))

@@ -323,3 +323,27 @@ def test_pointconv_matches_numpy_layer(n_pts, n_smp, feats, b, radius, hidden, d
   x = _sum_per_sample(per_pair, nb.ranges)
   ref = x.reshape(n_smp, -1) @ w.astype(np.float64)
   np.testing.assert_allclose(out, ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("mode", ['max', 'avg'])
+def test_pooling_matches_per_segment_loops(mode):
+  """pooling_layers_test.py: the pooled value of a segment is numpy's max / mean
+  over the rows that belong to it."""
+  rng = np.random.default_rng(9)
+  pts, smp, nb = _layer_case(rng, 3, 1500, 120, 4, 0.3)
+  feat = rng.normal(size=(1500, 6)).astype(F32)
+  out = pr.neighborhood_pool(feat, nb, mode)
+  ids = nb.original_neigh_ids
+  for s in range(120):
+    rows = feat[ids[ids[:, 1] == s, 0]]
+    if len(rows) == 0:
+      assert np.all(out[s] == (pr.LOWEST if mode == 'max' else 0))
+    else:
+      ref = rows.max(axis=0) if mode == 'max' else rows.astype(np.float64).mean(axis=0)
+      np.testing.assert_allclose(out[s], ref, rtol=1e-5, atol=1e-6)
+  bid = rng.integers(0, 5, 1500).astype(np.int32)
+  g = pr.global_pool(feat, bid, 6, mode)     # segment 5 stays empty
+  for b in range(5):
+    ref = feat[bid == b].max(axis=0) if mode == 'max' else feat[bid == b].mean(axis=0)
+    np.testing.assert_allclose(g[b], ref, rtol=1e-5, atol=1e-6)
+  assert np.all(g[5] == (pr.LOWEST if mode == 'max' else 0))
