@@ -46,7 +46,7 @@ def parse_args():
   ap.add_argument("--cpu-sample-clouds", type=int, default=1)
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
-  ap.add_argument("--workload", default="mcconv", choices=["mcconv", "neighbors", "hierarchy"],
+  ap.add_argument("--workload", default="mcconv", choices=["mcconv", "neighbors", "hierarchy", "classifier"],
                   help="mcconv: the headline step; neighbors: grid build + neighbor search + pdf "
                        "on 16 surface clouds (radius 0.05); hierarchy: 4-level Poisson-disk and "
                        "cell-average sampling of 8 x 100000 Gaussian-mixture points")
@@ -551,12 +551,65 @@ def run_side_workload(args):
   print(json.dumps(line), flush=True)
 
 
+def run_classifier_workload(args):
+  """Forward pass of the small classification network (widths 1-128-256-512-
+  1024-1024-40, MCConv with 4 kernel MLPs of 8 units) on 32 clouds of 1024 points
+  on one GPU: time per batch and the kernels it spends it in."""
+  import torch
+  from tensorflow_graphics_point_clouds_b200 import _lib, build, classifier, synthetic
+  if not torch.cuda.is_available():
+    raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+  build.build()
+  dev = torch.device("cuda", 0)
+  clouds, points = 32, 1024
+  radii = [0.1, 0.2, 0.4, 2 * np.sqrt(3)]
+  pts, bid = synthetic.unit_sphere_shapes(clouds, points, seed=4)
+  tp, tb = torch.from_numpy(pts).to(dev), torch.from_numpy(bid).to(dev)
+  feat = torch.ones((len(pts), 1), dtype=torch.float32, device=dev)
+  net = classifier.SmallClassifier(synthetic.small_classifier_weights(40), radii, dev)
+  sampler = ClockSampler(0)
+  sampler.start()
+  for _ in range(max(args.warmup, 3)):
+    net.forward(tp, tb, clouds, feat)
+  torch.cuda.synchronize()
+  _lib.profile_enable(True)
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    net.forward(tp, tb, clouds, feat)
+  e1.record()
+  torch.cuda.synchronize()
+  records = _lib.profile_collect()
+  _lib.profile_enable(False)
+  clocks = sampler.stop()
+  ms = e0.elapsed_time(e1) / args.steps
+  agg = {}
+  for name, kms in records:
+    a = agg.setdefault(name, [0, 0.0])
+    a[0] += 1; a[1] += kms
+  kernels = {name: {"launches_per_step": c / args.steps, "ms_per_step": t / args.steps}
+             for name, (c, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+  line = {
+      "metric": "classifier_forward_points_per_s", "value": clouds * points / (ms * 1e-3),
+      "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+      "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+      "config": {"workload": "classifier", "clouds": clouds, "points_per_cloud": points,
+                 "radii": [float(r) for r in radii]},
+      "clocks": clocks, "kernels": kernels,
+      "kernel_ms_per_step": sum(v["ms_per_step"] for v in kernels.values()),
+  }
+  print(json.dumps(line), flush=True)
+
+
 def main():
   args = parse_args()
   rank = int(os.environ.get("RANK", "0"))
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
-  if args.workload != "mcconv":
+  if args.workload == "classifier":
+    if rank == 0:
+      run_classifier_workload(args)
+  elif args.workload != "mcconv":
     if rank == 0:
       run_side_workload(args)
   elif args.impl == "reference":

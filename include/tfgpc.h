@@ -395,6 +395,14 @@ int tfgpc_global_pool(void* stream, int mode, int C, int64_t n,
                       const int32_t* batch_ids, float* out, void* ws,
                       size_t ws_bytes);
 int tfgpc_add_bias(void* stream, int64_t n, int C, float* x, const float* bias);
+/* x = act(x * scale + bias) in place, x [n,C], bias [C] or NULL: a batch
+ * normalisation in inference mode (its stored statistics folded into scale and
+ * bias) followed by the activation, as between the layers of
+ * modelnet40_small.py:236-243.  activation 0 = none, 1 = leaky ReLU with slope
+ * alpha (tf.keras.layers.LeakyReLU's default is 0.3). */
+int tfgpc_scale_bias_activation(void* stream, int64_t n, int C, float* x,
+                                float scale, const float* bias, int activation,
+                                float alpha);
 
 /* ---- fp32 matrix product on the tensor cores -----------------------------
  * c[M,N] = op(a) * op(b) in fp32 accuracy (three bf16 passes), the tf.matmul

@@ -293,3 +293,31 @@ def conv1x1(features, weights, bias):
   """Conv1x1.py:97."""
   return (features.astype(np.float64) @ weights.astype(np.float64)
           + bias.reshape(1, -1)).astype(F32)
+
+
+def small_classifier_forward(points, batch_ids, batch_size, features, weights, sample_radii,
+                             bn_eps=1e-3, leaky_alpha=0.3):
+  """modelnet40_small.py:121-261 (MCConv variant) at inference with freshly
+  initialised batch normalisations: hierarchy (PointHierarchy.py:40-98), per
+  level MCConv (MCConv.py:163-194, 254-269), BN + LeakyReLU + Conv1x1 + BN +
+  LeakyReLU between levels, BN + LeakyReLU + Dense twice as head."""
+  bn = F32(1.0 / np.sqrt(1.0 + bn_eps))
+  act = lambda x: leaky_relu((x * bn).astype(F32), leaky_alpha)
+  levels = point_hierarchy(points, batch_ids, batch_size, list(sample_radii), mode=0)
+  x = np.asarray(features, F32)
+  last = len(weights["conv"]) - 1
+  for i, (w1, b1, wf) in enumerate(weights["conv"]):
+    p_in, b_in = levels[i][0], levels[i][1]
+    p_out, b_out = levels[i + 1][0], levels[i + 1][1]
+    r = F32(sample_radii[i])
+    grid = Grid(p_in, b_in, batch_size, r)
+    nb = Neighborhood(grid, r, p_out, b_out)
+    basis, _, _ = mcconv_basis(p_in, p_out, nb, nb.get_pdf(), w1, b1, r)
+    x, _ = mcconv_forward(x, basis, nb, wf)
+    if i < last:
+      x = act(x)
+      x = act(conv1x1(x, *weights["conv1x1"][i]))
+  x = x[np.argsort(levels[-1][1], kind='stable')]
+  x = act(x)
+  x = act(conv1x1(x, *weights["dense"][0]))
+  return conv1x1(x, *weights["dense"][1])

@@ -64,6 +64,7 @@ SYMBOLS = {
     "tfgpc_global_pool_workspace_bytes": c_sz,
     "tfgpc_global_pool": c_int,
     "tfgpc_add_bias": c_int,
+    "tfgpc_scale_bias_activation": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
     "tfgpc_read_device": c_int,

@@ -1,0 +1,53 @@
+"""Forward pass of the reference's small classification network
+(modelnet40_small.py:121-261, MCConv variant) on the library's ops: point
+hierarchy by Poisson disk sampling, one Monte-Carlo convolution per level,
+inference batch normalisation + leaky ReLU + Conv1x1 between the levels, a
+two-layer head.  Weights come from the caller (synthetic.small_classifier_weights
+in the tests and the benchmark); dropout is the identity at inference."""
+import math
+
+import torch
+
+from . import mcconv, pc
+
+KERAS_BN_EPS = 1e-3        # tf.keras.layers.BatchNormalization default epsilon
+KERAS_LEAKY_ALPHA = 0.3    # tf.keras.layers.LeakyReLU default slope
+
+
+class SmallClassifier:
+  def __init__(self, weights, sample_radii, device):
+    to = lambda a: torch.from_numpy(a).to(device)
+    self.radii = [float(r) for r in sample_radii]
+    self.convs = []
+    for w1, b1, wf in weights["conv"]:
+      cin = wf.shape[1] // w1.shape[2]
+      self.convs.append(mcconv.MCConv(to(w1), to(b1), to(wf), cin))
+    self.conv1x1 = [(to(w), to(b)) for w, b in weights["conv1x1"]]
+    self.dense = [(to(w), to(b)) for w, b in weights["dense"]]
+    # a freshly initialised batch normalisation in inference mode: mean 0,
+    # variance 1, gamma 1, beta 0
+    self.bn_scale = 1.0 / math.sqrt(1.0 + KERAS_BN_EPS)
+
+  def _bn_act(self, x):
+    return mcconv.scale_bias_activation_(x.contiguous(), self.bn_scale, None, KERAS_LEAKY_ALPHA)
+
+  def forward(self, points, batch_ids, batch_size, features):
+    cloud = pc.PointCloud(points, batch_ids, batch_size)
+    hier = pc.PointHierarchy(cloud, self.radii, 'poisson')
+    clouds = hier._point_clouds
+    x = features
+    last = len(self.convs) - 1
+    for i, conv in enumerate(self.convs):
+      x = conv.forward(x, clouds[i], clouds[i + 1], self.radii[i], keep_for_backward=False)
+      if i < last:
+        x = self._bn_act(x)
+        x = mcconv.conv1x1(x, *self.conv1x1[i])
+        x = self._bn_act(x)
+    # return_sorted=True of the last convolution (modelnet40_small.py:249-254):
+    # rows in ascending batch id; the last radius leaves one point per cloud
+    order = torch.argsort(clouds[-1]._batch_ids.long(), stable=True)
+    x = x[order].contiguous()
+    x = self._bn_act(x)
+    x = mcconv.conv1x1(x, *self.dense[0])
+    x = self._bn_act(x)
+    return mcconv.conv1x1(x, *self.dense[1])

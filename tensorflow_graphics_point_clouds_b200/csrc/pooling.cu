@@ -94,6 +94,20 @@ __global__ void add_bias_kernel(int64_t n, int C, float* x, const float* __restr
   if (i < n * C) x[i] += __ldg(bias + (i % C));
 }
 
+// x = act(x * scale + bias): inference batch normalisation with stored
+// statistics folded into scale and bias, followed by the activation
+// (modelnet40_small.py:236-243).  act 0: none, 1: leaky ReLU with slope alpha.
+__global__ void scale_bias_act_kernel(int64_t total, int C, float* x, float scale,
+                                      const float* __restrict__ bias, int act, float alpha) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (bias) v += __ldg(bias + (i % C));
+    if (act == 1) v = v > 0.0f ? v : v * alpha;
+    x[i] = v;
+  }
+}
+
 }  // namespace
 }  // namespace tfgpc
 
@@ -156,6 +170,21 @@ extern "C" int tfgpc_add_bias(void* stream, int64_t n, int C, float* x, const fl
   cudaStream_t st = (cudaStream_t)stream;
   ProfScope prof(st, "add_bias");
   add_bias_kernel<<<blocks_for(n * C, 256), 256, 0, st>>>(n, C, x, bias);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_scale_bias_activation(void* stream, int64_t n, int C, float* x, float scale,
+                                           const float* bias, int activation, float alpha) {
+  TFGPC_REQUIRE(n >= 0 && C > 0, "ScaleBiasActivation expects n >= 0 and C > 0");
+  TFGPC_REQUIRE(activation == 0 || activation == 1,
+                "ScaleBiasActivation expects activation 0 (none) or 1 (leaky ReLU)");
+  if (n == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(x, "ScaleBiasActivation got a null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  ProfScope prof(st, "scale_bias_activation");
+  unsigned grid = min(blocks_for(n * C, 256), (unsigned)(sm_count() * 16));
+  scale_bias_act_kernel<<<grid, 256, 0, st>>>(n * C, C, x, scale, bias, activation, alpha);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

@@ -449,3 +449,17 @@ def conv1x1(features, weights, bias):
   out = matmul_f32(features, weights)
   _lib.check(_lib.lib().tfgpc_add_bias(_stream(), c_i64(n), c_int(cout_p), ptr(out), ptr(bias)))
   return out[:, :cout] if cout_p != cout else out
+
+
+def scale_bias_activation_(x, scale=1.0, bias=None, leaky_alpha=None):
+  """In place x = act(x * scale + bias) (tfgpc_scale_bias_activation): inference
+  batch normalisation folded into scale / bias, then an optional leaky ReLU."""
+  if not x.is_contiguous() or x.dtype != torch.float32:
+    raise _lib.TfgpcError(1, "scale_bias_activation_ expects a contiguous float32 tensor")
+  n, c = x.shape
+  b = None if bias is None else _f32(bias).reshape(-1)
+  _lib.check(_lib.lib().tfgpc_scale_bias_activation(
+      _stream(), c_i64(n), c_int(c), ptr(x), ctypes.c_float(float(scale)),
+      ptr(b) if b is not None else ctypes.c_void_p(0), c_int(0 if leaky_alpha is None else 1),
+      ctypes.c_float(0.0 if leaky_alpha is None else float(leaky_alpha))))
+  return x

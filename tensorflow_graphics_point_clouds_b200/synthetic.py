@@ -77,3 +77,53 @@ def mcconv_weights(seed, dims, cin, cout, num_mlps=1, hidden=16):
   wf = glorot_uniform(rng, cin * hidden, cout // num_mlps,
                       (num_mlps, cin * hidden, cout // num_mlps))
   return w1, b1, wf
+
+
+def unit_sphere_shapes(num_clouds, points_per_cloud, seed):
+  """Clouds of points on random ellipsoids, boxes and cylinders, centred and
+  scaled into the unit sphere: stand-ins with the shape of the 1024-point
+  ModelNet40 samples that modelnet40_small.py trains on."""
+  rng = np.random.default_rng(seed)
+  pts = np.empty((num_clouds, points_per_cloud, 3), F32)
+  for c in range(num_clouds):
+    kind = c % 3
+    axes = rng.uniform(0.3, 1.0, 3)
+    n = points_per_cloud
+    if kind == 0:     # ellipsoid
+      v = rng.normal(size=(n, 3))
+      p = v / np.linalg.norm(v, axis=1, keepdims=True) * axes
+    elif kind == 1:   # box
+      p = rng.uniform(-1, 1, (n, 3))
+      face = rng.integers(0, 3, n)
+      p[np.arange(n), face] = np.sign(rng.uniform(-1, 1, n))
+      p = p * axes
+    else:             # cylinder along z, side and caps
+      ang = rng.uniform(0, 2 * np.pi, n)
+      side = rng.uniform(size=n) < 0.7
+      rad = np.where(side, 1.0, np.sqrt(rng.uniform(size=n)))
+      z = np.where(side, rng.uniform(-1, 1, n), np.sign(rng.uniform(-1, 1, n)))
+      p = np.stack([rad * np.cos(ang) * axes[0], rad * np.sin(ang) * axes[0], z * axes[2]], 1)
+    p = p - p.mean(axis=0)
+    pts[c] = (p / np.linalg.norm(p, axis=1).max()).astype(F32)
+  bid = np.repeat(np.arange(num_clouds, dtype=np.int32), points_per_cloud)
+  return pts.reshape(-1, 3), bid
+
+
+def small_classifier_weights(seed, feature_sizes=(1, 128, 256, 512, 1024, 1024, 40), num_mlps=4,
+                             hidden=8):
+  """Random-init weights of the modelnet40_small.py network (MCConv variant):
+  per level the MCConv weights, then a Conv1x1 except after the last level,
+  then the two dense layers of the head."""
+  rng = np.random.default_rng(seed)
+  levels = len(feature_sizes) - 3
+  out = {"conv": [], "conv1x1": [], "dense": []}
+  for i in range(levels):
+    cin, cout = feature_sizes[i], feature_sizes[i + 1]
+    out["conv"].append(mcconv_weights(seed + 1 + i, 3, cin, cout, num_mlps, hidden))
+    if i < levels - 1:
+      out["conv1x1"].append((glorot_uniform(rng, cout, cout, (cout, cout)),
+                             (rng.normal(size=(1, cout)) * 0.01).astype(F32)))
+  for cin, cout in ((feature_sizes[-3], feature_sizes[-2]), (feature_sizes[-2], feature_sizes[-1])):
+    out["dense"].append((glorot_uniform(rng, cin, cout, (cin, cout)),
+                         (rng.normal(size=(1, cout)) * 0.01).astype(F32)))
+  return out

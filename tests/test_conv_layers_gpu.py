@@ -126,3 +126,20 @@ def test_conv1x1(n, cin, cout):
   bias = rng.normal(size=(1, cout)).astype(F32)
   out = mcconv.conv1x1(t(feat), t(w), t(bias))
   close(out.cpu().numpy(), pr.conv1x1(feat, w, bias))
+
+
+def test_small_classifier_forward():
+  """The classification network of modelnet40_small.py (MCConv variant, widths
+  1-128-256-512-1024-1024-40, sampling radii 0.1 / 0.2 / 0.4 / 2 sqrt(3)) on 32
+  clouds of 1024 points: logits against the NumPy / C restatement."""
+  from tensorflow_graphics_point_clouds_b200 import classifier, synthetic
+  b = 32
+  radii = [0.1, 0.2, 0.4, 2 * np.sqrt(3)]
+  pts, bid = synthetic.unit_sphere_shapes(b, 1024, seed=4)
+  feat = np.ones((len(pts), 1), F32)
+  weights = synthetic.small_classifier_weights(40)
+  ref = pr.small_classifier_forward(pts, bid, b, feat, weights, radii)
+  net = classifier.SmallClassifier(weights, radii, "cuda")
+  out = net.forward(t(pts), t(bid), b, t(feat))
+  assert out.shape == (b, 40)
+  close(out.cpu().numpy(), ref)
