@@ -1,8 +1,9 @@
 // Device-wide inclusive scan of int32 counts (reduce, scan of tile sums, scan).
 // Takes the place of the reference's recursive Blelloch scan with its host
 // loop (find_neighbors/cc/kernels/scan_alg_kernels.cu.cc:41-266): three
-// launches, no host synchronisation, 64-bit tile sums so that totals beyond
-// 2^31 are detected by the caller instead of wrapping silently.
+// launches (one for inputs of a single tile), no host synchronisation, 64-bit
+// tile sums so that totals beyond 2^31 are detected by the caller instead of
+// wrapping silently.
 #include "common.cuh"
 
 namespace tfgpc {
@@ -84,7 +85,7 @@ scan_tile_sums_kernel(int64_t* __restrict__ tile_sums, int64_t tiles, int64_t* _
 
 __global__ void __launch_bounds__(kScanThreads)
 scan_tiles_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int64_t n,
-                  const int64_t* __restrict__ tile_offsets) {
+                  const int64_t* __restrict__ tile_offsets, int64_t* __restrict__ total) {
   __shared__ int64_t warp_tot[kScanThreads / 32];
   int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
   int32_t item[kScanItems];
@@ -114,12 +115,15 @@ scan_tiles_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int
     if (lane_id() < kScanThreads / 32) warp_tot[lane_id()] = s - t;
   }
   __syncthreads();
-  int64_t run = tile_offsets[blockIdx.x] + warp_tot[w] + (x - local);
+  // tile_offsets == nullptr: the input is a single tile, scanned by this one
+  // launch, which then also writes the grand total
+  int64_t run = (tile_offsets ? tile_offsets[blockIdx.x] : 0) + warp_tot[w] + (x - local);
 #pragma unroll
   for (int i = 0; i < kScanItems; ++i) {
     run += item[i];
     if (base + i < n) out[base + i] = (int32_t)run;
   }
+  if (!tile_offsets && threadIdx.x == kScanThreads - 1) *total = run;
 }
 
 int inclusive_scan_i32(cudaStream_t stream, const int32_t* in, int32_t* out, int64_t n,
@@ -130,11 +134,17 @@ int inclusive_scan_i32(cudaStream_t stream, const int32_t* in, int32_t* out, int
   }
   int64_t tiles = (n + kScanTile - 1) / kScanTile;
   ProfScope prof(stream, "scan_i32");
+  if (tiles == 1) {
+    scan_tiles_kernel<<<1, kScanThreads, 0, stream>>>(in, out, n, nullptr, total);
+    TFGPC_LAUNCH_CHECK();
+    return TFGPC_OK;
+  }
   scan_reduce_kernel<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, n, block_sums);
   TFGPC_LAUNCH_CHECK();
   scan_tile_sums_kernel<<<1, 1024, 0, stream>>>(block_sums, tiles, total);
   TFGPC_LAUNCH_CHECK();
-  scan_tiles_kernel<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, out, n, block_sums);
+  scan_tiles_kernel<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, out, n, block_sums,
+                                                                  nullptr);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
