@@ -69,3 +69,25 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
   monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
   with pytest.raises(RuntimeError, match="no\\s+CPU or eager fallback"):
     _lib.lib()
+
+
+def test_layer_entries_reject_bad_arguments(lib):
+  """The entries of the KPConv / PointConv / pooling layers check their scalar
+  arguments before any launch."""
+  i64, f = ctypes.c_int64, ctypes.c_float
+  rc = lib.tfgpc_kp_basis(None, 3, 16, 17, i64(4), None, None, None, None, f(1.0), f(1.0), 0, None)
+  assert rc == 1 and b"kernel points" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_kp_basis(None, 3, 16, 15, i64(4), None, None, None, None, f(1.0), f(1.0), 2, None)
+  assert rc == 1 and b"interpolation" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_kp_basis(None, 3, 12, 5, i64(4), None, None, None, None, f(1.0), f(1.0), 0, None)
+  assert rc == 1 and b"basis functions" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_neighborhood_pool(None, 2, 8, i64(4), i64(4), i64(4), None, None, None, None)
+  assert rc == 1 and b"mode" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_global_pool(None, 0, 8, i64(4), i64(0), None, None, None, None,
+                             ctypes.c_size_t(0))
+  assert rc == 1 and b"batch size" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_scale_bias_activation(None, i64(4), 8, None, f(1.0), None, 3, f(0.0))
+  assert rc == 1 and b"activation" in lib.tfgpc_last_error()
+  rc = lib.tfgpc_mcconv_workspace_bytes(16, 128, 256, i64(100), i64(100), 1)
+  assert rc > 0
+  assert lib.tfgpc_global_pool_workspace_bytes(i64(32)) >= 128
