@@ -15,7 +15,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT_DIR, "libtfg_ref_kernels.so")
-DEFAULT_REFERENCE = "/root/reference"
+# where a checkout of the reference project lies (only needed to rebuild the library)
+DEFAULT_REFERENCE = os.environ.get("TFG_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 
 
 def build(reference=DEFAULT_REFERENCE, force=False):
