@@ -135,6 +135,27 @@ int tfgpc_find_neighbors_fill(void* stream, int D, int64_t ns,
                               const int32_t* ranges, int64_t total,
                               int32_t* neigh_out);
 
+/* The same two calls with a visiting order: sample_order [ns] is a permutation
+ * of 0..ns-1, and the samples are worked on in that sequence.  The results are
+ * the same as without it (ranges and lists stay indexed by the sample's own
+ * position); an order that keeps spatial neighbors together (for samples that
+ * are the grid's own points: the permutation the key sort returns) makes
+ * consecutive warps read the same cells.  No counterpart in the reference. */
+int tfgpc_find_neighbors_count_ordered(
+    void* stream, int D, int64_t ns, const float* samples,
+    const int32_t* samples_batch_ids, const int32_t* sample_order, int64_t n,
+    const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs,
+    int32_t* ranges_out, void* ws, size_t ws_bytes, int64_t* total_out);
+int tfgpc_find_neighbors_fill_ordered(
+    void* stream, int D, int64_t ns, const float* samples,
+    const int32_t* samples_batch_ids, const int32_t* sample_order, int64_t n,
+    const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs,
+    const int32_t* ranges, int64_t total, int32_t* neigh_out);
+
 /* Neighbor ids in the unsorted point order: ids_out[m] = (sorted_indices[
  * neighbors[m].x], neighbors[m].y), the gather + concat of
  * pylib/pc/Neighborhood.py:246-250; optionally also the per-pair density

@@ -91,7 +91,8 @@ __device__ __forceinline__ bool within_radius(const float* s, const float* __res
 
 template <int D, bool FILL>
 __global__ void __launch_bounds__(kFnThreads)
-find_neighbors_kernel(int64_t ns, const float* __restrict__ samples,
+find_neighbors_kernel(int64_t ns, const int32_t* __restrict__ order,
+                      const float* __restrict__ samples,
                       const int32_t* __restrict__ sbatch, const float* __restrict__ pts,
                       const int64_t* __restrict__ keys, const int2* __restrict__ ds,
                       int batch_size, const int32_t* __restrict__ num_cells,
@@ -114,8 +115,12 @@ find_neighbors_kernel(int64_t ns, const float* __restrict__ samples,
   // previous sample are kept instead of being searched again.
   int prev_cell[D], prev_b = -1;
   int2 my_range[kChunks];
-  for (int64_t s = (((int64_t)blockIdx.x * kFnThreads + threadIdx.x) >> 5) * kFnSpan; s < ns;
-       s += ((s + 1) % kFnSpan) ? 1 : (warps - 1) * kFnSpan + 1) {
+  for (int64_t v = (((int64_t)blockIdx.x * kFnThreads + threadIdx.x) >> 5) * kFnSpan; v < ns;
+       v += ((v + 1) % kFnSpan) ? 1 : (warps - 1) * kFnSpan + 1) {
+    // `order` lists the samples in the sequence to visit them in (one that keeps
+    // spatial neighbors together); what is written for a sample does not depend on it
+    const int64_t s = order ? (int64_t)__ldg(order + v) : v;
+    if (s < 0 || s >= ns) continue;
     float sp[D], smin[D];
     int cell[D];
     const int b = __ldg(sbatch + s);
@@ -186,7 +191,7 @@ extern "C" size_t tfgpc_find_neighbors_workspace_bytes(int64_t ns) {
   return align_up((size_t)(scan_block_sums_elems(ns) + 1) * sizeof(int64_t), 256) + 256;
 }
 
-static int find_neighbors_count_impl(bool mapped_read,
+static int find_neighbors_count_impl(bool mapped_read, const int32_t* order,
     void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
@@ -208,10 +213,12 @@ static int find_neighbors_count_impl(bool mapped_read,
   int64_t* total_dev = block_sums + scan_block_sums_elems(ns);
   unsigned grid = min(blocks_for((ns + kFnSpan - 1) / kFnSpan, kFnThreads / 32),
                       (unsigned)(sm_count() * 32));
+  // an order that is not a permutation leaves samples unvisited: they count zero
+  if (order) TFGPC_CUDA(cudaMemsetAsync(ranges_out, 0, sizeof(int32_t) * (size_t)ns, st));
   {
   ProfScope prof(st, "find_neighbors_count");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, false><<<grid, kFnThreads, 0, st>>>(
-      ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+      ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
       num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, ranges_out, nullptr,
       nullptr));
   }
@@ -241,13 +248,13 @@ extern "C" int tfgpc_find_neighbors_count(
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
     const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
     void* ws, size_t ws_bytes, int64_t* total_out) {
-  return find_neighbors_count_impl(true, stream, D, ns, samples, samples_batch_ids, n, points,
+  return find_neighbors_count_impl(true, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
                                   point_keys, ds, batch_size, num_cells, scaled_aabb_min,
                                   inv_cell_sizes, inv_radii, max_neighs, ranges_out, ws, ws_bytes,
                                   total_out);
 }
 
-extern "C" int tfgpc_find_neighbors_fill(
+static int find_neighbors_fill_impl(const int32_t* order,
     void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
@@ -265,11 +272,45 @@ extern "C" int tfgpc_find_neighbors_fill(
                       (unsigned)(sm_count() * 32));
   ProfScope prof(st, "find_neighbors_fill");
   TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, true><<<grid, kFnThreads, 0, st>>>(
-      ns, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+      ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
       num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,
       (int2*)neigh_out));
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
+}
+
+extern "C" int tfgpc_find_neighbors_fill(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
+    const float* inv_cell_sizes, const float* inv_radii, int max_neighs, const int32_t* ranges,
+    int64_t total, int32_t* neigh_out) {
+  return find_neighbors_fill_impl(nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
+                                  point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                  inv_cell_sizes, inv_radii, max_neighs, ranges, total, neigh_out);
+}
+
+extern "C" int tfgpc_find_neighbors_count_ordered(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    const int32_t* sample_order, int64_t n, const float* points, const int64_t* point_keys,
+    const int32_t* ds, int64_t batch_size, const int32_t* num_cells,
+    const float* scaled_aabb_min, const float* inv_cell_sizes, const float* inv_radii,
+    int max_neighs, int32_t* ranges_out, void* ws, size_t ws_bytes, int64_t* total_out) {
+  return find_neighbors_count_impl(true, sample_order, stream, D, ns, samples, samples_batch_ids,
+                                   n, points, point_keys, ds, batch_size, num_cells,
+                                   scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs,
+                                   ranges_out, ws, ws_bytes, total_out);
+}
+
+extern "C" int tfgpc_find_neighbors_fill_ordered(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    const int32_t* sample_order, int64_t n, const float* points, const int64_t* point_keys,
+    const int32_t* ds, int64_t batch_size, const int32_t* num_cells,
+    const float* scaled_aabb_min, const float* inv_cell_sizes, const float* inv_radii,
+    int max_neighs, const int32_t* ranges, int64_t total, int32_t* neigh_out) {
+  return find_neighbors_fill_impl(sample_order, stream, D, ns, samples, samples_batch_ids, n,
+                                  points, point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                  inv_cell_sizes, inv_radii, max_neighs, ranges, total, neigh_out);
 }
 
 // ---- neighbor ids in the unsorted point order, per-pair densities -----------------
@@ -376,7 +417,7 @@ extern "C" int tfgpc_find_neighbors_count_static(
                 kStaticScratchBytes, (long long)ns);
   // Nothing in the scratch has to start at zero: the scan overwrites every tile
   // sum and the total before it reads them, so stale contents are harmless.
-  return find_neighbors_count_impl(false, stream, D, ns, samples, samples_batch_ids, n, points,
+  return find_neighbors_count_impl(false, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
                                   point_keys, ds, batch_size, num_cells, scaled_aabb_min,
                                   inv_cell_sizes, inv_radii, max_neighs, ranges_out, scratch,
                                   kStaticScratchBytes, total_out);

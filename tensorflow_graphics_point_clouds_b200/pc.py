@@ -100,10 +100,13 @@ class Neighborhood:
     self._grid = grid
     self.max_neighbors = max_neighbors
     smp = self._point_cloud_sampled
+    # samples that are the grid's own cloud in its unsorted order: the key sort's
+    # permutation lists them cell by cell, the sequence the search is fastest in
+    order = grid._sorted_indices if smp is grid._point_cloud else None
     self._samples_neigh_ranges, self._neighbors = ops.find_neighbors(
         smp._points, smp._batch_ids, grid._sorted_points, grid._sorted_keys, grid.get_DS(),
         grid._num_cells, grid._scaled_aabb_min, grid._inv_cell_sizes,
-        torch.reciprocal(self._radii), max_neighbors)
+        torch.reciprocal(self._radii), max_neighbors, sample_order=order)
     self._orig_ids = None
     self._pdf = None
     self._point_pdf = None

@@ -378,3 +378,28 @@ def test_pdf_without_second_neighbor_search_matches_self_neighborhood():
   assert nb._samples_are_grid_points() and not nb._equal_samples
   close(nb.get_pdf(bandwidth=0.2, mode=0).cpu().numpy(), ref_pdf)
   close(nb._point_pdf.cpu().numpy(), nb_ref.point_pdf)
+
+
+@pytest.mark.parametrize("d", [2, 3, 4])
+def test_find_neighbors_visiting_order_does_not_change_results(d):
+  """The *_ordered entries work on the samples in a given sequence; ranges and
+  lists must equal those of the plain entries bit for bit, for the key sort's
+  permutation (what pc.Neighborhood passes for a cloud on its own grid) and
+  for an arbitrary one."""
+  rng = np.random.default_rng(40 + d)
+  pts, bid = random_cloud(rng, 3, 6000, d)
+  g_ref, g = grid_pair(pts, bid, 3, 0.2)
+  cloud = g._point_cloud
+  args = (cloud._points, cloud._batch_ids, g._sorted_points, g._sorted_keys, g.get_DS(),
+          g._num_cells, g._scaled_aabb_min, g._inv_cell_sizes,
+          torch.reciprocal(torch.full((d,), 0.2, device=DEV)))
+  r0, n0 = ops.find_neighbors(*args, 0)
+  for order in (g._sorted_indices, t(rng.permutation(len(pts)).astype(np.int32))):
+    r1, n1 = ops.find_neighbors(*args, 0, sample_order=order)
+    assert torch.equal(r0, r1) and torch.equal(n0, n1)
+  r2, n2 = ops.find_neighbors(*args, 7, sample_order=g._sorted_indices)
+  r3, n3 = ops.find_neighbors(*args, 7)
+  assert torch.equal(r2, r3) and torch.equal(n2, n3)
+  nb = pc.Neighborhood(g, 0.2, cloud)          # takes the ordered entries
+  nb_ref = pr.Neighborhood(g_ref, 0.2, pts, bid)
+  assert_neigh_equal(nb_ref, nb)
