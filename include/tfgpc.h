@@ -181,8 +181,14 @@ int tfgpc_original_neighbor_ids(void* stream, int64_t M,
  * call, larger ns is rejected with TFGPC_EINVAL; the array (about 33 KB) stays
  * resident on every GPU that loads the library until the process exits.
  * The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress) with that device current; make that first call
- * outside of any stream capture.  All calls on a device share the one array,
+ * (cudaGetSymbolAddress) with that device current, and, like the first launch
+ * of any kernel, makes the CUDA runtime load the kernels' code onto the device
+ * (which the runtime may back with memory of its own and a synchronisation):
+ * make that first call as a warm-up, outside of any stream capture and off the
+ * request path.  The address is cached per device for the life of the process
+ * and does not survive a cudaDeviceReset.  Per-launch timing
+ * (tfgpc_profile_enable) is suspended inside this call, since it would create
+ * CUDA events.  All calls on a device share the one array,
  * which keeps the previous call's contents (nothing in it needs clearing: each
  * call overwrites what it reads); two calls whose GPU work overlaps -- from
  * different streams or threads -- race on it, so serialise them. */
@@ -323,6 +329,10 @@ int tfgpc_sampling_store(void* stream, int D, int mode, int64_t n,
  * dweights_out [C*K, Cout] (all overwritten).  x_in_workspace != 0 tells it
  * that `ws` still holds the projection written by the forward call for the
  * same inputs (ws sized for backward); otherwise it is recomputed.  The
+ * weights are read from `weights` on every call, never from what an earlier call
+ * left in `ws`.  The status word of `ws` is cleared by the forward call and by a
+ * backward call that recomputes the projection; a backward call that reuses it
+ * keeps the forward call's word (a timeout there invalidates what it reads).  The
  * workspace size depends on n_in as well: for K in {16, 32, 64} and C a multiple
  * of 16 the projection and its gradients run on warp-level tensor-core MMAs
  * over a bf16 hi/mid copy of the features kept in the workspace.
@@ -435,6 +445,21 @@ size_t tfgpc_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int tfgpc_matmul_f32(void* stream, int64_t M, int64_t N, int64_t K,
                      const float* a, int a_transposed, const float* b,
                      int b_transposed, float* c, void* ws, size_t ws_bytes);
+
+/* ---- bounded-wait self test -------------------------------------------------
+ * No counterpart in the reference (its kernels have no device-side waits).
+ * Every device-side wait of the tensor-core kernels (mbarrier phases of the
+ * GEMMs and of the gradient kernel) gives up after a time limit, records that
+ * in the first int of the workspace and lets the kernel drain and return.  This
+ * entry makes that happen on purpose without disturbing anything: one warp
+ * waits, through the same wait routine, for a barrier phase that nothing
+ * completes, with a limit of limit_us microseconds (1 .. 100000).  It blocks on
+ * the stream; *returned_out [host] is 1 if the kernel ran to its end.
+ * Afterwards tfgpc_mcconv_status(stream, ws, ..) reports TFGPC_ETIMEOUT until
+ * the next GEMM call on `ws` clears the word.  ws: any workspace of the GEMM
+ * entries (256-byte aligned, at least 1024 bytes). */
+int tfgpc_debug_bounded_wait(void* stream, void* ws, size_t ws_bytes,
+                             unsigned limit_us, int* returned_out);
 
 /* ---- small blocking reads -------------------------------------------------
  * No counterpart in the reference (it reads its counts with cudaMemcpy behind

@@ -69,6 +69,7 @@ SYMBOLS = {
     "tfgpc_scale_bias_activation": c_int,
     "tfgpc_matmul_workspace_bytes": c_sz,
     "tfgpc_matmul_f32": c_int,
+    "tfgpc_debug_bounded_wait": c_int,
     "tfgpc_read_device": c_int,
     "tfgpc_profile_enable": c_int,
     "tfgpc_profile_collect": c_int,

@@ -58,6 +58,32 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCols = 192;     // D1 (64 columns) + D2 (128 columns)
 constexpr size_t kSmemBytes = (size_t)kSlots * kSlotBytes + 2 * kBxBytes + 2 * kDxBytes + 1024 + 256;
 
+// Debug builds (-DTFGPC_TC_TIMING) record, per CTA and role, the clock cycles
+// spent inside each barrier wait and in the role's whole loop.
+#ifdef TFGPC_TC_TIMING
+__device__ long long g_tc_timing[160 * 5 * 8];
+#define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tt_start = clock64();
+#define TT_WAIT(site, bar, parity)                                        \
+  do {                                                                    \
+    const long long tt0 = clock64();                                      \
+    mbar_wait(bar, parity, abort_flag, err_flag);                         \
+    tt_acc[site] += clock64() - tt0;                                      \
+  } while (0)
+#define TT_ADD(site, v) tt_acc[site] += (v)
+#define TT_MARK(name) const long long name = clock64();
+#define TT_STORE(role)                                                    \
+  do {                                                                    \
+    tt_acc[7] = clock64() - tt_start;                                     \
+    for (int i = 0; i < 8; ++i) g_tc_timing[(blockIdx.x * 5 + (role)) * 8 + i] = tt_acc[i]; \
+  } while (0)
+#else
+#define TT_DECL
+#define TT_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag, err_flag)
+#define TT_ADD(site, v)
+#define TT_MARK(name)
+#define TT_STORE(role)
+#endif
+
 struct Barriers {
   uint64_t f_full[kSlots], f_empty[kSlots];
   uint64_t bx_full[2], bx_empty[2];
@@ -150,17 +176,21 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
       }
     };
     if (walk.valid) prefetch();
+    TT_DECL
     while (walk.valid) {
+      TT_MARK(tp0)
       const Tile t = t_n;
       const int m0 = m0_n, my_idx = idx_n;
       const float4 b0 = b0_n, b1 = b1_n;
       walk.advance();
       if (walk.valid) prefetch();
+      TT_MARK(tp1)
+      TT_ADD(2, tp1 - tp0);
       // ---- F: two 64-channel blocks
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb, ++unit) {
         const uint32_t slot = unit % kSlots;
-        mbar_wait(smem_u32(&bars->f_empty[slot]), ((unit / kSlots) & 1) ^ 1, abort_flag, err_flag);
+        TT_WAIT(0, smem_u32(&bars->f_empty[slot]), ((unit / kSlots) & 1) ^ 1);
         const uint32_t base = smem_u32(f_ring + (size_t)slot * kSlotBytes) + dst_lane;
         const int nv = t.pe - m0 - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
@@ -174,10 +204,12 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
                      ::"r"(smem_u32(&bars->f_full[slot])) : "memory");
       }
+      TT_MARK(tp2)
+      TT_ADD(3, tp2 - tp1);
       // ---- Bx: this lane's half row in the columns of its sample, zeros elsewhere
       {
         const uint32_t stage = item & 1;
-        mbar_wait(smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
+        TT_WAIT(1, smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1);
         const int bm = m0 + brow;
         uint4 hv, mv;
         split2_bf16(b0.x, b0.y, hv.x, mv.x);
@@ -199,7 +231,13 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         if (lane == 0) mbar_arrive(smem_u32(&bars->bx_full[stage]));
       }
       ++item;
+      TT_ADD(6, 1);
+      TT_MARK(tp3)
+      TT_ADD(4, tp3 - tp2);
     }
+#ifdef TFGPC_TC_TIMING
+    if (warp == 0 && lane == 0) TT_STORE(0);
+#endif
   } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
     // ----------------------------------------------------------- MMA issuers
     // Both walk the same blocks; each commits to the accumulator's and the dXcat
@@ -208,17 +246,18 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     if (lane == 0) {
       uint32_t unit = 0, item = 0, tile_i = 0;
       Tile next = load_tile<G>(ranges, ns, blockIdx.x);
+      TT_DECL
       for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
         const Tile t = next;
         next = load_tile<G>(ranges, ns, g + gridDim.x);
         const int nb = t.blocks();
         if (nb == 0) continue;
         const uint32_t dbuf = tile_i & 1;
-        mbar_wait(smem_u32(&bars->dx_full[dbuf]), (tile_i >> 1) & 1, abort_flag, err_flag);
+        TT_WAIT(0, smem_u32(&bars->dx_full[dbuf]), (tile_i >> 1) & 1);
         const uint32_t dx_hi = smem_u32(dx + (size_t)dbuf * kDxBytes), dx_mid = dx_hi + kPart;
         for (int b = 0; b < nb; ++b, ++item) {
           const uint32_t abuf = item & 1;
-          mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
+          TT_WAIT(1, smem_u32(&bars->acc_empty[abuf]), ((item >> 1) & 1) ^ 1);
           tc_fence_after();
           const uint32_t d1 = tmem_base + abuf * kAccCols, d2 = d1 + 64;   // D1 uses 16 G columns
           if (first) {
@@ -227,7 +266,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb, ++unit) {
               const uint32_t slot = unit % kSlots;
-              mbar_wait(smem_u32(&bars->f_full[slot]), (unit / kSlots) & 1, abort_flag, err_flag);
+              TT_WAIT(2, smem_u32(&bars->f_full[slot]), (unit / kSlots) & 1);
               fence_proxy_async();   // the gathered rows were written through the generic proxy
               tc_fence_after();
               const uint32_t f_hi = smem_u32(f_ring + (size_t)slot * kSlotBytes), f_mid = f_hi + kPart;
@@ -249,7 +288,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
             }
           } else {
             // (2) D2 = dXcat * Bx^T: reduction over the 64 (sample, k) columns
-            mbar_wait(smem_u32(&bars->bx_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
+            TT_WAIT(2, smem_u32(&bars->bx_full[abuf]), (item >> 1) & 1);
             tc_fence_after();
             const uint32_t bx_hi = smem_u32(bx + (size_t)abuf * kBxBytes), bx_mid = bx_hi + kPart;
             uint32_t accumulate = 0;
@@ -271,23 +310,28 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         umma_commit(smem_u32(&bars->dx_empty[dbuf]));
         ++tile_i;
       }
+      TT_ADD(6, item);
+      TT_STORE(first ? 1 : 2);
     }
   } else if (warp == kDxWarp) {
     // ------------------------------------------------------- dXcat loader
     if (lane == 0) {
       uint32_t tile_i = 0;
       Tile next = load_tile<G>(ranges, ns, blockIdx.x);
+      TT_DECL
       for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
         const Tile t = next;
         next = load_tile<G>(ranges, ns, g + gridDim.x);
         if (t.blocks() == 0) continue;
         const uint32_t dbuf = tile_i & 1;
-        mbar_wait(smem_u32(&bars->dx_empty[dbuf]), ((tile_i >> 1) & 1) ^ 1, abort_flag, err_flag);
+        TT_WAIT(0, smem_u32(&bars->dx_empty[dbuf]), ((tile_i >> 1) & 1) ^ 1);
         const uint32_t full = smem_u32(&bars->dx_full[dbuf]);
         mbar_expect_tx(full, kDxBytes);
         bulk_g2s(smem_u32(dx + (size_t)dbuf * kDxBytes), image + g * (int64_t)kDxBytes, kDxBytes, full);
         ++tile_i;
       }
+      TT_ADD(6, tile_i);
+      TT_STORE(3);
     }
   } else {
     // -------------------------------------------------------------- epilogue
@@ -303,7 +347,9 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
     ItemWalk<G> walk;
     walk.init(ranges, ns, groups);
     uint32_t item = 0;
+    TT_DECL
     for (; walk.valid; walk.advance(), ++item) {
+      TT_MARK(te0)
       const Tile t = walk.t;
       const int m_first = t.pa + walk.b * kRows;
       const int rows = min(kRows, t.pe - m_first);   // pairs in this block
@@ -315,10 +361,11 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         pts[u] = mp < t.pe ? __ldg(&neigh[mp].x) : 0;
       }
       const uint32_t abuf = item & 1;
-      mbar_wait(smem_u32(&bars->acc_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
+      TT_WAIT(0, smem_u32(&bars->acc_full[abuf]), (item >> 1) & 1);
       tc_fence_after();
       const bool ok = !*abort_flag;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + abuf * kAccCols;
+      TT_MARK(te1)
       if (half == 0) {
         const int m = m_first + r;
         const bool live = ok && m < t.pe;
@@ -341,17 +388,27 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
           }
         }
       }
+      TT_MARK(te2)
+      TT_ADD(1, te1 - te0);
+      TT_ADD(2, te2 - te1);
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int col0 = 32 * (half + 2 * u);
         if (col0 < rows && ok) {
           uint32_t v[32];
+          TT_MARK(te3)
           tmem_ld_32x32(taddr + 64 + col0, v);
+          TT_MARK(te4)
+          TT_ADD(3, te4 - te3);
           if (col0 + 32 <= rows) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int p = __shfl_sync(0xffffffffu, pts[u], i);
+#ifndef TFGPC_WHATIF_NO_RED
               atomicAdd(dcol + (int64_t)p * kC, __uint_as_float(v[i]));
+#else
+              if (p == -12345) dcol[i] = __uint_as_float(v[i]);
+#endif
             }
           } else {
 #pragma unroll
@@ -362,10 +419,15 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
           }
         }
       }
+      TT_MARK(te5)
+      TT_ADD(4, te5 - te2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[abuf]));
     }
+#ifdef TFGPC_TC_TIMING
+    if (warp == kEpiWarp0 && lane == 0) { TT_ADD(6, item); TT_STORE(4); }
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -419,5 +481,12 @@ int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const
   TFGPC_REQUIRE(group == 3, "tensor-core projection gradients work on groups of 3 or 4 samples");
   return launch_grads_tc<3>(st, ns, M, basis, fs, neigh, ranges, image, dbasis, dfeat, err_flag);
 }
+
+#ifdef TFGPC_TC_TIMING
+// Debug builds only: copies the timing words of the last launch to the host.
+extern "C" int tfgpc_debug_tc_timing(long long* out, int count) {
+  return (int)cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * (size_t)count);
+}
+#endif
 
 }  // namespace tfgpc

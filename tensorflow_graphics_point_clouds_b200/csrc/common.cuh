@@ -54,6 +54,15 @@ struct ProfScope {
   cudaStream_t st;
 };
 
+// While one of these lives, the ProfScopes of this host thread record nothing
+// (and so create no events and grow no record table): for entry points that
+// promise to allocate nothing.
+struct ProfPause {
+  ProfPause();
+  ~ProfPause();
+  bool was_on;
+};
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

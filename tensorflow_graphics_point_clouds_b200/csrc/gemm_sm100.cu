@@ -425,6 +425,24 @@ int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int b
   return TFGPC_OK;
 }
 
+// One warp that waits, through the same bounded wait as every role of the
+// GEMM, for a barrier phase that nothing ever completes: the wait gives up after
+// `limit_ns`, records that in the status word and the kernel returns.
+__global__ void wait_probe_kernel(int* err_flag, unsigned long long limit_ns, int* returned) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, err_flag, limit_ns);
+    *returned = 1;
+  }
+}
+
 __global__ void split_kernel(const float* __restrict__ x, int64_t n, __nv_bfloat16* __restrict__ hi,
                              __nv_bfloat16* __restrict__ mid) {
   int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -665,3 +683,26 @@ int reduce_splits(cudaStream_t stream, const float* partial, int splits, int64_t
 }
 
 }  // namespace tfgpc
+
+// Exercises the bounded wait of the tensor-core kernels (see include/tfgpc.h).
+extern "C" int tfgpc_debug_bounded_wait(void* stream, void* ws, size_t ws_bytes,
+                                        unsigned limit_us, int* returned_out) {
+  using namespace tfgpc;
+  TFGPC_REQUIRE(ws && returned_out && ws_bytes >= 1024 && (uintptr_t)ws % 256 == 0,
+                "debug_bounded_wait expects a 256-byte aligned workspace of at least 1024 bytes");
+  TFGPC_REQUIRE(limit_us >= 1 && limit_us <= 100000,
+                "debug_bounded_wait expects a limit between 1 us and 100 ms");
+  cudaStream_t st = (cudaStream_t)stream;
+  // word 0 is the status word tfgpc_mcconv_status reads, word 1 the kernel's
+  // "I returned" mark
+  int* words = (int*)ws;
+  TFGPC_CUDA(cudaMemsetAsync(words, 0, 2 * sizeof(int), st));
+  wait_probe_kernel<<<1, 32, 0, st>>>(words, (unsigned long long)limit_us * 1000ull, words + 1);
+  TFGPC_LAUNCH_CHECK();
+  int back[2] = {0, 0};
+  int rc = read_small(st, words, sizeof(back), back);
+  if (rc) return rc;
+  *returned_out = back[1];
+  return TFGPC_OK;
+}
+

@@ -91,13 +91,18 @@ __global__ void build_grid_ds_kernel(int64_t n, const int64_t* __restrict__ keys
 // Per-cloud axis-aligned bounding box (the unsorted_segment_min / _max of
 // pylib/pc/PointCloud.py:38-43).  Floats are ordered through their bit
 // patterns: non-negative values compare like signed ints, negative values like
-// reversed unsigned ints, so one integer atomic per value is enough.
+// reversed unsigned ints, so one integer atomic per value is enough.  -0.0f
+// compares equal to 0.0f but carries the bit pattern of the most negative int:
+// it is turned into +0.0f first (x + 0.0f does that in round-to-nearest), else
+// it would overwrite a negative minimum and never raise a negative maximum.
 __device__ __forceinline__ void atomic_min_float(float* addr, float v) {
+  v = __fadd_rn(v, 0.0f);
   if (v >= 0.0f) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
   else atomicMax(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
 }
 
 __device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  v = __fadd_rn(v, 0.0f);
   if (v >= 0.0f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
   else atomicMin(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
 }

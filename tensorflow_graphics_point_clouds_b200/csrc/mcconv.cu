@@ -171,12 +171,16 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
                 tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1));
   McWs w = carve(ws, K, C, Cout, ns, n_in, true);
   if (!x_in_workspace) {
+    // (with x_in_workspace the word keeps what the forward call left: a timeout
+    // there means that the projection this call is about to read is incomplete)
     TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
     rc = project(st, K, C, ns, n_in, basis, features, neighbors, ranges, w);
     if (rc) return rc;
-    rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
-    if (rc) return rc;
   }
+  // The weights are split again on every call (2 MB): every branch below then
+  // works on the values of this call's `weights`, whatever the forward call saw.
+  rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
+  if (rc) return rc;
   rc = split_to_bf16(st, out_grads, ns * Cout, w.g_hi, w.g_mid);
   if (rc) return rc;
   // dX[ns, C*K] = dOut[ns, Cout] * W^T: B rows are W's rows, reduction over Cout

@@ -373,7 +373,8 @@ void* g_static_ptr[kMaxDevices] = {nullptr};
 
 // Device address of the scratch array on the current device.  The array's name
 // is only a host-side handle in host code, so the address is looked up once
-// per device (with that device current) and cached.
+// per device (with that device current) and cached for the life of the process:
+// it does not survive a cudaDeviceReset of that device.
 int static_scratch_ptr(void** out) {
   int dev = -1;
   TFGPC_CUDA(cudaGetDevice(&dev));
@@ -412,6 +413,8 @@ extern "C" int tfgpc_find_neighbors_count_static(
   void* scratch = nullptr;
   int rc = static_scratch_ptr(&scratch);
   if (rc) return rc;
+  // per-launch timing would create CUDA events and grow a host table
+  ProfPause no_timing;
   if (tfgpc_find_neighbors_workspace_bytes(ns) > kStaticScratchBytes)
     return fail(TFGPC_ENOMEM, "static scratch of %zu bytes is too small for %lld samples",
                 kStaticScratchBytes, (long long)ns);

@@ -44,6 +44,9 @@ ProfScope::~ProfScope() {
   if (slot >= 0) cudaEventRecord(g_prof[slot].b, st);
 }
 
+ProfPause::ProfPause() : was_on(g_prof_on) { g_prof_on = false; }
+ProfPause::~ProfPause() { g_prof_on = was_on; }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -51,18 +51,24 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Bounded wait.  `abort_flag` lives in shared memory: once any role gave up,
 // all later waits of the CTA return at once.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* err_flag) {
+__device__ __forceinline__ void mbar_wait_limit(uint32_t bar, uint32_t parity,
+                                                volatile int* abort_flag, int* err_flag,
+                                                unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return;
   const unsigned long long t0 = global_ns();
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag) return;
-    if (global_ns() - t0 > kWaitLimitNs) {
+    if (global_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       atomicExch(err_flag, 1);
       return;
     }
   }
+}
+
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* err_flag) {
+  mbar_wait_limit(bar, parity, abort_flag, err_flag, kWaitLimitNs);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,

@@ -154,3 +154,40 @@ def test_mcconv_layer_matches_oracle(d, g, h):
   close(dwf.cpu().numpy(), ref_dwf)
   close(dw1.cpu().numpy(), ref_dw1, rel=2e-4)
   close(db1.cpu().numpy(), ref_db1, rel=2e-4)
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+  """Every device-side wait of the tensor-core kernels gives up after a time
+  limit and reports through the workspace's status word.  Here one warp waits
+  (1 ms limit) for a barrier phase that nothing completes: the kernel must
+  return by itself, tfgpc_mcconv_status must report TFGPC_ETIMEOUT, and the
+  next product on the same workspace must clear the word and be correct."""
+  import ctypes
+  from tensorflow_graphics_point_clouds_b200 import _lib
+  from tensorflow_graphics_point_clouds_b200._lib import c_i64, c_int, c_sz, ptr
+  lib = _lib.lib()
+  m, n, k = 256, 128, 512
+  nbytes = lib.tfgpc_matmul_workspace_bytes(c_i64(m), c_i64(n), c_i64(k))
+  ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+  stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+  returned = c_int(0)
+  _lib.check(lib.tfgpc_debug_bounded_wait(stream, ptr(ws), c_sz(nbytes), ctypes.c_uint(1000),
+                                          ctypes.byref(returned)))
+  assert returned.value == 1                      # the kernel ran to its end
+  status = c_int(0)
+  rc = lib.tfgpc_mcconv_status(stream, ptr(ws), ctypes.byref(status))
+  assert rc == 4 and status.value == 4            # TFGPC_ETIMEOUT
+  assert b"bounded wait" in lib.tfgpc_last_error()
+  # the context is intact: a product on the same workspace succeeds
+  rng = np.random.default_rng(1)
+  a = rng.normal(size=(m, k)).astype(F32); b = rng.normal(size=(k, n)).astype(F32)
+  c = torch.empty((m, n), dtype=torch.float32, device="cuda")
+  ta, tb = t(a), t(b)
+  _lib.check(lib.tfgpc_matmul_f32(stream, c_i64(m), c_i64(n), c_i64(k), ptr(ta), c_int(0),
+                                  ptr(tb), c_int(0), ptr(c), ptr(ws), c_sz(nbytes)))
+  _lib.check(lib.tfgpc_mcconv_status(stream, ptr(ws), ctypes.byref(status)))
+  assert status.value == 0
+  close(c.cpu().numpy(), a.astype(np.float64) @ b.astype(np.float64))
+  # argument checks
+  assert lib.tfgpc_debug_bounded_wait(stream, ptr(ws), c_sz(nbytes), ctypes.c_uint(0),
+                                      ctypes.byref(returned)) == 1

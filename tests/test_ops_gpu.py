@@ -364,6 +364,35 @@ def test_compute_aabb(d):
   assert np.array_equal(mn.cpu().numpy(), ref_mn) and np.array_equal(mx.cpu().numpy(), ref_mx)
 
 
+def test_compute_aabb_negative_zero():
+  """-0.0 has the bit pattern of the most negative int: it must neither replace
+  a negative minimum nor be lost as the maximum of a cloud of negative values.
+  Clouds: 0 all negative with -0.0 as its maximum, 1 mixed signs with -0.0 in
+  between, 2 only zeros of both signs; points of a cloud are spread over many
+  threads so that the atomics meet in every order."""
+  rng = np.random.default_rng(8)
+  n = 30000
+  pts = np.empty((3 * n, 3), F32)
+  pts[:n] = -rng.uniform(0.5, 5.0, (n, 3))
+  pts[n:2 * n] = rng.uniform(-5.0, 5.0, (n, 3))
+  pts[2 * n:] = 0.0
+  zeros = rng.integers(0, 3 * n, 6000)
+  pts[zeros] = -0.0
+  pts[2 * n + rng.integers(0, n, 500)] = -0.0
+  bid = np.repeat(np.arange(3), n).astype(np.int32)
+  perm = rng.permutation(3 * n)
+  for p, b in ((pts, bid), (pts[perm], bid[perm])):
+    ref_mn, ref_mx = pr.aabb(p, b, 3)          # min - 1e-9, max + 1e-9 (PointCloud.py:38-43)
+    cloud = pc.PointCloud(t(p), t(b), 3)
+    mn, mx = cloud.get_AABB()
+    assert np.array_equal(mn.cpu().numpy(), ref_mn) and np.array_equal(mx.cpu().numpy(), ref_mx)
+    raw_mn, raw_mx = ops.compute_aabb(t(p), t(b), 3)
+    exp_mn = np.full((3, 3), np.inf, F32); exp_mx = np.full((3, 3), -np.inf, F32)
+    np.minimum.at(exp_mn, b, p); np.maximum.at(exp_mx, b, p)
+    assert np.array_equal(raw_mn.cpu().numpy(), exp_mn)
+    assert np.array_equal(raw_mx.cpu().numpy(), exp_mx)
+
+
 def test_pdf_without_second_neighbor_search_matches_self_neighborhood():
   """A neighborhood whose samples are the grid's own cloud (unsorted) gets its
   densities from one search; pylib's route is the sorted self neighborhood."""

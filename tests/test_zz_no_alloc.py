@@ -3,10 +3,12 @@
 tfgpc_find_neighbors_count_static is for hosts that cannot hand the library a
 temporary device buffer (a framework that owns all device memory, a service
 with its budget already committed): its scan scratch is a fixed array inside
-the library.  This test calls it through the C ABI twice in a row, on two
+the library.  This test calls it through the C ABI three times in a row, on
 different clouds, and checks ranges and pair count against the regular entry
-point, bit for bit.  The second call runs on the leftovers of the first, which
-must not matter.  The file sorts last so that a run stopping at the first
+point, bit for bit.  Every call runs on the leftovers of the one before, which
+must not matter: the sequence is a scan over several tiles, one over a single
+tile, and again one over several tiles (whose tile sums then sit on stale
+ones).  The file sorts last so that a run stopping at the first
 failure has already been through every other test.
 """
 import ctypes
@@ -45,9 +47,9 @@ def count_both(grid, samples, sample_bids, radius):
   return ref_ranges, ref_total.value, got_ranges, got_total.value
 
 
-def test_static_scratch_count_matches_workspace_count_twice():
+def test_static_scratch_count_matches_workspace_count_on_calls_in_a_row():
   rng = np.random.default_rng(77)
-  for n_pts, n_smp, radius in ((20000, 9000, 0.05), (3000, 700, 0.2)):
+  for n_pts, n_smp, radius in ((20000, 9000, 0.05), (3000, 700, 0.2), (15000, 13000, 0.07)):
     pts = torch.from_numpy(rng.uniform(0, 1, (n_pts, 3)).astype(np.float32)).cuda()
     bid = torch.from_numpy(rng.integers(0, 4, n_pts).astype(np.int32)).cuda()
     smp = torch.from_numpy(rng.uniform(0, 1, (n_smp, 3)).astype(np.float32)).cuda()
