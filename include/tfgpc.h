@@ -354,6 +354,47 @@ int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64_t ns,
                           float* dweights_out, void* ws, size_t ws_bytes);
 int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out);
 
+/* ---- MCConv backward on a group plan --------------------------------------
+ * No counterpart in the reference; same results as tfgpc_mcconv_backward.
+ * BasisProjGrads (basis_proj_grads_kernels.cu.cc:30-151) spends one gathered
+ * feature row and one C-wide atomic update per neighbor PAIR.  Samples that lie
+ * close together share most of their neighbors, so the work is regrouped: the
+ * samples are taken four at a time in a spatially coherent visiting order
+ * `order` [ns] (a permutation of the sample indices; for a cloud searched on its
+ * own grid the key sort's permutation), and the plan lists every group's
+ * distinct neighbors with the pairs through which its samples see them.  The
+ * gradient kernel then gathers, multiplies and reduces once per distinct
+ * neighbor of a group (about half as often as per pair at 32 neighbors per
+ * point), which is what bounds it: the L2's floating-point atomic units.
+ * tfgpc_mcconv_group_plan: ranges [ns] and neighbors_sorted [M,2] as written by
+ * FindNeighbors (ids ascending within each sample's list -- required),
+ * neighbor_ids [M,2] the ids the features are indexed by (the original ids of
+ * tfgpc_original_neighbor_ids; may equal neighbors_sorted).  plan: caller
+ * buffer of _group_plan_bytes(ns, M) bytes, 256-byte aligned; it depends only on
+ * the neighborhood and the order and can be reused by every call on them.
+ * tfgpc_mcconv_backward_grouped: arguments of tfgpc_mcconv_backward plus
+ * basis_pair [M,2,K] bf16 (tfgpc_kernel_basis_split), order and plan;
+ * neighbors = neighbor_ids.  Only for shapes with _grouped_supported(K, C) != 0
+ * (K = 16, C = 128); 16-byte aligned features. */
+int tfgpc_mcconv_grouped_supported(int K, int C);
+size_t tfgpc_mcconv_group_plan_bytes(int64_t ns, int64_t M);
+int tfgpc_mcconv_group_plan(void* stream, int64_t ns, int64_t M,
+                            const int32_t* order, const int32_t* ranges,
+                            const int32_t* neighbors_sorted,
+                            const int32_t* neighbor_ids, void* plan,
+                            size_t plan_bytes);
+int tfgpc_mcconv_backward_grouped(void* stream, int K, int C, int Cout,
+                                  int64_t ns, int64_t n_in, int64_t M,
+                                  const float* basis, const void* basis_pair,
+                                  const float* features,
+                                  const int32_t* neighbors,
+                                  const int32_t* ranges, const float* weights,
+                                  const float* out_grads, int x_in_workspace,
+                                  const int32_t* order, const void* plan,
+                                  float* dbasis_out, float* dfeat_out,
+                                  float* dweights_out, void* ws,
+                                  size_t ws_bytes);
+
 /* ---- MCConv kernel basis --------------------------------------------------
  * Replaces the TensorFlow op chain of pylib/pc/layers/MCConv.py:264-269 and
  * :163-171 for a kernel MLP with one hidden layer: per neighbor pair
@@ -377,6 +418,15 @@ int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
                              int activation, float alpha,
                              const float* basis_grads, float* dw1_out,
                              float* db1_out);
+/* tfgpc_kernel_basis that also writes every basis row as the bf16 pair the
+ * tensor-core kernels multiply with: basis_pair_out [M,2,K] bf16, row m =
+ * (hi terms k = 0..K-1, mid terms), basis ~= hi + mid. */
+int tfgpc_kernel_basis_split(void* stream, int D, int K, int64_t M,
+                             const float* points_in, const float* points_out,
+                             const int32_t* neighbors, const float* pdf,
+                             const float* w1, const float* b1,
+                             float inv_radius, int activation, float alpha,
+                             float* basis_out, void* basis_pair_out);
 
 /* ---- KPConv and PointConv bases --------------------------------------------
  * The per-pair basis values of the other two convolutions of pylib/pc/layers,

@@ -58,6 +58,11 @@ SYMBOLS = {
     "tfgpc_mcconv_forward": c_int,
     "tfgpc_mcconv_backward": c_int,
     "tfgpc_mcconv_status": c_int,
+    "tfgpc_mcconv_grouped_supported": c_int,
+    "tfgpc_mcconv_group_plan_bytes": c_sz,
+    "tfgpc_mcconv_group_plan": c_int,
+    "tfgpc_mcconv_backward_grouped": c_int,
+    "tfgpc_kernel_basis_split": c_int,
     "tfgpc_kernel_basis": c_int,
     "tfgpc_kernel_basis_grads": c_int,
     "tfgpc_kp_basis": c_int,

@@ -187,6 +187,13 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
       TT_MARK(tp1)
       TT_ADD(2, tp1 - tp0);
       // ---- F: two 64-channel blocks
+#ifdef TFGPC_TC_PROD_HOIST
+      // source rows of this lane's eight copies, the same for both channel blocks
+      const __nv_bfloat16* src_row[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it)
+        src_row[it] = fs_lane + (int64_t)__shfl_sync(0xffffffffu, my_idx, it, 16) * 2 * kC;
+#endif
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb, ++unit) {
         const uint32_t slot = unit % kSlots;
@@ -195,10 +202,14 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
         const int nv = t.pe - m0 - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
+#ifdef TFGPC_TC_PROD_HOIST
+          if (it < nv) cp_async16(base + it * 128 + ((j ^ it) << 4), src_row[it] + kb * 64);
+#else
           const int idx = __shfl_sync(0xffffffffu, my_idx, it, 16);
           // row row_base + 8 * l4 + it: (row % 8) == it, the swizzle is a constant
           if (it < nv)
             cp_async16(base + it * 128 + ((j ^ it) << 4), fs_lane + (int64_t)idx * 2 * kC + kb * 64);
+#endif
         }
         // arrives on the slot's barrier once this thread's copies have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
@@ -401,6 +412,17 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
           TT_MARK(te4)
           TT_ADD(3, te4 - te3);
           if (col0 + 32 <= rows) {
+#ifdef TFGPC_TC_EPI_LDG
+            // the 32 neighbor ids by uniform loads (one sector each, served by L1),
+            // all independent of one another and of the reductions
+            const int2* idp = neigh + m_first + col0;
+            int p[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = __ldg(&idp[i].x);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              atomicAdd(dcol + (int64_t)p[i] * kC, __uint_as_float(v[i]));
+#else
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int p = __shfl_sync(0xffffffffu, pts[u], i);
@@ -410,6 +432,7 @@ basis_proj_grads_tc_kernel(int64_t ns, int64_t M, const float* __restrict__ basi
               if (p == -12345) dcol[i] = __uint_as_float(v[i]);
 #endif
             }
+#endif
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {

@@ -458,6 +458,24 @@ __global__ void split_kernel(const float* __restrict__ x, int64_t n, __nv_bfloat
   }
 }
 
+// Row v of the output is the split of row order[v] of x (cols a multiple of 4,
+// 16-byte aligned rows).
+__global__ void split_rows_gather_kernel(const float* __restrict__ x,
+                                         const int32_t* __restrict__ order, int64_t rows,
+                                         int cols4, __nv_bfloat16* __restrict__ hi,
+                                         __nv_bfloat16* __restrict__ mid) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols4) return;
+  const int64_t v = i / cols4;
+  const int c = (int)(i - v * cols4);
+  const float4 val = __ldg(reinterpret_cast<const float4*>(x + (int64_t)__ldg(order + v) * cols4 * 4) + c);
+  uint2 h, m;
+  split2_bf16(val.x, val.y, h.x, m.x);
+  split2_bf16(val.z, val.w, h.y, m.y);
+  *reinterpret_cast<uint2*>(hi + i * 4) = h;
+  *reinterpret_cast<uint2*>(mid + i * 4) = m;
+}
+
 __global__ void split_transpose_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
                                        __nv_bfloat16* __restrict__ hi_t,
                                        __nv_bfloat16* __restrict__ mid_t) {
@@ -660,6 +678,18 @@ int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16*
   if (n <= 0) return TFGPC_OK;
   ProfScope prof(stream, "split_bf16");
   split_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, stream>>>(x, n, hi, mid);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+int split_rows_gather_to_bf16(cudaStream_t stream, const float* x, const int32_t* order,
+                              int64_t rows, int64_t cols, __nv_bfloat16* hi, __nv_bfloat16* mid) {
+  if (rows <= 0 || cols <= 0) return TFGPC_OK;
+  TFGPC_REQUIRE(cols % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)hi % 8 == 0 &&
+                (uintptr_t)mid % 8 == 0, "split_rows_gather expects 16-byte aligned rows");
+  ProfScope prof(stream, "split_bf16");
+  split_rows_gather_kernel<<<blocks_for(rows * (cols / 4), 256), 256, 0, stream>>>(
+      x, order, rows, (int)(cols / 4), hi, mid);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

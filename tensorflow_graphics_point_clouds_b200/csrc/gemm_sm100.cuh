@@ -69,6 +69,9 @@ int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K);
 int split_to_bf16(cudaStream_t stream, const float* x, int64_t n, __nv_bfloat16* hi,
                   __nv_bfloat16* mid);
 // [rows, cols] fp32 -> transposed [cols, rows] bf16 pair.
+// hi/mid row v = split of row order[v] of x [rows, cols] (cols a multiple of 4).
+int split_rows_gather_to_bf16(cudaStream_t stream, const float* x, const int32_t* order,
+                              int64_t rows, int64_t cols, __nv_bfloat16* hi, __nv_bfloat16* mid);
 int split_transpose_to_bf16(cudaStream_t stream, const float* x, int64_t rows, int64_t cols,
                             __nv_bfloat16* hi_t, __nv_bfloat16* mid_t);
 // out[i] = sum_s partial[s * stride + i], i < n.

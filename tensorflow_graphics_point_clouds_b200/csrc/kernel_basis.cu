@@ -11,7 +11,7 @@
 // Backward: dpre = dbasis / pdf * act'(pre); dw1[d, k] = sum_m diff_d * dpre_k,
 // db1[k] = sum_m dpre_k, accumulated in registers over a grid-stride loop,
 // reduced through shuffles and shared memory, one atomic per block and value.
-#include "common.cuh"
+#include "basis_proj.cuh"
 
 namespace tfgpc {
 namespace {
@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(kKbThreads)
 kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __restrict__ p_out,
                     const int2* __restrict__ neigh, const float* __restrict__ pdf,
                     const float* __restrict__ w1, const float* __restrict__ b1, float inv_radius,
-                    int act, float alpha, float* __restrict__ basis) {
+                    int act, float alpha, float* __restrict__ basis,
+                    __nv_bfloat16* __restrict__ pair) {
   __shared__ float w_s[D * K + K];
   for (int i = threadIdx.x; i < D * K + K; i += kKbThreads)
     w_s[i] = i < D * K ? __ldg(w1 + i) : __ldg(b1 + i - D * K);
@@ -86,6 +87,17 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
       } else {
         reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
         reinterpret_cast<float4*>(dst)[2 * q + 1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+      if (pair) {
+        // the same row as bf16 hi / mid terms: [m][hi K | mid K]
+        uint4 hv, mv;
+        split2_bf16(v[0], v[1], hv.x, mv.x);
+        split2_bf16(v[2], v[3], hv.y, mv.y);
+        split2_bf16(v[4], v[5], hv.z, mv.z);
+        split2_bf16(v[6], v[7], hv.w, mv.w);
+        uint4* prow = reinterpret_cast<uint4*>(pair + m * (2 * K));
+        prow[q] = hv;
+        prow[K / 8 + q] = mv;
       }
     }
   }
@@ -281,31 +293,52 @@ int check_kb_args(const char* op, int D, int K, int64_t M, int act) {
 
 using namespace tfgpc;
 
-extern "C" int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M, const float* points_in,
-                                  const float* points_out, const int32_t* neighbors,
-                                  const float* pdf, const float* w1, const float* b1,
-                                  float inv_radius, int activation, float alpha,
-                                  float* basis_out) {
+static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float* points_in,
+                             const float* points_out, const int32_t* neighbors, const float* pdf,
+                             const float* w1, const float* b1, float inv_radius, int activation,
+                             float alpha, float* basis_out, __nv_bfloat16* pair_out) {
   int rc = check_kb_args("KernelBasis", D, K, M, activation);
   if (rc) return rc;
   if (M == 0) return TFGPC_OK;
   TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && basis_out,
                 "KernelBasis got a null pointer");
-  TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0, "KernelBasis expects a 16-byte aligned output");
+  TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0 && (uintptr_t)pair_out % 16 == 0,
+                "KernelBasis expects 16-byte aligned outputs");
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(M, kKbThreads), (unsigned)(sm_count() * 16));
   ProfScope prof(st, "kernel_basis");
   if ((uintptr_t)basis_out % 32 == 0) {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_out)));
+        alpha, basis_out, pair_out)));
   } else {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_out)));
+        alpha, basis_out, pair_out)));
   }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
+}
+
+extern "C" int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M, const float* points_in,
+                                  const float* points_out, const int32_t* neighbors,
+                                  const float* pdf, const float* w1, const float* b1,
+                                  float inv_radius, int activation, float alpha,
+                                  float* basis_out) {
+  return kernel_basis_impl(stream, D, K, M, points_in, points_out, neighbors, pdf, w1, b1,
+                           inv_radius, activation, alpha, basis_out, nullptr);
+}
+
+extern "C" int tfgpc_kernel_basis_split(void* stream, int D, int K, int64_t M,
+                                        const float* points_in, const float* points_out,
+                                        const int32_t* neighbors, const float* pdf,
+                                        const float* w1, const float* b1, float inv_radius,
+                                        int activation, float alpha, float* basis_out,
+                                        void* basis_pair_out) {
+  TFGPC_REQUIRE(M == 0 || basis_pair_out, "KernelBasis got a null pointer");
+  return kernel_basis_impl(stream, D, K, M, points_in, points_out, neighbors, pdf, w1, b1,
+                           inv_radius, activation, alpha, basis_out,
+                           (__nv_bfloat16*)basis_pair_out);
 }
 
 extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,

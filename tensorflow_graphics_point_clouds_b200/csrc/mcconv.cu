@@ -33,6 +33,12 @@ int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const
                         const __nv_bfloat16* fs, const int32_t* neigh, const int32_t* ranges,
                         const void* image, float* dbasis, float* dfeat, int* err_flag);
 
+// basis_proj_grads_tcu.cu: the gradients on the rows of a group plan
+int basis_proj_grads_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* plan,
+                         const __nv_bfloat16* basis_pair, const __nv_bfloat16* fs,
+                         const int32_t* ranges, const void* image, float* dbasis, float* dfeat,
+                         int* err_flag);
+
 namespace {
 
 struct McWs {
@@ -43,6 +49,7 @@ struct McWs {
   float* dx;                        // [ns, C*K]    (backward)
   __nv_bfloat16* fs;                // [n_in, 2, C] split features (tensor-core projection)
   __nv_bfloat16 *wt_hi, *wt_mid;    // [Cout, C*K]: W transposed (backward)
+  __nv_bfloat16 *gv_hi, *gv_mid;    // [ns, Cout]: out_grads rows in visiting order (grouped backward)
   int dw_splits;
   size_t bytes;
 };
@@ -63,6 +70,7 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   if (basis_proj_mma_supported(K, C)) w.fs = (__nv_bfloat16*)take((size_t)n_in * C * 4);
   w.dw_splits = 1;
   w.g_hi = w.g_mid = nullptr; w.dx = nullptr; w.wt_hi = w.wt_mid = nullptr;
+  w.gv_hi = w.gv_mid = nullptr;
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
@@ -72,6 +80,10 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
     w.wt_hi = (__nv_bfloat16*)take(ck * Cout * 2);
     w.wt_mid = (__nv_bfloat16*)take(ck * Cout * 2);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
+    if (basis_proj_grads_tc_supported(K, C)) {
+      w.gv_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
+      w.gv_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
+    }
   }
   w.bytes = (size_t)(p - (char*)ws);
   return w;
@@ -226,6 +238,74 @@ extern "C" int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64
   GemmOperand g_mn{w.g_hi, w.g_mid, (int64_t)Cout, Major::MN};
   // the reduction over the samples is cut into slices (see gemm_pick_k_splits)
   // that the GEMM adds into dweights_out
+  return gemm_bf16x3(st, ck, Cout, ns, x_mn, g_mn, dweights_out, Cout, w.dw_splits, 0, w.err);
+}
+
+extern "C" int tfgpc_mcconv_grouped_supported(int K, int C) {
+  return basis_proj_grads_tc_supported(K, C) ? 1 : 0;
+}
+
+// The backward pass on the rows of a group plan: dX is produced in the plan's
+// visiting order (the rows of out_grads are gathered while they are split), the
+// projection gradients run per distinct neighbor of a group instead of per
+// pair, dW is unchanged.
+extern "C" int tfgpc_mcconv_backward_grouped(
+    void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in, int64_t M, const float* basis,
+    const void* basis_pair, const float* features, const int32_t* neighbors,
+    const int32_t* ranges, const float* weights, const float* out_grads, int x_in_workspace,
+    const int32_t* order, const void* plan, float* dbasis_out, float* dfeat_out,
+    float* dweights_out, void* ws, size_t ws_bytes) {
+  int rc = check_mc_args("MCConvBackward", K, C, Cout, ns, n_in, M);
+  if (rc) return rc;
+  TFGPC_REQUIRE(basis_proj_grads_tc_supported(K, C),
+                "MCConvBackward on a group plan expects K = 16 basis functions and C = 128 features");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t ck = (int64_t)C * K;
+  TFGPC_REQUIRE(dweights_out && weights, "MCConvBackward got a null pointer");
+  if (ns == 0 || M == 0) {
+    TFGPC_CUDA(cudaMemsetAsync(dweights_out, 0, sizeof(float) * (size_t)ck * Cout, st));
+    if (M > 0 && dbasis_out) TFGPC_CUDA(cudaMemsetAsync(dbasis_out, 0, sizeof(float) * (size_t)M * K, st));
+    if (n_in > 0 && dfeat_out) TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+    return TFGPC_OK;
+  }
+  TFGPC_REQUIRE(basis && basis_pair && features && neighbors && ranges && out_grads && order &&
+                plan && dbasis_out && dfeat_out && ws, "MCConvBackward got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)basis_pair % 16 == 0 &&
+                (uintptr_t)out_grads % 16 == 0 && (uintptr_t)features % 16 == 0 &&
+                (uintptr_t)dbasis_out % 32 == 0 && (uintptr_t)dfeat_out % 16 == 0 &&
+                (uintptr_t)ws % 256 == 0 && (uintptr_t)plan % 256 == 0,
+                "MCConvBackward on a group plan expects 16-byte aligned buffers (dbasis 32, "
+                "workspace and plan 256)");
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1))
+    return fail(TFGPC_ENOMEM, "MCConvBackward workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1));
+  McWs w = carve(ws, K, C, Cout, ns, n_in, true);
+  if (!x_in_workspace) {
+    TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
+    rc = project(st, K, C, ns, n_in, basis, features, neighbors, ranges, w);
+    if (rc) return rc;
+  }
+  rc = split_to_bf16(st, out_grads, ns * Cout, w.g_hi, w.g_mid);
+  if (rc) return rc;
+  rc = split_rows_gather_to_bf16(st, out_grads, order, ns, Cout, w.gv_hi, w.gv_mid);
+  if (rc) return rc;
+  constexpr int group = 4;
+  if (ns % group != 0) {
+    char* last = (char*)w.dx + (size_t)(ns / group) * 4 * ck * 4;
+    TFGPC_CUDA(cudaMemsetAsync(last, 0, (size_t)4 * ck * 4, st));
+  }
+  rc = split_transpose_to_bf16(st, weights, ck, Cout, w.wt_hi, w.wt_mid);
+  if (rc) return rc;
+  GemmOperand wt_mn{w.wt_hi, w.wt_mid, ck, Major::MN};
+  GemmOperand gv_k{w.gv_hi, w.gv_mid, (int64_t)Cout, Major::K};
+  rc = gemm_bf16x3_grad_image_tn(st, C, ns, Cout, wt_mn, gv_k, w.dx, group, w.err);
+  if (rc) return rc;
+  TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
+  rc = basis_proj_grads_tcu(st, ns, M, plan, (const __nv_bfloat16*)basis_pair, w.fs, ranges, w.dx,
+                            dbasis_out, dfeat_out, w.err);
+  if (rc) return rc;
+  GemmOperand x_mn{w.x_hi, w.x_mid, ck, Major::MN};
+  GemmOperand g_mn{w.g_hi, w.g_mid, (int64_t)Cout, Major::MN};
   return gemm_bf16x3(st, ck, Cout, ns, x_mn, g_mn, dweights_out, Cout, w.dw_splits, 0, w.err);
 }
 

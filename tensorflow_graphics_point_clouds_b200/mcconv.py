@@ -90,6 +90,25 @@ class ProjectionGemm:
         ptr(self.ws), c_sz(self.nbytes)))
     return dbasis, dfeat, dw
 
+  def backward_grouped(self, basis, basis_pair, features, neighbors, ranges, weights, out_grads,
+                       order, plan, reuse_forward=True):
+    """The same gradients through tfgpc_mcconv_backward_grouped: the projection
+    gradients run once per distinct neighbor of a group of four samples (taken in
+    `order`) instead of once per pair."""
+    basis, features, weights = _f32(basis), _f32(features), _f32(weights)
+    neighbors, ranges, out_grads = _i32(neighbors), _i32(ranges), _f32(out_grads)
+    dbasis = torch.empty_like(basis)
+    dfeat = torch.empty_like(features)
+    dw = torch.empty_like(weights)
+    self._ensure_workspace(features.shape[0])
+    _lib.check(_lib.lib().tfgpc_mcconv_backward_grouped(
+        _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
+        c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(basis_pair),
+        ptr(features), ptr(neighbors), ptr(ranges), ptr(weights), ptr(out_grads),
+        c_int(int(reuse_forward and self._x_valid)), ptr(_i32(order)), ptr(plan), ptr(dbasis),
+        ptr(dfeat), ptr(dw), ptr(self.ws), c_sz(self.nbytes)))
+    return dbasis, dfeat, dw
+
   def check_status(self):
     """Blocks on the stream; raises TfgpcError(4) if a GEMM wait timed out."""
     status = c_int(0)
@@ -137,6 +156,43 @@ def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activati
   return basis
 
 
+def kernel_basis_split(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
+                       alpha=0.2):
+  """kernel_basis that also returns every row as the bf16 (hi, mid) pair the
+  tensor-core kernels multiply with: (basis [M, K] float32, pair [M, 2, K] bf16)."""
+  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
+  d, k = w1.shape
+  m = neighbors.shape[0]
+  basis = torch.empty((m, k), dtype=torch.float32, device=points_in.device)
+  pair = torch.empty((m, 2, k), dtype=torch.bfloat16, device=points_in.device)
+  _lib.check(_lib.lib().tfgpc_kernel_basis_split(
+      _stream(), c_int(d), c_int(k), c_i64(m), ptr(points_in), ptr(points_out), ptr(neighbors),
+      ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)), c_int(activation),
+      ctypes.c_float(alpha), ptr(basis), ptr(pair)))
+  return basis, pair
+
+
+def group_plan(neighborhood, order=None):
+  """Row plan of the grouped kernels for a neighborhood (tfgpc_mcconv_group_plan):
+  the samples four at a time in `order` (default: the neighborhood's own visiting
+  order, else the sample order), every group's distinct neighbors and the pairs
+  that reach them.  Returns (order [ns] int32, plan buffer)."""
+  ranges = _i32(neighborhood._samples_neigh_ranges)
+  ns, m = ranges.shape[0], neighborhood._neighbors.shape[0]
+  if order is None:
+    order = getattr(neighborhood, '_sample_order', None)
+  if order is None:
+    order = torch.arange(ns, dtype=torch.int32, device=ranges.device)
+  order = _i32(order)
+  nbytes = _lib.lib().tfgpc_mcconv_group_plan_bytes(c_i64(ns), c_i64(m))
+  plan = _workspace(nbytes, ranges.device)
+  _lib.check(_lib.lib().tfgpc_mcconv_group_plan(
+      _stream(), c_i64(ns), c_i64(m), ptr(order), ptr(ranges), ptr(_i32(neighborhood._neighbors)),
+      ptr(_i32(neighborhood._original_neigh_ids)), ptr(plan), c_sz(nbytes)))
+  return order, plan
+
+
 def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, basis_grads,
                        activation=0, alpha=0.2):
   """Gradients of kernel_basis with respect to w1 and b1 (tfgpc_kernel_basis_grads)."""
@@ -159,8 +215,10 @@ class MCConv:
   Weights use the reference's layouts: w1 [G, D, H], b1 [G, 1, H] (one hidden
   layer kernel MLP, leaky ReLU), wf [G, C_in*H, C_out/G]."""
 
-  def __init__(self, w1, b1, wf, num_features_in):
+  def __init__(self, w1, b1, wf, num_features_in, grouped=True):
     self.w1, self.b1, self.wf = _f32(w1), _f32(b1), _f32(wf)
+    self.grouped = bool(grouped)
+    self._grouped = None
     self.num_mlps, self.dims, self.hidden = self.w1.shape
     self.cin = int(num_features_in)
     self.cout = self.wf.shape[2] * self.num_mlps
@@ -190,9 +248,18 @@ class MCConv:
     neigh = neighborhood or self.build_neighborhood(point_cloud_in, point_cloud_out, radius)
     pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
     w1, b1 = self._flat_kernel_weights()
-    basis = kernel_basis(point_cloud_in._points, point_cloud_out._points,
-                         neigh._original_neigh_ids, pdf, w1, b1, radius)
     ns = point_cloud_out._points.shape[0]
+    # wide layers run their backward pass on a group plan (see group_plan)
+    grouped = (keep_for_backward and self.grouped and neigh._neighbors.shape[0] > 0 and
+               _lib.lib().tfgpc_mcconv_grouped_supported(c_int(self.k), c_int(self.cin)) != 0)
+    if grouped:
+      basis, pair = kernel_basis_split(point_cloud_in._points, point_cloud_out._points,
+                                       neigh._original_neigh_ids, pdf, w1, b1, radius)
+      self._grouped = (pair,) + group_plan(neigh)
+    else:
+      basis = kernel_basis(point_cloud_in._points, point_cloud_out._points,
+                           neigh._original_neigh_ids, pdf, w1, b1, radius)
+      self._grouped = None
     if (self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward):
       self._op = ProjectionGemm(self.k, self.cin, self.cout, ns, features.device,
                                 backward=keep_for_backward)
@@ -208,8 +275,14 @@ class MCConv:
     """Gradients of the last forward call: (d_features, d_w1, d_b1, d_wf) in the
     layouts of the weights."""
     neigh, pc_in, pc_out, radius, pdf, basis, features, wd, w1, b1 = self._saved
-    dbasis, dfeat, dwd = self._op.backward(basis, features, neigh._original_neigh_ids,
-                                           neigh._samples_neigh_ranges, wd, out_grads)
+    if self._grouped is not None:
+      pair, order, plan = self._grouped
+      dbasis, dfeat, dwd = self._op.backward_grouped(
+          basis, pair, features, neigh._original_neigh_ids, neigh._samples_neigh_ranges, wd,
+          out_grads, order, plan)
+    else:
+      dbasis, dfeat, dwd = self._op.backward(basis, features, neigh._original_neigh_ids,
+                                             neigh._samples_neigh_ranges, wd, out_grads)
     dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, neigh._original_neigh_ids, pdf,
                                   w1, b1, radius, dbasis)
     dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()

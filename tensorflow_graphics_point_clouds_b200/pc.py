@@ -103,6 +103,9 @@ class Neighborhood:
     # samples that are the grid's own cloud in its unsorted order: the key sort's
     # permutation lists them cell by cell, the sequence the search is fastest in
     order = grid._sorted_indices if smp is grid._point_cloud else None
+    # a sequence that visits the samples cell by cell, where one is known (the
+    # samples of a self neighborhood are the sorted points: already in it)
+    self._sample_order = order
     self._samples_neigh_ranges, self._neighbors = ops.find_neighbors(
         smp._points, smp._batch_ids, grid._sorted_points, grid._sorted_keys, grid.get_DS(),
         grid._num_cells, grid._scaled_aabb_min, grid._inv_cell_sizes,

@@ -1,0 +1,136 @@
+"""The group plan and the backward pass that runs on it.
+
+The plan lists, for groups of four samples taken in a visiting order, the
+distinct neighbors of the group and the pairs that reach them; it is checked
+against a direct NumPy construction.  The grouped backward pass must give the
+gradients of the plain one (tfgpc_mcconv_backward) and of the oracle, within
+|x - y| <= 1e-4 * max(|y|, rms(y)).
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pylib_ref as pr
+from tensorflow_graphics_point_clouds_b200 import _lib, mcconv, pc
+from test_ops_gpu import close, t, random_cloud
+
+pytestmark = pytest.mark.gpu
+F32 = np.float32
+
+
+def read_plan(plan, ns, m):
+  """The arrays of a plan buffer (layout of csrc/group_plan.cu)."""
+  groups = (ns + 3) // 4
+  raw = plan.cpu().numpy()
+  base = plan.data_ptr()
+  pos = (-base) % 256          # the library aligns nothing itself: buffers come 256-byte aligned
+  assert pos == 0
+
+  def take(nbytes, dtype, count):
+    nonlocal pos
+    a = raw[pos:pos + count * np.dtype(dtype).itemsize].view(dtype)
+    pos += (nbytes + 255) // 256 * 256
+    return a
+  begin = take((groups + 1) * 4, np.int32, groups + 1)
+  rows = take(max(groups, 1) * 4, np.int32, groups)
+  ids = take((m + 256) * 4, np.int32, m + 256)
+  pairs = take((m + 256) * 16, np.int32, (m + 256) * 4).reshape(-1, 4)
+  return begin, rows, ids, pairs
+
+
+def check_plan(nb, order, plan):
+  ranges = nb._samples_neigh_ranges.cpu().numpy()
+  srt = nb._neighbors.cpu().numpy()
+  ids = nb._original_neigh_ids.cpu().numpy()
+  order = order.cpu().numpy()
+  ns, m = len(ranges), len(srt)
+  begin, rows, row_ids, row_pairs = read_plan(plan, ns, m)
+  starts = np.concatenate([[0], ranges[:-1]])
+  seen = np.zeros(m, bool)
+  for g in range((ns + 3) // 4):
+    smp = order[4 * g:4 * g + 4]
+    lists = [np.arange(starts[s], ranges[s]) for s in smp]
+    total = sum(len(l) for l in lists)
+    assert begin[g + 1] - begin[g] == total
+    r0, nr = begin[g], rows[g]
+    if total > 512:
+      assert nr == total                       # not merged: one row per pair
+    else:
+      union = np.unique(np.concatenate([srt[l, 0] for l in lists])) if total else np.zeros(0, int)
+      assert nr == len(union)
+    for q, l in enumerate(lists):
+      col = row_pairs[r0:r0 + nr, q]
+      have = col[col >= 0]
+      assert np.array_equal(np.sort(have), l)  # every pair of the sample exactly once
+      assert np.array_equal(row_ids[r0:r0 + nr][col >= 0], ids[have, 0])
+      seen[have] = True
+    for q in range(len(lists), 4):
+      assert np.all(row_pairs[r0:r0 + nr, q] == -1)
+  assert seen.all()
+
+
+@pytest.mark.parametrize("n_pts,n_smp,radius,own", [(3000, 0, 0.12, True), (3000, 701, 0.2, False),
+                                                    (2000, 0, 0.45, True), (500, 3, 0.5, False),
+                                                    (3000, 0, 0.03, True)])
+def test_group_plan_matches_numpy(n_pts, n_smp, radius, own):
+  rng = np.random.default_rng(n_pts + n_smp)
+  pts, bid = random_cloud(rng, 3, n_pts, 3)
+  cloud = pc.PointCloud(t(pts), t(bid), 3)
+  grid = pc.Grid(cloud, radius)
+  if own:
+    nb = pc.Neighborhood(grid, radius, cloud)           # visiting order = key sort permutation
+  else:
+    smp, sbid = random_cloud(rng, 3, n_smp, 3)
+    nb = pc.Neighborhood(grid, radius, pc.PointCloud(t(smp), t(sbid), 3))
+  order, plan = mcconv.group_plan(nb)
+  torch.cuda.synchronize()
+  check_plan(nb, order, plan)
+
+
+@pytest.mark.parametrize("n_pts,radius,own", [(3001, 0.12, True), (2500, 0.3, True),
+                                              (1500, 0.55, True), (3000, 0.1, False),
+                                              (602, 0.05, True)])
+def test_grouped_backward_matches_plain_and_oracle(n_pts, radius, own):
+  """C_in = 128, K = 16: sample counts that are not multiples of four, groups
+  with more than one 128-row block, groups too large to merge, samples without
+  neighbors other than themselves, samples in an arbitrary order."""
+  rng = np.random.default_rng(n_pts)
+  b, cin, cout, h = 3, 128, 64, 16
+  pts, bid = random_cloud(rng, b, n_pts, 3)
+  feat = rng.normal(size=(n_pts, cin)).astype(F32)
+  w1 = rng.normal(size=(1, 3, h)).astype(F32)
+  b1 = (rng.normal(size=(1, 1, h)) * 0.1).astype(F32)
+  wf = (rng.normal(size=(1, cin * h, cout)) * 0.05).astype(F32)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  if own:
+    smp_cloud, smp, sbid = cloud, pts, bid
+  else:
+    smp, sbid = random_cloud(rng, b, 777, 3)
+    smp_cloud = pc.PointCloud(t(smp), t(sbid), b)
+  d_out = rng.normal(size=(len(smp), cout)).astype(F32)
+  outs = []
+  for grouped in (True, False):
+    layer = mcconv.MCConv(t(w1), t(b1), t(wf), cin, grouped=grouped)
+    out = layer.forward(t(feat), cloud, smp_cloud, radius)
+    assert (layer._grouped is not None) == grouped
+    res = layer.backward(t(d_out))
+    layer._op.check_status()
+    outs.append([out] + list(res))
+  for a, bb in zip(*outs):
+    close(a.cpu().numpy(), bb.cpu().numpy())
+  # oracle
+  g_ref = pr.Grid(pts, bid, b, radius)
+  nb_ref = pr.Neighborhood(g_ref, radius, smp, sbid)
+  pdf = nb_ref.get_pdf(bandwidth=0.2, mode=0)
+  basis, diff, hid = pr.mcconv_basis(pts, smp, nb_ref, pdf, w1, b1, radius)
+  ref_out, x = pr.mcconv_forward(feat, basis, nb_ref, wf)
+  ref_dwf, ref_db, ref_df, _ = pr.mcconv_backward(feat, basis, nb_ref, wf, x, d_out)
+  out, dfeat, dw1, db1, dwf = outs[0]
+  close(out.cpu().numpy(), ref_out)
+  close(dfeat.cpu().numpy(), ref_df)
+  close(dwf.cpu().numpy(), ref_dwf)
+  dpre = ref_db.astype(np.float64) / pdf.reshape(-1, 1) * np.where(hid > 0, 1.0, 0.2)
+  close(dw1.cpu().numpy(), (diff.astype(np.float64).T @ dpre).reshape(3, 1, h).transpose(1, 0, 2),
+        rel=2e-4)
