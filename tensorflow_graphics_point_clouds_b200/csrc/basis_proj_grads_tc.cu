@@ -44,6 +44,10 @@ using namespace bptc;
 
 namespace {
 
+#ifdef TFGPC_TC_TIMING
+__device__ long long tt_array[160 * 5 * 8];
+#endif
+
 constexpr int kProdWarps = 8;
 constexpr int kMmaWarp = 8;            // issues product (1); warp 9 issues product (2)
 constexpr int kDxWarp = 10;
@@ -57,32 +61,6 @@ constexpr uint32_t kDxBytes = 2 * kPart;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCols = 192;     // D1 (64 columns) + D2 (128 columns)
 constexpr size_t kSmemBytes = (size_t)kSlots * kSlotBytes + 2 * kBxBytes + 2 * kDxBytes + 1024 + 256;
-
-// Debug builds (-DTFGPC_TC_TIMING) record, per CTA and role, the clock cycles
-// spent inside each barrier wait and in the role's whole loop.
-#ifdef TFGPC_TC_TIMING
-__device__ long long g_tc_timing[160 * 5 * 8];
-#define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tt_start = clock64();
-#define TT_WAIT(site, bar, parity)                                        \
-  do {                                                                    \
-    const long long tt0 = clock64();                                      \
-    mbar_wait(bar, parity, abort_flag, err_flag);                         \
-    tt_acc[site] += clock64() - tt0;                                      \
-  } while (0)
-#define TT_ADD(site, v) tt_acc[site] += (v)
-#define TT_MARK(name) const long long name = clock64();
-#define TT_STORE(role)                                                    \
-  do {                                                                    \
-    tt_acc[7] = clock64() - tt_start;                                     \
-    for (int i = 0; i < 8; ++i) g_tc_timing[(blockIdx.x * 5 + (role)) * 8 + i] = tt_acc[i]; \
-  } while (0)
-#else
-#define TT_DECL
-#define TT_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag, err_flag)
-#define TT_ADD(site, v)
-#define TT_MARK(name)
-#define TT_STORE(role)
-#endif
 
 struct Barriers {
   uint64_t f_full[kSlots], f_empty[kSlots];
@@ -508,7 +486,7 @@ int basis_proj_grads_tc(cudaStream_t st, int group, int64_t ns, int64_t M, const
 #ifdef TFGPC_TC_TIMING
 // Debug builds only: copies the timing words of the last launch to the host.
 extern "C" int tfgpc_debug_tc_timing(long long* out, int count) {
-  return (int)cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(long long) * (size_t)count);
+  return (int)cudaMemcpyFromSymbol(out, tt_array, sizeof(long long) * (size_t)count);
 }
 #endif
 

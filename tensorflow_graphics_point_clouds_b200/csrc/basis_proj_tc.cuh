@@ -88,6 +88,32 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
 }
 
 
+// Debug builds (-DTFGPC_TC_TIMING) record, per CTA and role, the clock cycles
+// spent inside each barrier wait and in the role's whole loop, in a file-scope
+// array `tt_array` [160 * 5 * 8] that the including file defines.
+#ifdef TFGPC_TC_TIMING
+#define TT_DECL long long tt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tt_start = clock64();
+#define TT_WAIT(site, bar, parity)                                        \
+  do {                                                                    \
+    const long long tt0 = clock64();                                      \
+    mbar_wait(bar, parity, abort_flag, err_flag);                         \
+    tt_acc[site] += clock64() - tt0;                                      \
+  } while (0)
+#define TT_ADD(site, v) tt_acc[site] += (v)
+#define TT_MARK(name) const long long name = clock64();
+#define TT_STORE(role)                                                    \
+  do {                                                                    \
+    tt_acc[7] = clock64() - tt_start;                                     \
+    for (int i = 0; i < 8; ++i) tt_array[(blockIdx.x * 5 + (role)) * 8 + i] = tt_acc[i]; \
+  } while (0)
+#else
+#define TT_DECL
+#define TT_WAIT(site, bar, parity) mbar_wait(bar, parity, abort_flag, err_flag)
+#define TT_ADD(site, v)
+#define TT_MARK(name)
+#define TT_STORE(role)
+#endif
+
 // Instruction descriptor of tcgen05.mma kind::f16: D fp32, A and B bf16.
 inline uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
   uint32_t d = 0;

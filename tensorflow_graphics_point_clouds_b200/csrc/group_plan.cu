@@ -16,9 +16,10 @@
 //                                   contiguous; the space between two groups is
 //                                   sized for "no sharing at all" and partly unused)
 //   int32 group_rows[groups]        number of rows of group g
-//   int32 rows_id[M + pad]          neighbor id of a row (index into the features)
-//   int4  rows_pair[M + pad]        pair index per sample slot of the group, -1 if
-//                                   the sample does not see this neighbor
+//   int32 rows_id[M + 3 groups + pad]   neighbor id of a row (index into the features)
+//   int4  rows_pair[same]               pair index per sample slot of the group, -1
+//                                       if the sample does not see this neighbor
+// (every group starts on a multiple of four rows)
 //   scratch of the scan
 // Groups whose pair count exceeds kMaxMerge are not merged (one row per pair).
 #include "group_plan.cuh"
@@ -36,7 +37,7 @@ PlanView plan_view(void* buf, int64_t ns, int64_t M) {
   v.groups = (ns + kG - 1) / kG;
   char* p = (char*)buf;
   auto take = [&](size_t b) { char* r = p; p += align_up(b, 256); return r; };
-  const size_t rows = (size_t)M + kRowPad;
+  const size_t rows = (size_t)M + 3 * (size_t)v.groups + kRowPad;
   v.group_begin = (int32_t*)take((size_t)(v.groups + 1) * 4);
   v.group_rows = (int32_t*)take((size_t)(v.groups > 0 ? v.groups : 1) * 4);
   v.rows_id = (int32_t*)take(rows * 4);
@@ -73,7 +74,8 @@ group_pairs_kernel(int64_t ns, int64_t groups, const int32_t* __restrict__ order
       total += n;
     }
   }
-  pairs_out[g] = total;
+  // rounded up to four rows: every group then starts 16-byte aligned in rows_id
+  pairs_out[g] = (total + 3) & ~3;
 }
 
 // Number of elements of the ascending list l[0..n) that are smaller than x.
@@ -86,7 +88,11 @@ __device__ __forceinline__ int lower_bound(const int32_t* l, int n, int x) {
   return lo;
 }
 
-// One warp per group.  The four neighbor lists (ascending ids of the sorted
+// One warp per group.  Where the ids of a group span fewer than kBitmapBits
+// values (neighbors of samples in one or two cells: a few tube segments of the
+// sorted points) the warp sets one bit per id and ranks an id by the bits below
+// it; the group may then hold any number of pairs.  Otherwise
+// the four neighbor lists (ascending ids of the sorted
 // points, as FindNeighbors writes them) are copied to shared memory; an element
 // is "first" if no list of a lower slot holds the same id; the row of an id is
 // the number of first elements with a smaller id, counted list by list with one
@@ -99,6 +105,8 @@ group_merge_kernel(int64_t ns, int64_t groups, const int32_t* __restrict__ order
                    int4* __restrict__ rows_pair) {
   __shared__ int32_t s_val[kPlanWarps][kMaxMerge];
   __shared__ int16_t s_pre[kPlanWarps][kMaxMerge + 2];
+  __shared__ uint32_t s_bits[kPlanWarps][kBitmapBits / 32];
+  __shared__ uint16_t s_wpre[kPlanWarps][kBitmapBits / 32];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int32_t* val = s_val[w];
   int16_t* pre = s_pre[w];
@@ -122,6 +130,68 @@ group_merge_kernel(int64_t ns, int64_t groups, const int32_t* __restrict__ order
       i = e - off;
       m = a + i;
     };
+    // ---- groups whose ids span few values: one bit per value, rank = bits below
+    int lo = INT32_MAX, hi = -1;
+    if (lane < 8 && total > 0) {
+      // lists ascend: the smallest id is a list's first, the largest its last element
+      const int q = lane & 3;
+      const int a = q == 0 ? a0 : q == 1 ? a1 : q == 2 ? a2 : a3;
+      const int n = q == 0 ? n0 : q == 1 ? n1 : q == 2 ? n2 : n3;
+      if (n > 0) {
+        const int x = __ldg(&nb_sorted[lane < 4 ? a : a + n - 1].x);
+        lo = x; hi = x;
+      }
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    lo = __shfl_sync(0xffffffffu, lo, 0);
+    hi = __shfl_sync(0xffffffffu, hi, 0);
+    if (total > 0 && hi - lo < kBitmapBits) {
+      uint32_t* bits = s_bits[w];
+      uint16_t* wpre = s_wpre[w];
+      const int words = ((hi - lo) >> 5) + 1;
+      for (int i = lane; i < words; i += 32) bits[i] = 0u;
+      __syncwarp();
+      for (int e = lane; e < total; e += 32) {
+        int q, i, m;
+        locate(e, q, i, m);
+        const int x = __ldg(&nb_sorted[m].x) - lo;
+        atomicOr(&bits[x >> 5], 1u << (x & 31));
+      }
+      __syncwarp();
+      // exclusive running count of the set bits, word by word
+      const int per = (words + 31) >> 5;
+      int mine = 0;
+      for (int i = lane * per; i < min(words, (lane + 1) * per); ++i) mine += __popc(bits[i]);
+      int run = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, run, o);
+        if (lane >= o) run += v;
+      }
+      const int rows = __shfl_sync(0xffffffffu, run, 31);
+      run -= mine;
+      for (int i = lane * per; i < min(words, (lane + 1) * per); ++i) {
+        wpre[i] = (uint16_t)run;
+        run += __popc(bits[i]);
+      }
+      for (int r = lane; r < rows; r += 32) rows_pair[base + r] = make_int4(-1, -1, -1, -1);
+      __syncwarp();
+      for (int e = lane; e < total; e += 32) {
+        int q, i, m;
+        locate(e, q, i, m);
+        const int x = __ldg(&nb_sorted[m].x) - lo;
+        const int rank = wpre[x >> 5] + __popc(bits[x >> 5] & ((1u << (x & 31)) - 1u));
+        rows_id[base + rank] = __ldg(&nb_ids[m].x);   // every pair of a row holds the same id
+        reinterpret_cast<int32_t*>(rows_pair + base + rank)[q] = m;
+      }
+      if (lane == 0) group_rows[g] = rows;
+      __syncwarp();
+      continue;
+    }
     if (total > kMaxMerge) {
       // too many pairs to merge in shared memory: every pair is its own row
       for (int e = lane; e < total; e += 32) {
@@ -195,8 +265,9 @@ extern "C" int tfgpc_mcconv_group_plan(void* stream, int64_t ns, int64_t M, cons
                                        const int32_t* ranges, const int32_t* neighbors_sorted,
                                        const int32_t* neighbor_ids, void* plan,
                                        size_t plan_bytes) {
-  TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && M >= 0 && M <= (int64_t)INT32_MAX - gp::kRowPad,
-                "group plan expects 0 <= ns, M < 2^31");
+  TFGPC_REQUIRE(ns >= 0 && ns < (int64_t)INT32_MAX && M >= 0 &&
+                M + 3 * ((ns + gp::kG - 1) / gp::kG) + gp::kRowPad <= (int64_t)INT32_MAX,
+                "group plan expects 0 <= ns and M + ns < 2^31");
   TFGPC_REQUIRE(plan && (uintptr_t)plan % 256 == 0, "group plan expects a 256-byte aligned buffer");
   if (plan_bytes < tfgpc_mcconv_group_plan_bytes(ns, M))
     return fail(TFGPC_ENOMEM, "group plan buffer too small: %zu < %zu", plan_bytes,

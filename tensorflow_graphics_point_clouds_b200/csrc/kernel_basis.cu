@@ -71,6 +71,7 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
     pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
     const float inv_pdf = 1.0f / __ldg(pdf + m);
     float* dst = basis + m * K;
+    uint4 pr[K / 4];   // hi chunks, then mid chunks, of the bf16 pair
 #pragma unroll
     for (int q = 0; q < K / 8; ++q) {
       float v[8];
@@ -90,15 +91,21 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
       }
       if (pair) {
         // the same row as bf16 hi / mid terms: [m][hi K | mid K]
-        uint4 hv, mv;
-        split2_bf16(v[0], v[1], hv.x, mv.x);
-        split2_bf16(v[2], v[3], hv.y, mv.y);
-        split2_bf16(v[4], v[5], hv.z, mv.z);
-        split2_bf16(v[6], v[7], hv.w, mv.w);
-        uint4* prow = reinterpret_cast<uint4*>(pair + m * (2 * K));
-        prow[q] = hv;
-        prow[K / 8 + q] = mv;
+        split2_bf16(v[0], v[1], pr[q].x, pr[K / 8 + q].x);
+        split2_bf16(v[2], v[3], pr[q].y, pr[K / 8 + q].y);
+        split2_bf16(v[4], v[5], pr[q].z, pr[K / 8 + q].z);
+        split2_bf16(v[6], v[7], pr[q].w, pr[K / 8 + q].w);
       }
+    }
+    if (pair) {
+      // whole 32-byte sectors per store
+      uint8_t* prow = reinterpret_cast<uint8_t*>(pair + m * (2 * K));
+#pragma unroll
+      for (int i = 0; i < K / 8; ++i)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"l"(prow + 32 * i), "r"(pr[2 * i].x), "r"(pr[2 * i].y), "r"(pr[2 * i].z),
+                       "r"(pr[2 * i].w), "r"(pr[2 * i + 1].x), "r"(pr[2 * i + 1].y),
+                       "r"(pr[2 * i + 1].z), "r"(pr[2 * i + 1].w) : "memory");
     }
   }
 }
@@ -302,8 +309,8 @@ static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float*
   if (M == 0) return TFGPC_OK;
   TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && basis_out,
                 "KernelBasis got a null pointer");
-  TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0 && (uintptr_t)pair_out % 16 == 0,
-                "KernelBasis expects 16-byte aligned outputs");
+  TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0 && (uintptr_t)pair_out % 32 == 0,
+                "KernelBasis expects 16-byte aligned outputs (32 for the bf16 pair)");
   cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for(M, kKbThreads), (unsigned)(sm_count() * 16));
   ProfScope prof(st, "kernel_basis");

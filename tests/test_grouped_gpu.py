@@ -35,8 +35,9 @@ def read_plan(plan, ns, m):
     return a
   begin = take((groups + 1) * 4, np.int32, groups + 1)
   rows = take(max(groups, 1) * 4, np.int32, groups)
-  ids = take((m + 256) * 4, np.int32, m + 256)
-  pairs = take((m + 256) * 16, np.int32, (m + 256) * 4).reshape(-1, 4)
+  cap = m + 3 * groups + 256
+  ids = take(cap * 4, np.int32, cap)
+  pairs = take(cap * 16, np.int32, cap * 4).reshape(-1, 4)
   return begin, rows, ids, pairs
 
 
@@ -53,13 +54,11 @@ def check_plan(nb, order, plan):
     smp = order[4 * g:4 * g + 4]
     lists = [np.arange(starts[s], ranges[s]) for s in smp]
     total = sum(len(l) for l in lists)
-    assert begin[g + 1] - begin[g] == total
+    assert begin[g + 1] - begin[g] == (total + 3) // 4 * 4     # groups start on multiples of 4
     r0, nr = begin[g], rows[g]
-    if total > 512:
-      assert nr == total                       # not merged: one row per pair
-    else:
-      union = np.unique(np.concatenate([srt[l, 0] for l in lists])) if total else np.zeros(0, int)
-      assert nr == len(union)
+    union = np.unique(np.concatenate([srt[l, 0] for l in lists])) if total else np.zeros(0, int)
+    # large groups whose ids span too many values are not merged: one row per pair
+    assert nr == len(union) or (total > 512 and nr == total)
     for q, l in enumerate(lists):
       col = row_pairs[r0:r0 + nr, q]
       have = col[col >= 0]
