@@ -5,10 +5,14 @@ kernel basis, basis projection + weight GEMM, and all gradients).
     python bench.py --gpus N --steps K --warmup W            # this library
     python bench.py --impl reference --gpus N ...            # CPU port of the reference path
 
-Workload (synthetic, seeded): 32 clouds x 16384 points uniform in [0,1)^3 per
-GPU, radius 0.079 (about 32 neighbors per point), C_in = 128, one kernel MLP
-with 16 hidden units (K = 16), C_out = 256, fp32.  With N GPUs every rank works
-on its own 32 clouds (weak scaling) and the weight gradients are all-reduced.
+Workload (synthetic, seeded): ONE batch of 32 clouds x 16384 points uniform in
+[0,1)^3, radius 0.079 (about 32 neighbors per point), C_in = 128, one kernel MLP
+with 16 hidden units (K = 16), C_out = 256, fp32.  With N GPUs the batch is
+sharded by cloud (32 / N clouds per rank, strong scaling) and the weight
+gradients are all-reduced; before timing, every rank checks its shard's results
+against the whole batch computed on its own GPU.  `--scaling weak` gives every
+rank its own 32 clouds instead; a strong run on several GPUs also times the weak
+variant and reports it under "weak_scaling".
 Prints one JSON line on rank 0.
 """
 import argparse
@@ -46,6 +50,14 @@ def parse_args():
   ap.add_argument("--cpu-sample-clouds", type=int, default=1)
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                  help="strong: one batch of --clouds clouds sharded over the GPUs; "
+                       "weak: --clouds clouds per GPU")
+  ap.add_argument("--no-shard-check", action="store_true",
+                  help="skip the shard == whole-batch comparison of a multi-GPU strong run")
+  ap.add_argument("--no-side", action="store_true",
+                  help="skip the neighbor-search and sampling-hierarchy side measurements")
+  ap.add_argument("--side-steps", type=int, default=5)
   ap.add_argument("--workload", default="mcconv", choices=["mcconv", "neighbors", "hierarchy", "classifier"],
                   help="mcconv: the headline step; neighbors: grid build + neighbor search + pdf "
                        "on 16 surface clouds (radius 0.05); hierarchy: 4-level Poisson-disk and "
@@ -53,14 +65,21 @@ def parse_args():
   return ap.parse_args()
 
 
-def workload_config(args, world):
+def workload_config(args, world, scaling=None):
+  scaling = scaling or args.scaling
+  total_clouds = args.clouds * (world if scaling == "weak" else 1)
+  per_gpu = (args.clouds if scaling == "weak" else
+             "%d-%d" % (args.clouds // world, -(-args.clouds // world)) if args.clouds % world
+             else args.clouds // world)
   return {
-      "workload": "MCConv layer fwd+bwd from raw points, %d clouds x %d points per GPU, "
+      "workload": "MCConv layer fwd+bwd from raw points, %d clouds x %d points%s, "
                   "uniform in [0,1)^3, radius %.3f (~32 neighbors/point), Cin=%d, K=%d, Cout=%d"
-                  % (args.clouds, args.points, args.radius, args.cin, args.hidden, args.cout),
-      "clouds_per_gpu": args.clouds, "points_per_cloud": args.points, "radius": args.radius,
+                  % (args.clouds, args.points, " per GPU" if scaling == "weak" else " in all",
+                     args.radius, args.cin, args.hidden, args.cout),
+      "clouds": total_clouds, "clouds_per_gpu": per_gpu, "points_per_cloud": args.points,
+      "radius": args.radius,
       "cin": args.cin, "k": args.hidden, "cout": args.cout, "bandwidth": 0.2,
-      "global_points": args.clouds * args.points * world,
+      "global_points": total_clouds * args.points,
       "parallelism": "clouds sharded over %d GPU(s); weight gradients all-reduced" % world,
       "l2": "inputs and intermediates are far larger than L2 (features 268 MB, projection "
             "4.3 GB per step), so no explicit flush between iterations",
@@ -68,7 +87,9 @@ def workload_config(args, world):
 
 
 def make_inputs(args, rank):
-  """Seeded host inputs of one rank (seed 2 is the single-GPU workload)."""
+  """Seeded host inputs of a batch of args.clouds clouds (rank 0: seed 2, the
+  batch of the single-GPU and of every strong-scaling run; other ranks: their own
+  batch in a weak-scaling run)."""
   from tensorflow_graphics_point_clouds_b200 import synthetic
   pts, bid = synthetic.uniform_clouds(args.clouds, args.points, seed=2 + 1000 * rank)
   rng = np.random.default_rng(12345 + rank)
@@ -77,6 +98,18 @@ def make_inputs(args, rank):
   d_out = rng.standard_normal((n, args.cout), dtype=F32)
   w1, b1, wf = synthetic.mcconv_weights(7, 3, args.cin, args.cout, 1, args.hidden)
   return pts, bid, feat, d_out, w1, b1, wf
+
+
+def shard_inputs(inputs, args, rank, world):
+  """The clouds of `rank` out of the whole batch: (inputs of the shard, number of
+  its clouds, index of its first point).  Clouds are stored one after the other
+  with args.points points each."""
+  from tensorflow_graphics_point_clouds_b200 import dist as tdist
+  pts, bid, feat, d_out, w1, b1, wf = inputs
+  b, e = tdist.shard_clouds(args.clouds, world, rank)
+  lo, hi = b * args.points, e * args.points
+  return ((pts[lo:hi], (bid[lo:hi] - b).astype(np.int32), feat[lo:hi], d_out[lo:hi], w1, b1, wf),
+          e - b, lo)
 
 
 # ------------------------------------------------------------------ peaks ----
@@ -117,12 +150,13 @@ def kernel_model(name, sizes):
   n, m = sizes["n"], sizes["m"]
   c, k, co = sizes["cin"], sizes["k"], sizes["cout"]
   ck = c * k
-  if name in ("basis_proj_split", "basis_proj_split_mma"):
+  if name in ("basis_proj_split", "basis_proj_split_mma", "basis_proj_fwd_tcu"):
     # basis rows + neighbor ids, every feature row once, ranges, the projection
     return "hbm", m * (4 * k + 8) + n * 4 * c + n * 4 + n * ck * 4
-  if name in ("basis_proj_grads", "basis_proj_grads_mma", "basis_proj_grads_tc"):
+  if name in ("basis_proj_grads", "basis_proj_grads_mma", "basis_proj_grads_tc",
+              "basis_proj_grads_tcu"):
     return "hbm", n * ck * 4 + m * (4 * k + 8) + n * 4 * c + n * 4 + m * 4 * k + n * 4 * c
-  if name in ("gemm_bf16x3_k_mn", "gemm_bf16x3_mn_k_t"):      # out = X W
+  if name in ("gemm_bf16x3_k_mn", "gemm_bf16x3_mn_k_t", "gemm_bf16x3_mn_k_scatter"):  # out = X W
     return "tensor", 2.0 * n * ck * co
   if name in ("gemm_bf16x3_k_k", "gemm_bf16x3_k_k_image", "gemm_bf16x3_k_mn_image",
               "gemm_bf16x3_mn_k_image"):  # dX = dOut W^T (4-byte output dominates)
@@ -135,8 +169,14 @@ def kernel_model(name, sizes):
     return "hbm", n * 36
   if name == "compute_pdf":
     return "hbm", n * 20 + m * 8
-  if name == "split_bf16":
-    return "hbm", None
+  if name == "kernel_basis":          # ids, two point gathers, density, the 4K-byte row
+    return "hbm", m * (8 + 24 + 4 + 4 * k)
+  if name == "kernel_basis_grads":
+    return "hbm", m * (8 + 24 + 4 + 4 * k)
+  if name == "group_plan":            # both id lists in, one row entry (id + 4 pair slots) per pair out
+    return "hbm", m * (8 + 8 + 20) + n * 4
+  if name == "original_neighbor_ids":
+    return "hbm", m * 20
   return "hbm", None
 
 
@@ -214,8 +254,27 @@ def cpu_port_step(args, pts, bid, feat, d_out, w1, b1, wf, clouds):
   return time.perf_counter() - t0
 
 
+def use_all_host_threads():
+  """Gives the CPU port every core this process may run on.  Launchers such as
+  torchrun export OMP_NUM_THREADS=1, which would otherwise leave the OpenMP loops
+  of the oracle and the BLAS behind NumPy on one thread."""
+  import oracle as orc
+  try:
+    cores = len(os.sched_getaffinity(0))
+  except AttributeError:
+    cores = os.cpu_count() or 1
+  orc.set_num_threads(cores)
+  try:
+    import threadpoolctl
+    threadpoolctl.threadpool_limits(limits=cores)
+  except Exception:  # BLAS thread count stays what the environment set
+    pass
+  return cores
+
+
 def cpu_baseline(args, inputs, reps=1):
   import oracle as orc
+  use_all_host_threads()
   clouds = max(1, min(args.cpu_sample_clouds, args.clouds))
   best = min(cpu_port_step(args, *inputs, clouds) for _ in range(reps))
   return {"value": clouds * args.points / best, "unit": UNIT, "cores": orc.num_threads(),
@@ -233,6 +292,7 @@ def run_reference(args, rank, world):
     return
   import oracle as orc
   orc.build()
+  use_all_host_threads()
   inputs = make_inputs(args, 0)
   clouds = max(1, min(args.cpu_sample_clouds, args.clouds))
   for _ in range(min(args.warmup, 1)):
@@ -243,7 +303,7 @@ def run_reference(args, rank, world):
   line = {
       "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
       "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t,
-      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+      "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
       "data": "synthetic", "config": workload_config(args, world),
       "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                        "sample": "each step is %d of the %d clouds (%d points)"
@@ -256,10 +316,164 @@ def run_reference(args, rank, world):
 
 # ---------------------------------------------------------------- our arm ----
 
+class LayerRun:
+  """One rank's inputs on the device and the step that runs on them."""
+
+  def __init__(self, args, inputs, clouds, dev, world):
+    import torch
+    from tensorflow_graphics_point_clouds_b200 import mcconv
+    pts, bid, feat, d_out, w1, b1, wf = inputs
+    self.args, self.clouds, self.dev, self.world = args, clouds, dev, world
+    self.n = pts.shape[0]
+    self.host = {k: torch.from_numpy(np.ascontiguousarray(v)).pin_memory() for k, v in
+                 dict(pts=pts, bid=bid, feat=feat, d_out=d_out).items()}
+    self.dev_in = {k: v.to(dev) for k, v in self.host.items()}
+    self.layer = mcconv.MCConv(torch.from_numpy(w1).to(dev), torch.from_numpy(b1).to(dev),
+                               torch.from_numpy(wf).to(dev), args.cin)
+    self.pairs = 0
+
+  def step(self, x, allreduce=True):
+    from tensorflow_graphics_point_clouds_b200 import pc
+    from tensorflow_graphics_point_clouds_b200 import dist as tdist
+    # cell counts are the maximum over the whole batch, i.e. over all shards
+    cloud = pc.PointCloud(x["pts"], x["bid"], self.clouds,
+                          num_cells_reduce=tdist.allreduce_max_ if self.world > 1 else None)
+    out = self.layer.forward(x["feat"], cloud, cloud, self.args.radius)
+    self.pairs = int(self.layer._saved[0]._neighbors.shape[0])
+    dfeat, dw1, db1, dwf = self.layer.backward(x["d_out"])
+    if allreduce:
+      tdist.allreduce_sum_([dwf, dw1, db1])   # the path's only exchange step
+    return out, dfeat, dwf, dw1, db1
+
+
+def shard_check(args, full_inputs, run, first_point, dev, world):
+  """Every rank runs the WHOLE batch once on its own GPU and compares its shard's
+  results with the matching slices: neighbor ranges and lists (re-based) bit for
+  bit, output rows and feature gradients within 1e-4 of max(|ref|, rms), and the
+  all-reduced weight gradients with those of the whole batch.  Returns the list
+  of mismatches (empty = ok)."""
+  import torch
+  from tensorflow_graphics_point_clouds_b200 import dist as tdist
+  whole = LayerRun(args, full_inputs, args.clouds, dev, 1)
+  ref = whole.step(whole.dev_in, allreduce=False)
+  ref_nb = whole.layer._saved[0]
+  got = run.step(run.dev_in, allreduce=True)
+  nb = run.layer._saved[0]
+  lo, hi = first_point, first_point + run.n
+  bad = []
+
+  def rel(a, b):
+    a, b = a.double(), b.double()
+    scale = torch.maximum(b.abs(), b.pow(2).mean().sqrt())
+    return float(((a - b).abs() / scale).max())
+
+  ref_ranges = ref_nb._samples_neigh_ranges
+  pair_lo = int(ref_ranges[lo - 1]) if lo > 0 else 0
+  pair_hi = int(ref_ranges[hi - 1])
+  if not torch.equal(nb._samples_neigh_ranges, ref_ranges[lo:hi] - pair_lo):
+    bad.append("ranges")
+  ids = ref_nb._original_neigh_ids[pair_lo:pair_hi] - lo
+  if nb._original_neigh_ids.shape != ids.shape or not torch.equal(nb._original_neigh_ids, ids):
+    bad.append("neighbor lists")
+  for name, a, b in (("out", got[0], ref[0][lo:hi]), ("dfeat", got[1], ref[1][lo:hi]),
+                     ("dW", got[2], ref[2]), ("dw1", got[3], ref[3]), ("db1", got[4], ref[4])):
+    err = rel(a, b)
+    if not err <= (2e-4 if name in ("dw1", "db1") else 1e-4):
+      bad.append("%s (rel err %.2e)" % (name, err))
+  del whole
+  torch.cuda.empty_cache()
+  return bad
+
+
+def timed_steps(run, steps, barrier, collect_kernels):
+  """Device-resident timing of `steps` steps: (ms per step on this rank, kernel records)."""
+  import torch
+  from tensorflow_graphics_point_clouds_b200 import _lib
+  barrier()
+  if collect_kernels:
+    _lib.profile_enable(True)
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(steps):
+    run.step(run.dev_in)
+  e1.record()
+  barrier()
+  records = []
+  if collect_kernels:
+    records = _lib.profile_collect()
+    _lib.profile_enable(False)
+  return e0.elapsed_time(e1) / steps, records
+
+
+def e2e_steps(run, steps, barrier):
+  """End to end: every step copies its inputs from pinned host memory and its
+  results back to pinned host memory.  The copies run on two copy streams so that
+  the upload of step i+1 and the download of step i-1 overlap the kernels of step i
+  (two sets of device input buffers and of host output buffers).
+  Returns (ms per step on this rank, bytes up per step, bytes down per step)."""
+  import torch
+  host, dev = run.host, run.dev
+  h2d = sum(v.numel() * v.element_size() for v in host.values())
+  main = torch.cuda.current_stream()
+  s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+  dev_bufs = [{k: torch.empty_like(v, device=dev) for k, v in host.items()} for _ in range(2)]
+  ev_in = [torch.cuda.Event() for _ in range(2)]
+  ev_free = [torch.cuda.Event() for _ in range(2)]   # step that used the buffer set has finished
+  ev_out = [torch.cuda.Event() for _ in range(2)]    # download into the host set has finished
+  out_host = [None, None]
+  d2h = [0]
+
+  def upload(i):
+    b = i % 2
+    with torch.cuda.stream(s_in):
+      s_in.wait_event(ev_free[b])
+      for k, v in host.items():
+        dev_bufs[b][k].copy_(v, non_blocking=True)
+      ev_in[b].record(s_in)
+
+  def run_one(i):
+    b = i % 2
+    main.wait_event(ev_in[b])
+    res = run.step(dev_bufs[b])
+    ev_free[b].record(main)
+    done = torch.cuda.Event()
+    done.record(main)
+    if out_host[b] is None:
+      out_host[b] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+      d2h[0] = sum(r.numel() * r.element_size() for r in res)
+    with torch.cuda.stream(s_out):
+      s_out.wait_event(done)
+      s_out.wait_event(ev_out[b])
+      for h, r in zip(out_host[b], res):
+        r.record_stream(s_out)
+        h.copy_(r, non_blocking=True)
+      ev_out[b].record(s_out)
+
+  def loop(count):
+    upload(0)
+    for i in range(count):
+      if i + 1 < count:
+        upload(i + 1)
+      run_one(i)
+    main.wait_stream(s_out)
+
+  for b in range(2):
+    ev_free[b].record(main)
+    ev_out[b].record(main)
+  loop(2)
+  barrier()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  loop(steps)
+  e1.record()
+  barrier()
+  return e0.elapsed_time(e1) / steps, h2d, d2h[0]
+
+
 def run_ours(args, rank, local_rank, world):
   import torch
   import torch.distributed as dist
-  from tensorflow_graphics_point_clouds_b200 import _lib, build, mcconv, pc
+  from tensorflow_graphics_point_clouds_b200 import build
   from tensorflow_graphics_point_clouds_b200 import dist as tdist
 
   if not torch.cuda.is_available():
@@ -270,118 +484,86 @@ def run_ours(args, rank, local_rank, world):
   if world > 1:
     dist.init_process_group("nccl", device_id=dev)
 
-  inputs = make_inputs(args, rank)
-  pts, bid, feat, d_out, w1, b1, wf = inputs
-  n = pts.shape[0]
-  host = {k: torch.from_numpy(v).pin_memory() for k, v in
-          dict(pts=pts, bid=bid, feat=feat, d_out=d_out).items()}
-  dev_in = {k: v.to(dev) for k, v in host.items()}
-  layer = mcconv.MCConv(torch.from_numpy(w1).to(dev), torch.from_numpy(b1).to(dev),
-                        torch.from_numpy(wf).to(dev), args.cin)
-  sizes = {"n": n, "m": 0, "cin": args.cin, "k": args.hidden, "cout": args.cout}
-
-  def step(x):
-    cloud = pc.PointCloud(x["pts"], x["bid"], args.clouds)
-    out = layer.forward(x["feat"], cloud, cloud, args.radius)
-    sizes["m"] = int(layer._saved[0]._neighbors.shape[0])
-    dfeat, dw1, db1, dwf = layer.backward(x["d_out"])
-    tdist.allreduce_sum_([dwf, dw1, db1])   # the path's only exchange step
-    return out, dfeat, dwf, dw1, db1
-
   def barrier():
     torch.cuda.synchronize()
     if world > 1:
       dist.barrier()
       torch.cuda.synchronize()
 
+  strong = args.scaling == "strong"
+  full_inputs = make_inputs(args, 0 if strong else rank)
+  if strong:
+    inputs, clouds, first_point = shard_inputs(full_inputs, args, rank, world)
+  else:
+    inputs, clouds, first_point = full_inputs, args.clouds, 0
+  run = LayerRun(args, inputs, clouds, dev, world)
+  n_global = args.clouds * args.points * (1 if strong else world)
+  sizes = {"n": run.n, "m": 0, "cin": args.cin, "k": args.hidden, "cout": args.cout}
+
   # nvidia-smi needs a few hundred ms to deliver its first sample: start it
   # before the warm-up so that it is sampling (under the same load) throughout
   # the timed region
   sampler = ClockSampler(local_rank)
   sampler.start()
+  check = None
+  if strong and world > 1 and not args.no_shard_check:
+    bad = shard_check(args, full_inputs, run, first_point, dev, world)
+    flag = torch.tensor([0 if bad else 1], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    check = "ok" if int(flag.item()) == 1 else "FAILED"
+    if bad:
+      sys.stderr.write("shard_check rank %d: mismatch in %s\n" % (rank, ", ".join(bad)))
+    if rank == 0:
+      sys.stderr.write("shard_check: %s\n" % check)
   for _ in range(max(args.warmup, 3)):
-    step(dev_in)
-  layer._op.check_status()
+    run.step(run.dev_in)
+  run.layer._op.check_status()
 
   # ---- device-resident timing
-  barrier()
-  _lib.profile_enable(True)
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  e0.record()
-  for _ in range(args.steps):
-    step(dev_in)
-  e1.record()
-  barrier()
-  records = _lib.profile_collect()
-  _lib.profile_enable(False)
+  ms_rank, records = timed_steps(run, args.steps, barrier, True)
   clocks = sampler.stop()
-  layer._op.check_status()
-  ms_per_step = tdist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+  run.layer._op.check_status()
+  sizes["m"] = run.pairs
+  ms_per_step = tdist.max_over_ranks(ms_rank, dev)
+  pairs_global = run.pairs
+  if world > 1:
+    t = torch.tensor([run.pairs], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    pairs_global = int(t.item())
 
   # ---- end to end: host buffers in, host buffers out, every step
   e2e = None
   if not args.no_e2e:
-    # Every step copies its inputs from pinned host memory and its results back
-    # to pinned host memory.  The copies run on two copy streams so that the
-    # upload of step i+1 and the download of step i-1 overlap the kernels of
-    # step i (two sets of device input buffers and of host output buffers).
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
-    main = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    dev_bufs = [{k: torch.empty_like(v, device=dev) for k, v in host.items()} for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]   # step that used the buffer set has finished
-    ev_out = [torch.cuda.Event() for _ in range(2)]    # download into the host set has finished
-    out_host = [None, None]
-    d2h = 0
+    e2e_rank, h2d, d2h = e2e_steps(run, args.steps, barrier)
+    e2e_ms = tdist.max_over_ranks(e2e_rank, dev)
+    per_rank = torch.tensor([h2d / (e2e_rank * 1e-3) / 1e9, d2h / (e2e_rank * 1e-3) / 1e9],
+                            dtype=torch.float64, device=dev)
+    if world > 1:
+      gathered = [torch.zeros_like(per_rank) for _ in range(world)]
+      dist.all_gather(gathered, per_rank)
+    else:
+      gathered = [per_rank]
+    e2e = {"value": n_global / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "h2d_gbs_per_rank": [round(float(g[0]), 2) for g in gathered],
+           "d2h_gbs_per_rank": [round(float(g[1]), 2) for g in gathered],
+           "note": "bytes per step are this rank's; GB/s = bytes / the rank's own step time, both "
+                   "directions in flight at once with the kernels"}
 
-    def upload(i):
-      b = i % 2
-      with torch.cuda.stream(s_in):
-        s_in.wait_event(ev_free[b])
-        for k, v in host.items():
-          dev_bufs[b][k].copy_(v, non_blocking=True)
-        ev_in[b].record(s_in)
-
-    def run(i):
-      nonlocal d2h
-      b = i % 2
-      main.wait_event(ev_in[b])
-      res = step(dev_bufs[b])
-      ev_free[b].record(main)
-      done = torch.cuda.Event()
-      done.record(main)
-      if out_host[b] is None:
-        out_host[b] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
-        d2h = sum(r.numel() * r.element_size() for r in res)
-      with torch.cuda.stream(s_out):
-        s_out.wait_event(done)
-        s_out.wait_event(ev_out[b])
-        for h, r in zip(out_host[b], res):
-          r.record_stream(s_out)
-          h.copy_(r, non_blocking=True)
-        ev_out[b].record(s_out)
-
-    def e2e_loop(count):
-      upload(0)
-      for i in range(count):
-        if i + 1 < count:
-          upload(i + 1)
-        run(i)
-      main.wait_stream(s_out)
-
-    for b in range(2):
-      ev_free[b].record(main)
-      ev_out[b].record(main)
-    e2e_loop(2)
-    barrier()
-    e0.record()
-    e2e_loop(args.steps)
-    e1.record()
-    barrier()
-    e2e_ms = tdist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
-    e2e = {"value": n * world / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+  # ---- weak scaling beside a strong multi-GPU run: every rank its own batch
+  weak = None
+  if strong and world > 1:
+    del run
+    torch.cuda.empty_cache()
+    wrun = LayerRun(args, make_inputs(args, rank), args.clouds, dev, world)
+    for _ in range(3):
+      wrun.step(wrun.dev_in)
+    wms, _ = timed_steps(wrun, args.steps, barrier, False)
+    wms = tdist.max_over_ranks(wms, dev)
+    weak = {"value": args.clouds * args.points * world / (wms * 1e-3), "unit": UNIT,
+            "ms_per_step": wms, "clouds_per_gpu": args.clouds, "scaling": "weak"}
+    del wrun
+    torch.cuda.empty_cache()
 
   if rank == 0:
     peaks = measured_peaks()
@@ -404,32 +586,54 @@ def run_ours(args, rank, local_rank, world):
       achieved = amount / (avg_ms * 1e-3) / 1e12
       peak, runit = peaks["bf16_tflops"], "TFLOP/s"
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
-                "frac": achieved / peak, "traffic": (NCU_TRAFFIC_BYTES_PER_POINT[top] * n
+                "frac": achieved / peak, "traffic": (NCU_TRAFFIC_BYTES_PER_POINT[top] * sizes["n"]
                             if top in NCU_TRAFFIC_BYTES_PER_POINT else None),
                 "avg_launch_ms": avg_ms, "peak_source": peaks["source"],
                 "note": "tensor-bound kernels issue 3 bf16 passes per algorithmic flop"
                         if bound == "tensor" else "algorithmic bytes / launch time"}
+    # every modelled kernel against its own bound (rank 0's launches)
+    per_kernel = {}
+    for name, v in modelled.items():
+      kb, amt = kernel_model(name, sizes)
+      k_ms = v[1] / v[0]
+      if kb == "hbm":
+        per_kernel[name] = {"bound": "hbm", "frac": amt / (k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+      else:
+        per_kernel[name] = {"bound": "tensor", "frac_algorithmic":
+                            amt / (k_ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                            "frac_issued": 3 * amt / (k_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
     line = {
-        "metric": METRIC, "value": n * world / (ms_per_step * 1e-3), "unit": UNIT,
+        "metric": METRIC, "value": n_global / (ms_per_step * 1e-3), "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, world), "clocks": clocks, "e2e": e2e,
         "gpu_launches": int(sum(v[0] for v in agg.values())),
         "roofline": roofline,
         "kernels": kernels,
+        "kernel_roofline_fracs": per_kernel,
         "kernel_ms_per_step": total_kernel_ms / args.steps,
-        "neighbor_pairs": sizes["m"],
-        "neighbor_pairs_per_s": sizes["m"] * world / (ms_per_step * 1e-3),
+        "neighbor_pairs": pairs_global,
+        "neighbor_pairs_per_layer_step_per_s": pairs_global / (ms_per_step * 1e-3),
     }
+    if check is not None:
+      line["shard_check"] = check
+    if weak is not None:
+      line["weak_scaling"] = weak
     if world == 1 and not args.no_cpu_baseline:
       import oracle as orc
       orc.build()
-      line["cpu_baseline"] = cpu_baseline(args, inputs)
+      line["cpu_baseline"] = cpu_baseline(args, full_inputs)
+    if not args.no_side and args.workload == "mcconv":
+      line["side"] = {}
+      for wl in ("neighbors", "hierarchy"):
+        side_args = argparse.Namespace(**vars(args))
+        side_args.workload, side_args.steps, side_args.warmup = wl, args.side_steps, 3
+        line["side"][wl] = side_workload_line(side_args, local_rank)
     print(json.dumps(line), flush=True)
   if world > 1:
+    barrier()
     dist.destroy_process_group()
-
 
 
 # ------------------------------------------------- secondary workloads -------
@@ -451,6 +655,10 @@ SIDE_MODELS = {
 
 
 def run_side_workload(args):
+  print(json.dumps(side_workload_line(args, 0)), flush=True)
+
+
+def side_workload_line(args, device_index):
   """Grid / neighbor / pdf (surface clouds) or the sampling hierarchy (Gaussian
   mixtures) on one GPU: per-kernel time and algorithmic GB/s against the HBM peak."""
   import torch
@@ -458,7 +666,7 @@ def run_side_workload(args):
   if not torch.cuda.is_available():
     raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
   build.build()
-  dev = torch.device("cuda", 0)
+  dev = torch.device("cuda", device_index)
   peaks = measured_peaks()
   if args.workload == "neighbors":
     pts, bid = synthetic.surface_clouds(16, seed=1)
@@ -495,7 +703,7 @@ def run_side_workload(args):
     step(False)
   torch.cuda.synchronize()
   pairs = step(True)
-  sampler = ClockSampler(0)
+  sampler = ClockSampler(device_index)
   sampler.start()
   _lib.profile_enable(True)
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -548,7 +756,7 @@ def run_side_workload(args):
       "clocks": clocks, "kernels": kernels, "peak_hbm_gbs": peaks["hbm_gbs"],
       "peak_source": peaks["source"],
   }
-  print(json.dumps(line), flush=True)
+  return line
 
 
 def run_classifier_workload(args):

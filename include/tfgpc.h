@@ -354,28 +354,32 @@ int tfgpc_mcconv_backward(void* stream, int K, int C, int Cout, int64_t ns,
                           float* dweights_out, void* ws, size_t ws_bytes);
 int tfgpc_mcconv_status(void* stream, const void* ws, int* status_out);
 
-/* ---- MCConv backward on a group plan --------------------------------------
- * No counterpart in the reference; same results as tfgpc_mcconv_backward.
- * BasisProjGrads (basis_proj_grads_kernels.cu.cc:30-151) spends one gathered
- * feature row and one C-wide atomic update per neighbor PAIR.  Samples that lie
+/* ---- MCConv forward and backward on a group plan -------------------------
+ * No counterpart in the reference; same results as tfgpc_mcconv_forward /
+ * _backward.  BasisProj and BasisProjGrads (basis_proj_kernels.cu.cc:30-127,
+ * basis_proj_grads_kernels.cu.cc:30-151) spend one gathered feature row -- and
+ * the gradients one C-wide atomic update -- per neighbor PAIR.  Samples that lie
  * close together share most of their neighbors, so the work is regrouped: the
  * samples are taken four at a time in a spatially coherent visiting order
  * `order` [ns] (a permutation of the sample indices; for a cloud searched on its
  * own grid the key sort's permutation), and the plan lists every group's
  * distinct neighbors with the pairs through which its samples see them.  The
- * gradient kernel then gathers, multiplies and reduces once per distinct
- * neighbor of a group (about half as often as per pair at 32 neighbors per
- * point), which is what bounds it: the L2's floating-point atomic units.
+ * kernels then gather, multiply and reduce once per distinct neighbor of a
+ * group (about half as often as per pair at 32 neighbors per point).
  * tfgpc_mcconv_group_plan: ranges [ns] and neighbors_sorted [M,2] as written by
  * FindNeighbors (ids ascending within each sample's list -- required),
  * neighbor_ids [M,2] the ids the features are indexed by (the original ids of
  * tfgpc_original_neighbor_ids; may equal neighbors_sorted).  plan: caller
  * buffer of _group_plan_bytes(ns, M) bytes, 256-byte aligned; it depends only on
  * the neighborhood and the order and can be reused by every call on them.
- * tfgpc_mcconv_backward_grouped: arguments of tfgpc_mcconv_backward plus
- * basis_pair [M,2,K] bf16 (tfgpc_kernel_basis_split), order and plan;
- * neighbors = neighbor_ids.  Only for shapes with _grouped_supported(K, C) != 0
- * (K = 16, C = 128); 16-byte aligned features. */
+ * _forward_grouped / _backward_grouped: arguments of tfgpc_mcconv_forward /
+ * _backward with the basis given as basis_pair [M,2,K] bf16
+ * (tfgpc_kernel_basis_split; 32-byte aligned) instead of fp32, plus order and
+ * plan; the neighbor list itself is not needed any more.  The projection is kept
+ * in the workspace in the visiting order: x_in_workspace != 0 is only valid
+ * after _forward_grouped on the same workspace, order and plan.  Only for shapes
+ * with _grouped_supported(K, C) != 0 (K = 16, C = 128) and Cout >= 128;
+ * 16-byte aligned features, 32-byte aligned out. */
 int tfgpc_mcconv_grouped_supported(int K, int C);
 size_t tfgpc_mcconv_group_plan_bytes(int64_t ns, int64_t M);
 int tfgpc_mcconv_group_plan(void* stream, int64_t ns, int64_t M,
@@ -383,12 +387,17 @@ int tfgpc_mcconv_group_plan(void* stream, int64_t ns, int64_t M,
                             const int32_t* neighbors_sorted,
                             const int32_t* neighbor_ids, void* plan,
                             size_t plan_bytes);
+int tfgpc_mcconv_forward_grouped(void* stream, int K, int C, int Cout,
+                                 int64_t ns, int64_t n_in, int64_t M,
+                                 const void* basis_pair, const float* features,
+                                 const float* weights, const int32_t* order,
+                                 const void* plan, float* out, void* ws,
+                                 size_t ws_bytes);
 int tfgpc_mcconv_backward_grouped(void* stream, int K, int C, int Cout,
                                   int64_t ns, int64_t n_in, int64_t M,
-                                  const float* basis, const void* basis_pair,
-                                  const float* features,
-                                  const int32_t* neighbors,
-                                  const int32_t* ranges, const float* weights,
+                                  const void* basis_pair,
+                                  const float* features, const int32_t* ranges,
+                                  const float* weights,
                                   const float* out_grads, int x_in_workspace,
                                   const int32_t* order, const void* plan,
                                   float* dbasis_out, float* dfeat_out,
@@ -419,14 +428,50 @@ int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
                              const float* basis_grads, float* dw1_out,
                              float* db1_out);
 /* tfgpc_kernel_basis that also writes every basis row as the bf16 pair the
- * tensor-core kernels multiply with: basis_pair_out [M,2,K] bf16, row m =
- * (hi terms k = 0..K-1, mid terms), basis ~= hi + mid. */
+ * tensor-core kernels multiply with: basis_pair_out [M,2,K] bf16 (32-byte
+ * aligned), row m = (hi terms k = 0..K-1, mid terms), basis ~= hi + mid.
+ * basis_out may be NULL (only the pair is written). */
 int tfgpc_kernel_basis_split(void* stream, int D, int K, int64_t M,
                              const float* points_in, const float* points_out,
                              const int32_t* neighbors, const float* pdf,
                              const float* w1, const float* b1,
                              float inv_radius, int activation, float alpha,
                              float* basis_out, void* basis_pair_out);
+
+/* ---- MCConv kernel MLP, general form ---------------------------------------
+ * Replaces the TensorFlow ops of pylib/pc/layers/MCConv.py:163-171 and :264-269
+ * and what autodiff makes of them, for kernel MLPs with any number of hidden
+ * layers (the loop of MCConv.py:165-168), including the gradients with respect
+ * to the point coordinates that monte_carlo_conv_test.py:182-219 checks.
+ * num_mlps independent MLPs; layer l of each maps H_{l-1} values (H_0 = D) to
+ * layer_sizes[l-1] = H_l values [host, num_layers <= 4 entries, each <= 64] and
+ * is followed by the activation (0 = leaky ReLU with slope alpha, 1 = ELU).
+ * weights: the layers' tensors [num_mlps, H_{l-1}, H_l] one after the other;
+ * biases: [num_mlps, H_l] per layer, one after the other (at most 8192 floats in
+ * all).  basis_out [M, num_mlps * H_last], column g * H_last + h, divided by
+ * pdf [M].
+ * _grads: basis_grads [M, num_mlps * H_last] -> dweights_out / dbiases_out in
+ * the layouts of weights / biases (overwritten); optional (NULL to skip)
+ * dpoints_in_out [n_in, D], dpoints_out_out [ns, D] (overwritten; the two may
+ * be the SAME array when points_in and points_out are one cloud) and dpdf_out
+ * [M], the gradient with respect to the per-pair density. */
+int tfgpc_kernel_mlp_basis(void* stream, int D, int num_mlps, int num_layers,
+                           const int32_t* layer_sizes, int64_t M,
+                           const float* points_in, const float* points_out,
+                           const int32_t* neighbors, const float* pdf,
+                           const float* weights, const float* biases,
+                           float inv_radius, int activation, float alpha,
+                           float* basis_out);
+int tfgpc_kernel_mlp_grads(void* stream, int D, int num_mlps, int num_layers,
+                           const int32_t* layer_sizes, int64_t M, int64_t n_in,
+                           int64_t ns, const float* points_in,
+                           const float* points_out, const int32_t* neighbors,
+                           const float* pdf, const float* weights,
+                           const float* biases, float inv_radius,
+                           int activation, float alpha,
+                           const float* basis_grads, float* dweights_out,
+                           float* dbiases_out, float* dpoints_in_out,
+                           float* dpoints_out_out, float* dpdf_out);
 
 /* ---- KPConv and PointConv bases --------------------------------------------
  * The per-pair basis values of the other two convolutions of pylib/pc/layers,

@@ -161,6 +161,100 @@ def mcconv_basis(points_in, points_out, neigh, pdf, w1, b1, radius):
   return (hid / pdf.reshape(-1, 1)).astype(F32), diff, hid
 
 
+def _act(x, name):
+  """Activations of MCConv.py:27-31 and their derivatives (float64)."""
+  name = name.lower()
+  if name == 'elu':
+    return np.where(x > 0, x, np.expm1(x)), np.where(x > 0, 1.0, np.exp(x))
+  alpha = 0.0 if name == 'relu' else 0.2
+  return np.where(x > 0, x, alpha * x), np.where(x > 0, 1.0, alpha)
+
+
+def kernel_mlp_forward(diff, weights, biases, non_linearity='leaky_relu'):
+  """The kernel MLP of MCConv.py:163-171 with any number of hidden layers:
+  weights[l] [num_mlps, H_{l-1}, H_l], biases[l] [num_mlps, 1, H_l], every layer
+  followed by the activation.  diff [M, D] -> (hidden [M, num_mlps * H_last]
+  float64, the per-layer pre-activations)."""
+  g = weights[0].shape[0]
+  cur = np.tile(diff.astype(np.float64)[None], (g, 1, 1))
+  pres = []
+  for w, b in zip(weights, biases):
+    pre = np.matmul(cur, w.astype(np.float64)) + b.astype(np.float64)
+    pres.append((cur, pre))
+    cur = _act(pre, non_linearity)[0]
+  hid = np.transpose(cur, (1, 0, 2)).reshape(diff.shape[0], -1)
+  return hid, pres
+
+
+def kernel_mlp_backward(d_hid, pres, weights, non_linearity='leaky_relu'):
+  """Gradients of kernel_mlp_forward: d_hid [M, num_mlps * H_last] ->
+  (d_diff [M, D], [d_weights], [d_biases]) in float64."""
+  g = weights[0].shape[0]
+  m = d_hid.shape[0]
+  cur = np.transpose(d_hid.reshape(m, g, -1), (1, 0, 2))
+  d_w, d_b = [], []
+  for (inp, pre), w in zip(reversed(pres), reversed(weights)):
+    dpre = cur * _act(pre, non_linearity)[1]
+    d_w.insert(0, np.matmul(np.transpose(inp, (0, 2, 1)), dpre))
+    d_b.insert(0, dpre.sum(axis=1, keepdims=True))
+    cur = np.matmul(dpre, np.transpose(w.astype(np.float64), (0, 2, 1)))
+  return cur.sum(axis=0), d_w, d_b
+
+
+def mcconv_layer(points_in, points_out, features, neigh, pdf, weights, biases, wf, radius,
+                 non_linearity='leaky_relu'):
+  """The whole layer of MCConv.py:196-278 for a given neighborhood and given
+  per-pair densities, in float64 (multi-layer kernel MLP): [Ns, Cout]."""
+  ids = neigh.original_neigh_ids
+  diff = (points_in[ids[:, 0]].astype(np.float64) - points_out[ids[:, 1]]) / radius
+  hid, _ = kernel_mlp_forward(diff, weights, biases, non_linearity)
+  basis = hid / pdf.astype(np.float64).reshape(-1, 1)
+  ns, cin, g = len(neigh.ranges), features.shape[1], wf.shape[0]
+  k = basis.shape[1]
+  x = np.zeros((ns, cin, k))
+  np.add.at(x, ids[:, 1], features[ids[:, 0]].astype(np.float64)[:, :, None] * basis[:, None, :])
+  xg = np.transpose(x.reshape(ns, cin, g, k // g), (2, 0, 1, 3)).reshape(g, ns, -1)
+  out = np.matmul(xg, wf.astype(np.float64))
+  return np.transpose(out, (1, 0, 2)).reshape(ns, -1)
+
+
+def mcconv_layer_grads(points_in, points_out, features, neigh, pdf, weights, biases, wf, radius,
+                       d_out, non_linearity='leaky_relu'):
+  """Analytic gradients of mcconv_layer in float64: a dict with d_features,
+  d_wf, d_weights, d_biases, d_points_in, d_points_out and d_pdf (per pair: the
+  density enters as basis = hidden / pdf)."""
+  ids = neigh.original_neigh_ids
+  p_in, p_out = points_in.astype(np.float64), points_out.astype(np.float64)
+  diff = (p_in[ids[:, 0]] - p_out[ids[:, 1]]) / radius
+  hid, pres = kernel_mlp_forward(diff, weights, biases, non_linearity)
+  pdf64 = pdf.astype(np.float64).reshape(-1, 1)
+  basis = hid / pdf64
+  ns, cin, g = len(neigh.ranges), features.shape[1], wf.shape[0]
+  k = basis.shape[1]
+  h = k // g
+  f64 = features.astype(np.float64)
+  x = np.zeros((ns, cin, k))
+  np.add.at(x, ids[:, 1], f64[ids[:, 0]][:, :, None] * basis[:, None, :])
+  co = wf.shape[2]
+  dog = np.transpose(d_out.astype(np.float64).reshape(ns, g, co), (1, 0, 2))
+  xg = np.transpose(x.reshape(ns, cin, g, h), (2, 0, 1, 3)).reshape(g, ns, cin * h)
+  d_wf = np.matmul(np.transpose(xg, (0, 2, 1)), dog)
+  dxg = np.matmul(dog, np.transpose(wf.astype(np.float64), (0, 2, 1)))
+  dx = np.transpose(dxg.reshape(g, ns, cin, h), (1, 2, 0, 3)).reshape(ns, cin, k)
+  dxm = dx[ids[:, 1]]                                     # [M, cin, k]
+  d_basis = np.einsum('mck,mc->mk', dxm, f64[ids[:, 0]])
+  d_feat = np.zeros_like(f64)
+  np.add.at(d_feat, ids[:, 0], np.einsum('mck,mk->mc', dxm, basis))
+  d_hid = d_basis / pdf64
+  d_pdf = -(d_basis * hid).sum(axis=1) / (pdf64[:, 0] ** 2)
+  d_diff, d_w, d_b = kernel_mlp_backward(d_hid, pres, weights, non_linearity)
+  d_pin = np.zeros_like(p_in); d_pout = np.zeros_like(p_out)
+  np.add.at(d_pin, ids[:, 0], d_diff / radius)
+  np.add.at(d_pout, ids[:, 1], -d_diff / radius)
+  return dict(d_features=d_feat, d_wf=d_wf, d_weights=d_w, d_biases=d_b, d_points_in=d_pin,
+              d_points_out=d_pout, d_pdf=d_pdf, d_basis=d_basis)
+
+
 def mcconv_forward(features, basis, neigh, wf):
   """MCConv.py:174-194.  wf [num_mlps, Cin*H, Cout/num_mlps] -> [Ns, Cout]."""
   g = wf.shape[0]

@@ -61,10 +61,13 @@ SYMBOLS = {
     "tfgpc_mcconv_grouped_supported": c_int,
     "tfgpc_mcconv_group_plan_bytes": c_sz,
     "tfgpc_mcconv_group_plan": c_int,
+    "tfgpc_mcconv_forward_grouped": c_int,
     "tfgpc_mcconv_backward_grouped": c_int,
     "tfgpc_kernel_basis_split": c_int,
     "tfgpc_kernel_basis": c_int,
     "tfgpc_kernel_basis_grads": c_int,
+    "tfgpc_kernel_mlp_basis": c_int,
+    "tfgpc_kernel_mlp_grads": c_int,
     "tfgpc_kp_basis": c_int,
     "tfgpc_pointconv_pdf": c_int,
     "tfgpc_neighborhood_pool": c_int,

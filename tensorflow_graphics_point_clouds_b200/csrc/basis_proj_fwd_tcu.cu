@@ -1,0 +1,362 @@
+// The basis projection on tcgen05 tensor cores, on the rows of a group plan
+// (group_plan.cu): C = 128 channels, K = 16 basis functions, groups of four
+// samples taken in the visiting order.
+//
+//   X[s, c, k] = sum over the pairs m of s:  feat[nbr(m), c] * basis[m, k]
+// (BasisProj, basis_proj_kernels.cu.cc:30-127).  A row of the plan is a distinct
+// neighbor j of the group; Bx[row, (q, k)] holds the basis row of the pair through
+// which sample q of the group sees j (zero if it does not).  Then
+//   Xcat[c, (q, k)] = sum over rows  F[row, c] * Bx[row, (q, k)]
+// is one accumulator of 128 channels x 64 columns per group, with the rows as the
+// reduction index: every feature row is gathered once per group (about half as
+// often as once per pair) and no per-sample bookkeeping is left.
+// Both operands are MN-major for the tensor core: F as [row][channel] and Bx as
+// [row][(q, k)], 128-byte rows with the 16-byte chunks XOR-ed with row % 8, i.e.
+// exactly what the copies of the gradient kernel (basis_proj_grads_tcu.cu) write.
+// fp32 accuracy comes from the 3-pass bf16 split of both operands.
+//
+// The result is written as the bf16 (hi, mid) pair the weight GEMM consumes,
+// row v = 4 g + q of X in the VISITING order (the GEMM scatters its output rows
+// back to the sample order).
+// Roles: warps 0-7 issue the copies, warp 8 issues the MMAs, warps 9-16 drain the
+// accumulator (double buffered in tensor memory).  Every mbarrier wait is bounded.
+#include "basis_proj_tc.cuh"
+#include "group_plan.cuh"
+
+namespace tfgpc {
+
+using namespace tc;
+using namespace bptc;
+
+namespace {
+
+constexpr int kG = gp::kG;
+constexpr int kProdWarps = 8;
+constexpr int kMmaWarp = 8;
+constexpr int kEpiWarp0 = 9;
+constexpr int kThreads = 17 * 32;
+constexpr int kUnits = 4;              // ring of 64-channel feature blocks; a block of rows takes two
+constexpr uint32_t kPart = 16384;      // one 128 x 128-byte operand tile (hi or mid)
+constexpr uint32_t kUnitBytes = 2 * kPart;
+constexpr uint32_t kBxBytes = 2 * kPart;
+constexpr uint32_t kTmemCols = 128;    // two accumulators of 64 columns
+constexpr size_t kSmemBytes = (size_t)kUnits * kUnitBytes + 2 * kBxBytes + 1024 + 256;
+
+struct Barriers {
+  uint64_t f_full[kUnits], f_empty[kUnits];
+  uint64_t bx_full[2], bx_empty[2];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct UTile {
+  int ra, rows;
+  __device__ __forceinline__ int blocks() const { return (rows + kRows - 1) / kRows; }
+};
+
+__device__ __forceinline__ UTile load_utile(const int32_t* __restrict__ group_begin,
+                                            const int32_t* __restrict__ group_rows, int64_t groups,
+                                            int64_t g) {
+  UTile t;
+  if (g >= groups) { t.ra = 0; t.rows = 0; return t; }
+  t.ra = __ldg(group_begin + g);
+  t.rows = __ldg(group_rows + g);
+  return t;
+}
+
+struct UWalk {
+  const int32_t *gb, *gr;
+  int64_t groups, g;
+  UTile t, tn;
+  int b;
+  bool valid;
+  __device__ __forceinline__ void settle() {
+    while (g < groups && b >= t.blocks()) {
+      g += gridDim.x;
+      t = tn;
+      tn = load_utile(gb, gr, groups, g + gridDim.x);
+      b = 0;
+    }
+    valid = g < groups;
+  }
+  __device__ __forceinline__ void init(const int32_t* begin, const int32_t* rows, int64_t n) {
+    gb = begin; gr = rows; groups = n; g = blockIdx.x; b = 0;
+    t = load_utile(gb, gr, groups, g);
+    tn = load_utile(gb, gr, groups, g + gridDim.x);
+    settle();
+  }
+  __device__ __forceinline__ void advance() { ++b; settle(); }
+};
+
+// 16-byte copy that writes zeros instead when `valid` is false.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+               ::"r"(dst), "l"(src), "r"(valid ? 16u : 0u) : "memory");
+}
+
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+                 "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict__ group_begin,
+                          const int32_t* __restrict__ group_rows,
+                          const int32_t* __restrict__ rows_id, const int4* __restrict__ rows_pair,
+                          const __nv_bfloat16* __restrict__ basis_pair,
+                          const __nv_bfloat16* __restrict__ fs, __nv_bfloat16* __restrict__ x_hi,
+                          __nv_bfloat16* __restrict__ x_mid, uint32_t idesc, int* err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* f_ring = smem;
+  uint8_t* bx = f_ring + (size_t)kUnits * kUnitBytes;
+  Barriers* bars = (Barriers*)(bx + 2 * kBxBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kUnits; ++i) {
+      mbar_init(smem_u32(&bars->f_full[i]), kProdWarps * 32);
+      mbar_init(smem_u32(&bars->f_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->bx_full[i]), kProdWarps * 32);
+      mbar_init(smem_u32(&bars->bx_empty[i]), 1);
+      mbar_init(smem_u32(&bars->acc_full[i]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[i]), 8);
+    }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *(volatile uint32_t*)&bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp < kProdWarps) {
+    // ------------------------------------------------------------- producers
+    // warp w owns rows 16 w .. 16 w + 15 of every block of 128 rows.  The plan
+    // entries of block i+1 are fetched into registers while the copies of block i
+    // are issued; every copy signals the consumer's barrier when it lands.
+    const int row_base = warp * 16;
+    // F: lanes 0-15 copy row `it`, lanes 16-31 row `it + 8` of the warp's 16;
+    // lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
+    const int l4 = lane >> 4, part = (lane >> 3) & 1, j = lane & 7;
+    const __nv_bfloat16* const fs_lane = fs + part * kC + j * 8;
+    const uint32_t f_dst_lane = part * kPart + (row_base + 8 * l4) * 128;
+    // Bx: lane -> (row lane / 2 of the warp's 16, slots 2 (lane % 2) and 2 (lane % 2) + 1)
+    const int brow = lane >> 1, bq0 = 2 * (lane & 1);
+    uint32_t item = 0;
+    UWalk walk;
+    walk.init(group_begin, group_rows, groups);
+    // plan entries of the next block: the ids of this lane's eight rows (the plan
+    // starts every group on a multiple of four rows: 16-byte loads) and the pair
+    // indices of its two slots
+    int left_n = 0;
+    int4 ida_n = make_int4(0, 0, 0, 0), idb_n = ida_n;
+    int2 pr_n = make_int2(-1, -1);
+    auto prefetch = [&]() {
+      const int r0 = walk.t.ra + walk.b * kRows + row_base;        // first row of this warp
+      left_n = walk.t.rows - walk.b * kRows - row_base;             // rows of the warp that exist (may be <= 0)
+      const int4* idp = reinterpret_cast<const int4*>(rows_id + r0 + 8 * l4);
+      ida_n = idb_n = make_int4(0, 0, 0, 0);
+      if (8 * l4 < left_n) ida_n = __ldg(idp);
+      if (8 * l4 + 4 < left_n) idb_n = __ldg(idp + 1);
+      pr_n = make_int2(-1, -1);
+      if (brow < left_n)
+        pr_n = __ldg(reinterpret_cast<const int2*>(rows_pair + r0 + brow) + (lane & 1));
+    };
+    if (walk.valid) prefetch();
+    while (walk.valid) {
+      const int left = left_n;
+      const int ids[8] = {ida_n.x, ida_n.y, ida_n.z, ida_n.w, idb_n.x, idb_n.y, idb_n.z, idb_n.w};
+      const int2 pr = pr_n;
+      walk.advance();
+      if (walk.valid) prefetch();
+      // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  The MMAs read
+      // whole steps of 16 rows, which are exactly one warp's rows: a warp with at
+      // least one row zero-fills the rest of its 16, a warp without rows copies
+      // nothing (its step is never read).  (An id beyond the group's rows may be
+      // anything: it is only used as the address of a copy of zero bytes, so it is
+      // replaced by 0.)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        const uint32_t unit = (2 * item + kb) % kUnits;
+        mbar_wait(smem_u32(&bars->f_empty[unit]), (((2 * item + kb) / kUnits) & 1) ^ 1, abort_flag,
+                  err_flag);
+        const uint32_t base = smem_u32(f_ring + (size_t)unit * kUnitBytes) + f_dst_lane;
+        const int nv = left - 8 * l4;   // this lane's rows `it` with it < nv exist
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          // row row_base + 8 * l4 + it: (row % 8) == it, the swizzle is a constant
+          if (left > 0)
+            cp_async16_zfill(base + it * 128 + ((j ^ it) << 4),
+                             fs_lane + (int64_t)(it < nv ? ids[it] : 0) * 2 * kC + kb * 64, it < nv);
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
+                     ::"r"(smem_u32(&bars->f_full[unit])) : "memory");
+      }
+      // ---- Bx: the basis rows of the plan's pairs, zeros where there is none
+      {
+        const uint32_t stage = item & 1;
+        mbar_wait(smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
+        const int r = row_base + brow;
+        const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + r * 128;
+        if (left > 0) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int m = u == 0 ? pr.x : pr.y;
+            const __nv_bfloat16* src = basis_pair + (int64_t)(m < 0 ? 0 : m) * (2 * kK);
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)   // (hi | mid part, half of the 16 basis functions)
+              cp_async16_zfill(base + (c4 >> 1) * kPart + (((2 * (bq0 + u) + (c4 & 1)) ^ (r & 7)) << 4),
+                               src + (c4 >> 1) * kK + (c4 & 1) * 8, m >= 0);
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
+                     ::"r"(smem_u32(&bars->bx_full[stage])) : "memory");
+      }
+      ++item;
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t item = 0, tile_i = 0;
+      UTile next = load_utile(group_begin, group_rows, groups, blockIdx.x);
+      for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
+        const UTile t = next;
+        next = load_utile(group_begin, group_rows, groups, g + gridDim.x);
+        const int nb = t.blocks();
+        if (nb == 0) continue;
+        const uint32_t abuf = tile_i & 1;
+        mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((tile_i >> 1) & 1) ^ 1, abort_flag, err_flag);
+        tc_fence_after();
+        const uint32_t d = tmem_base + abuf * 64;
+        uint32_t accumulate = 0;
+        for (int b = 0; b < nb; ++b, ++item) {
+          const uint32_t u0 = (2 * item) % kUnits;          // even: u0 + 1 is the next unit in memory
+          const uint32_t fph = ((2 * item) / kUnits) & 1;
+          const uint32_t stage = item & 1;
+          mbar_wait(smem_u32(&bars->f_full[u0]), fph, abort_flag, err_flag);
+          mbar_wait(smem_u32(&bars->f_full[u0 + 1]), fph, abort_flag, err_flag);
+          mbar_wait(smem_u32(&bars->bx_full[stage]), (item >> 1) & 1, abort_flag, err_flag);
+          fence_proxy_async();   // the copied rows were written through the generic proxy
+          tc_fence_after();
+          const uint32_t f_hi = smem_u32(f_ring + (size_t)u0 * kUnitBytes), f_mid = f_hi + kPart;
+          const uint32_t bx_hi = smem_u32(bx + (size_t)stage * kBxBytes), bx_mid = bx_hi + kPart;
+          const int steps = (min(kRows, t.rows - b * kRows) + 15) >> 4;
+          for (int kk = 0; kk < steps; ++kk) {
+            // both operands MN-major: 8 rows (reduction index) per 1024-byte atom, a
+            // step of 16 rows is 2048 bytes; the two 64-channel blocks of A lie one
+            // ring unit apart
+            const uint64_t da_hi = make_desc(f_hi + kk * 2048, kUnitBytes, 1024);
+            const uint64_t da_mid = make_desc(f_mid + kk * 2048, kUnitBytes, 1024);
+            const uint64_t db_hi = make_desc(bx_hi + kk * 2048, 8192, 1024);
+            const uint64_t db_mid = make_desc(bx_mid + kk * 2048, 8192, 1024);
+            umma_bf16(d, da_hi, db_mid, idesc, accumulate);
+            umma_bf16(d, da_mid, db_hi, idesc, 1u);
+            umma_bf16(d, da_hi, db_hi, idesc, 1u);
+            accumulate = 1u;
+          }
+          umma_commit(smem_u32(&bars->f_empty[u0]));
+          umma_commit(smem_u32(&bars->f_empty[u0 + 1]));
+          umma_commit(smem_u32(&bars->bx_empty[stage]));
+        }
+        umma_commit(smem_u32(&bars->acc_full[abuf]));
+        ++tile_i;
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    // Two warps per quarter of the tensor-memory lanes (lane = channel).  Half h
+    // takes samples 2 h and 2 h + 1 of the group: 16 columns each, i.e. this
+    // channel's 16 basis functions, 32 contiguous bytes of the sample's row in
+    // each of the hi and mid arrays; a warp writes 1 KB runs.
+    const int quarter = warp & 3;
+    const int half = (warp - kEpiWarp0) >> 2;
+    const int c = quarter * 32 + lane;
+    uint32_t tile_i = 0;
+    UTile next = load_utile(group_begin, group_rows, groups, blockIdx.x);
+    for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
+      const UTile t = next;
+      next = load_utile(group_begin, group_rows, groups, g + gridDim.x);
+      if (t.blocks() == 0) {
+        // no pair at all: the projection of these samples is zero
+        const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int64_t v = g * kG + 2 * half + u;
+          if (v < ns) {
+            const int64_t off = v * (kC * kK) + c * kK;
+            st_global_256(x_hi + off, zero); st_global_256(x_hi + off + 8, zero);
+            st_global_256(x_mid + off, zero); st_global_256(x_mid + off + 8, zero);
+          }
+        }
+        continue;
+      }
+      const uint32_t abuf = tile_i & 1;
+      mbar_wait(smem_u32(&bars->acc_full[abuf]), (tile_i >> 1) & 1, abort_flag, err_flag);
+      tc_fence_after();
+      const bool ok = !*abort_flag;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + abuf * 64;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int q = 2 * half + u;
+        const int64_t v = g * kG + q;
+        uint32_t a[16];
+        tmem_ld_x16(taddr + 16 * q, a);
+        if (v < ns && ok) {
+          uint32_t hv[8], mv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            split2_bf16(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]), hv[i], mv[i]);
+          const int64_t off = v * (kC * kK) + c * kK;
+          st_global_256(x_hi + off, hv);
+          st_global_256(x_mid + off, mv);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[abuf]));
+      ++tile_i;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+// X in the plan's visiting order as the bf16 (hi, mid) pair: x_hi, x_mid
+// [ns, C * K], row v = the sample at position v of the order the plan was built
+// with.  basis_pair [M, 2, 16] bf16, fs [n_in, 2, C] bf16.
+int basis_proj_fwd_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* plan,
+                       const __nv_bfloat16* basis_pair, const __nv_bfloat16* fs,
+                       __nv_bfloat16* x_hi, __nv_bfloat16* x_mid, int* err_flag) {
+  TFGPC_REQUIRE((uintptr_t)fs % 16 == 0 && (uintptr_t)basis_pair % 16 == 0 &&
+                (uintptr_t)x_hi % 32 == 0 && (uintptr_t)x_mid % 32 == 0 &&
+                (uintptr_t)plan % 256 == 0,
+                "grouped projection expects 16-byte aligned inputs and 32-byte aligned outputs");
+  gp::PlanView v = gp::plan_view(const_cast<void*>(plan), ns, M);
+  auto kern = basis_proj_fwd_tcu_kernel;
+  TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kSmemBytes));
+  const int grid = (int)(v.groups < sm_count() ? v.groups : sm_count());
+  if (grid == 0) return TFGPC_OK;
+  ProfScope prof(st, "basis_proj_fwd_tcu");
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ns, v.groups, v.group_begin, v.group_rows, v.rows_id,
+                                           v.rows_pair, basis_pair, fs, x_hi, x_mid,
+                                           make_idesc(kC, 16 * kG, true, true), err_flag);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
+}  // namespace tfgpc

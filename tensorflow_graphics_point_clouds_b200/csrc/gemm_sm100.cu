@@ -100,6 +100,9 @@ struct Barriers {
 // four rows (basis_proj_grads_tc.cu describes the layout).  OUT = 2: the map of C
 // describes C^T ([N, M] row-major): boxes are transposed on their way through
 // shared memory, for products whose natural left operand is the small matrix.
+// OUT = 4: like 2, but row j of C^T goes to row row_order[j] of the output
+// (`image` is then the fp32 output, image_channels its row length): the rows of a
+// product computed in another sequence than the caller's are put back in place.
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
@@ -108,7 +111,7 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
                    const __grid_constant__ CUtensorMap tm_b_mid,
                    const __grid_constant__ CUtensorMap tm_c, int64_t m_total, int64_t n_total,
                    int bn, uint32_t idesc, TileSchedule sch, int* err_flag, uint8_t* image,
-                   int image_channels, int image_group) {
+                   int image_channels, int image_group, const int32_t* __restrict__ row_order) {
   extern __shared__ uint8_t smem_raw[];
   // the swizzled tiles need 1024-byte alignment
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -267,6 +270,34 @@ gemm_bf16x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi,
             store_image_row(image, image_channels, image_group, row, (n * bn + c0) / 16, r);
           continue;
         }
+        if (OUT == 4) {
+          // as OUT == 3 below: after the transposition this thread holds columns
+          // row0 .. row0 + 31 of C^T's row n * bn + c0 + lane, 128 contiguous bytes
+          uint8_t* box = my_stage;
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            *reinterpret_cast<uint32_t*>(box + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) +
+                                         (lane & 3) * 4) = r[i];
+          __syncwarp();
+          const int64_t j = (int64_t)n * bn + c0 + lane;
+          if (j < n_total && !*abort_flag) {
+            float* dst = reinterpret_cast<float*>(image) +
+                         (int64_t)__ldg(row_order + j) * image_channels + row0;
+            if (row0 + 32 <= m_total) {
+#pragma unroll
+              for (int q = 0; q < 8; q += 2)   // whole 32-byte sectors per store
+                st_global_256(dst + 4 * q,
+                              *reinterpret_cast<const uint4*>(box + lane * 128 + ((q ^ (lane & 7)) << 4)),
+                              *reinterpret_cast<const uint4*>(box + lane * 128 + (((q + 1) ^ (lane & 7)) << 4)));
+            } else {
+              for (int e = 0; row0 + e < m_total; ++e)
+                dst[e] = *reinterpret_cast<const float*>(box + lane * 128 +
+                                                         (((e >> 2) ^ (lane & 7)) << 4) + (e & 3) * 4);
+            }
+          }
+          continue;
+        }
         if (OUT == 3) {
           // C^T tile: this thread holds 32 rows (samples c0 .. c0+31 of the tile)
           // of column row0 + lane.  Transposed through the warp's staging box, it
@@ -408,19 +439,20 @@ uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
 template <bool A_MN, bool B_MN, int OUT = 0>
 int launch(cudaStream_t st, const CUtensorMap* maps, int64_t M, int64_t N, int bn,
            TileSchedule sch, int* err_flag, uint8_t* image = nullptr, int image_channels = 0,
-           int image_group = 4) {
+           int image_group = 4, const int32_t* row_order = nullptr) {
   auto kern = gemm_bf16x3_kernel<A_MN, B_MN, OUT>;
   TFGPC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)kSmemBytes));
   const int tiles = sch.m_tiles * sch.n_tiles * sch.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  ProfScope prof(st, OUT == 3 ? "gemm_bf16x3_mn_k_image" : OUT == 2 ? "gemm_bf16x3_mn_k_t"
+  ProfScope prof(st, OUT == 4 ? "gemm_bf16x3_mn_k_scatter" : OUT == 3 ? "gemm_bf16x3_mn_k_image"
+                     : OUT == 2 ? "gemm_bf16x3_mn_k_t"
                      : OUT == 1 ? (B_MN ? "gemm_bf16x3_k_mn_image" : "gemm_bf16x3_k_k_image")
                               : A_MN ? (B_MN ? "gemm_bf16x3_mn_mn" : "gemm_bf16x3_mn_k")
                                      : (B_MN ? "gemm_bf16x3_k_mn" : "gemm_bf16x3_k_k"));
   kern<<<grid, kThreads, kSmemBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], M, N, bn,
                                            make_idesc(kBM, bn, A_MN, B_MN), sch, err_flag, image,
-                                           image_channels, image_group);
+                                           image_channels, image_group, row_order);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -592,6 +624,35 @@ int gemm_bf16x3_grad_image_tn(cudaStream_t stream, int channels, int64_t N, int6
   sch.k_blocks_per_split = sch.k_blocks;
   return launch<true, false, 3>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)image, channels,
                                 group);
+}
+
+int gemm_bf16x3_tn_scatter(cudaStream_t stream, int64_t M, int64_t N, int64_t K,
+                           const GemmOperand& a, const GemmOperand& b, float* out, int64_t ld_out,
+                           const int32_t* row_order, int* err_flag) {
+  TFGPC_REQUIRE(M > 0 && N > 0 && K > 0 && M < (int64_t)INT32_MAX && N < (int64_t)INT32_MAX &&
+                K < (int64_t)INT32_MAX && ld_out < (int64_t)INT32_MAX,
+                "GEMM expects positive sizes below 2^31");
+  TFGPC_REQUIRE(a.major == Major::MN && b.major == Major::K && row_order && out &&
+                (uintptr_t)out % 32 == 0 && ld_out % 8 == 0,
+                "row-scattering GEMM expects an MN-major left and a K-major right operand and "
+                "32-byte aligned output rows");
+  int bn = (int)(N < kBNMax ? N : kBNMax);
+  bn = (bn + 31) / 32 * 32;
+  CUtensorMap maps[5] = {};
+  int rc;
+  if ((rc = make_map(&maps[0], a.hi, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[1], a.mid, M, K, a.ld, 64, kBK))) return rc;
+  if ((rc = make_map(&maps[2], b.hi, K, N, b.ld, kBK, bn))) return rc;
+  if ((rc = make_map(&maps[3], b.mid, K, N, b.ld, kBK, bn))) return rc;
+  TileSchedule sch;
+  sch.m_tiles = (int)((M + kBM - 1) / kBM);
+  sch.n_tiles = (int)((N + bn - 1) / bn);
+  sch.k_blocks = (int)((K + kBK - 1) / kBK);
+  sch.k_splits = 1;
+  sch.add_slices = 0;
+  sch.k_blocks_per_split = sch.k_blocks;
+  return launch<true, false, 4>(stream, maps, M, N, bn, sch, err_flag, (uint8_t*)out, (int)ld_out, 4,
+                                row_order);
 }
 
 int gemm_bf16x3_tn(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,

@@ -62,6 +62,13 @@ int gemm_bf16x3_grad_image_tn(cudaStream_t stream, int channels, int64_t N, int6
 int gemm_bf16x3_tn(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const GemmOperand& a,
                    const GemmOperand& b, float* ct, int64_t ldct, int* err_flag);
 
+// The same product with row j of C^T written to row row_order[j] of `out`
+// ([*, ld_out] fp32, 32-byte aligned rows): for right operands whose rows come in
+// another sequence than the caller's.
+int gemm_bf16x3_tn_scatter(cudaStream_t stream, int64_t M, int64_t N, int64_t K,
+                           const GemmOperand& a, const GemmOperand& b, float* out, int64_t ld_out,
+                           const int32_t* row_order, int* err_flag);
+
 // Number of k slices that fills the GPU for an [M,N] output with reduction K.
 int gemm_pick_k_splits(int64_t M, int64_t N, int64_t K);
 

@@ -83,7 +83,8 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
         for (int d = 0; d < D; ++d) pre = fmaf(diff[d], w_s[d * K + k], pre);
         v[i] = act_fwd(pre, act, alpha) * inv_pdf;
       }
-      if (WIDE) {
+      if (!basis) {
+      } else if (WIDE) {
         st_global_256(dst + 8 * q, v);
       } else {
         reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
@@ -307,7 +308,7 @@ static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float*
   int rc = check_kb_args("KernelBasis", D, K, M, activation);
   if (rc) return rc;
   if (M == 0) return TFGPC_OK;
-  TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && basis_out,
+  TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && (basis_out || pair_out),
                 "KernelBasis got a null pointer");
   TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0 && (uintptr_t)pair_out % 32 == 0,
                 "KernelBasis expects 16-byte aligned outputs (32 for the bf16 pair)");

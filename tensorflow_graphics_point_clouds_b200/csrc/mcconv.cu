@@ -39,6 +39,11 @@ int basis_proj_grads_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* pla
                          const int32_t* ranges, const void* image, float* dbasis, float* dfeat,
                          int* err_flag);
 
+// basis_proj_fwd_tcu.cu: the projection on the rows of a group plan
+int basis_proj_fwd_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* plan,
+                       const __nv_bfloat16* basis_pair, const __nv_bfloat16* fs,
+                       __nv_bfloat16* x_hi, __nv_bfloat16* x_mid, int* err_flag);
+
 namespace {
 
 struct McWs {
@@ -49,7 +54,6 @@ struct McWs {
   float* dx;                        // [ns, C*K]    (backward)
   __nv_bfloat16* fs;                // [n_in, 2, C] split features (tensor-core projection)
   __nv_bfloat16 *wt_hi, *wt_mid;    // [Cout, C*K]: W transposed (backward)
-  __nv_bfloat16 *gv_hi, *gv_mid;    // [ns, Cout]: out_grads rows in visiting order (grouped backward)
   int dw_splits;
   size_t bytes;
 };
@@ -70,7 +74,6 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
   if (basis_proj_mma_supported(K, C)) w.fs = (__nv_bfloat16*)take((size_t)n_in * C * 4);
   w.dw_splits = 1;
   w.g_hi = w.g_mid = nullptr; w.dx = nullptr; w.wt_hi = w.wt_mid = nullptr;
-  w.gv_hi = w.gv_mid = nullptr;
   if (backward) {
     w.g_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
     w.g_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
@@ -80,10 +83,6 @@ McWs carve(void* ws, int K, int C, int Cout, int64_t ns, int64_t n_in, bool back
     w.wt_hi = (__nv_bfloat16*)take(ck * Cout * 2);
     w.wt_mid = (__nv_bfloat16*)take(ck * Cout * 2);
     w.dw_splits = gemm_pick_k_splits((int64_t)ck, Cout, ns);
-    if (basis_proj_grads_tc_supported(K, C)) {
-      w.gv_hi = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
-      w.gv_mid = (__nv_bfloat16*)take((size_t)ns * Cout * 2);
-    }
   }
   w.bytes = (size_t)(p - (char*)ws);
   return w;
@@ -245,20 +244,75 @@ extern "C" int tfgpc_mcconv_grouped_supported(int K, int C) {
   return basis_proj_grads_tc_supported(K, C) ? 1 : 0;
 }
 
+namespace {
+
+int check_grouped_args(const char* op, int K, int C, int Cout, const void* features,
+                       const void* basis_pair, const void* ws, const void* plan) {
+  TFGPC_REQUIRE(basis_proj_grads_tc_supported(K, C),
+                "%s on a group plan expects K = 16 basis functions and C = 128 features", op);
+  TFGPC_REQUIRE(Cout >= 128, "%s on a group plan expects at least 128 output features", op);
+  TFGPC_REQUIRE((uintptr_t)features % 16 == 0 && (uintptr_t)basis_pair % 32 == 0 &&
+                (uintptr_t)ws % 256 == 0 && (uintptr_t)plan % 256 == 0,
+                "%s on a group plan expects 16-byte aligned features, a 32-byte aligned basis pair "
+                "and 256-byte aligned workspace and plan", op);
+  return TFGPC_OK;
+}
+
+// The projection in the plan's visiting order, into the workspace.
+int project_grouped(cudaStream_t st, int C, int64_t ns, int64_t n_in, int64_t M,
+                    const void* basis_pair, const float* features, const void* plan,
+                    const McWs& w) {
+  int rc = split_features(st, features, n_in, C, w.fs);
+  if (rc) return rc;
+  return basis_proj_fwd_tcu(st, ns, M, plan, (const __nv_bfloat16*)basis_pair, w.fs, w.x_hi,
+                            w.x_mid, w.err);
+}
+
+}  // namespace
+
+// Forward pass on the rows of a group plan: the projection is computed once per
+// distinct neighbor of a group and written in the plan's visiting order; the
+// weight GEMM puts its output rows back into the sample order.
+extern "C" int tfgpc_mcconv_forward_grouped(
+    void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in, int64_t M,
+    const void* basis_pair, const float* features, const float* weights, const int32_t* order,
+    const void* plan, float* out, void* ws, size_t ws_bytes) {
+  int rc = check_mc_args("MCConvForward", K, C, Cout, ns, n_in, M);
+  if (rc) return rc;
+  if (ns == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(weights && out && ws && order && plan && (M == 0 || (basis_pair && features)),
+                "MCConvForward got a null pointer");
+  rc = check_grouped_args("MCConvForward", K, C, Cout, features, basis_pair, ws, plan);
+  if (rc) return rc;
+  TFGPC_REQUIRE((uintptr_t)out % 32 == 0, "MCConvForward on a group plan expects a 32-byte aligned output");
+  if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 0))
+    return fail(TFGPC_ENOMEM, "MCConvForward workspace too small: %zu < %zu", ws_bytes,
+                tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 0));
+  cudaStream_t st = (cudaStream_t)stream;
+  McWs w = carve(ws, K, C, Cout, ns, n_in, false);
+  const int64_t ck = (int64_t)C * K;
+  TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
+  rc = project_grouped(st, C, ns, n_in, M, basis_pair, features, plan, w);
+  if (rc) return rc;
+  rc = split_to_bf16(st, weights, ck * Cout, w.w_hi, w.w_mid);
+  if (rc) return rc;
+  GemmOperand a{w.x_hi, w.x_mid, ck, Major::K};
+  GemmOperand b{w.w_hi, w.w_mid, (int64_t)Cout, Major::MN};
+  // out^T = W^T * X^T; column v of out^T is the sample order[v]
+  return gemm_bf16x3_tn_scatter(st, Cout, ns, ck, b, a, out, Cout, order, w.err);
+}
+
 // The backward pass on the rows of a group plan: dX is produced in the plan's
 // visiting order (the rows of out_grads are gathered while they are split), the
 // projection gradients run per distinct neighbor of a group instead of per
 // pair, dW is unchanged.
 extern "C" int tfgpc_mcconv_backward_grouped(
-    void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in, int64_t M, const float* basis,
-    const void* basis_pair, const float* features, const int32_t* neighbors,
-    const int32_t* ranges, const float* weights, const float* out_grads, int x_in_workspace,
-    const int32_t* order, const void* plan, float* dbasis_out, float* dfeat_out,
-    float* dweights_out, void* ws, size_t ws_bytes) {
+    void* stream, int K, int C, int Cout, int64_t ns, int64_t n_in, int64_t M,
+    const void* basis_pair, const float* features, const int32_t* ranges, const float* weights,
+    const float* out_grads, int x_in_workspace, const int32_t* order, const void* plan,
+    float* dbasis_out, float* dfeat_out, float* dweights_out, void* ws, size_t ws_bytes) {
   int rc = check_mc_args("MCConvBackward", K, C, Cout, ns, n_in, M);
   if (rc) return rc;
-  TFGPC_REQUIRE(basis_proj_grads_tc_supported(K, C),
-                "MCConvBackward on a group plan expects K = 16 basis functions and C = 128 features");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t ck = (int64_t)C * K;
   TFGPC_REQUIRE(dweights_out && weights, "MCConvBackward got a null pointer");
@@ -268,26 +322,26 @@ extern "C" int tfgpc_mcconv_backward_grouped(
     if (n_in > 0 && dfeat_out) TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));
     return TFGPC_OK;
   }
-  TFGPC_REQUIRE(basis && basis_pair && features && neighbors && ranges && out_grads && order &&
-                plan && dbasis_out && dfeat_out && ws, "MCConvBackward got a null pointer");
-  TFGPC_REQUIRE((uintptr_t)basis % 16 == 0 && (uintptr_t)basis_pair % 16 == 0 &&
-                (uintptr_t)out_grads % 16 == 0 && (uintptr_t)features % 16 == 0 &&
-                (uintptr_t)dbasis_out % 32 == 0 && (uintptr_t)dfeat_out % 16 == 0 &&
-                (uintptr_t)ws % 256 == 0 && (uintptr_t)plan % 256 == 0,
-                "MCConvBackward on a group plan expects 16-byte aligned buffers (dbasis 32, "
-                "workspace and plan 256)");
+  TFGPC_REQUIRE(basis_pair && features && ranges && out_grads && order && plan && dbasis_out &&
+                dfeat_out && ws, "MCConvBackward got a null pointer");
+  rc = check_grouped_args("MCConvBackward", K, C, Cout, features, basis_pair, ws, plan);
+  if (rc) return rc;
+  TFGPC_REQUIRE((uintptr_t)out_grads % 16 == 0 && (uintptr_t)dbasis_out % 32 == 0 &&
+                (uintptr_t)dfeat_out % 16 == 0,
+                "MCConvBackward on a group plan expects 16-byte aligned gradients (dbasis 32)");
   if (ws_bytes < tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1))
     return fail(TFGPC_ENOMEM, "MCConvBackward workspace too small: %zu < %zu", ws_bytes,
                 tfgpc_mcconv_workspace_bytes(K, C, Cout, ns, n_in, 1));
   McWs w = carve(ws, K, C, Cout, ns, n_in, true);
   if (!x_in_workspace) {
     TFGPC_CUDA(cudaMemsetAsync(w.err, 0, sizeof(int), st));
-    rc = project(st, K, C, ns, n_in, basis, features, neighbors, ranges, w);
+    rc = project_grouped(st, C, ns, n_in, M, basis_pair, features, plan, w);
     if (rc) return rc;
   }
-  rc = split_to_bf16(st, out_grads, ns * Cout, w.g_hi, w.g_mid);
-  if (rc) return rc;
-  rc = split_rows_gather_to_bf16(st, out_grads, order, ns, Cout, w.gv_hi, w.gv_mid);
+  // X lies in the visiting order (tfgpc_mcconv_forward_grouped wrote it so): the
+  // rows of out_grads are brought into the same order while they are split, for
+  // both products
+  rc = split_rows_gather_to_bf16(st, out_grads, order, ns, Cout, w.g_hi, w.g_mid);
   if (rc) return rc;
   constexpr int group = 4;
   if (ns % group != 0) {
@@ -297,7 +351,7 @@ extern "C" int tfgpc_mcconv_backward_grouped(
   rc = split_transpose_to_bf16(st, weights, ck, Cout, w.wt_hi, w.wt_mid);
   if (rc) return rc;
   GemmOperand wt_mn{w.wt_hi, w.wt_mid, ck, Major::MN};
-  GemmOperand gv_k{w.gv_hi, w.gv_mid, (int64_t)Cout, Major::K};
+  GemmOperand gv_k{w.g_hi, w.g_mid, (int64_t)Cout, Major::K};
   rc = gemm_bf16x3_grad_image_tn(st, C, ns, Cout, wt_mn, gv_k, w.dx, group, w.err);
   if (rc) return rc;
   TFGPC_CUDA(cudaMemsetAsync(dfeat_out, 0, sizeof(float) * (size_t)n_in * C, st));

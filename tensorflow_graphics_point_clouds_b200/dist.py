@@ -43,6 +43,14 @@ def allreduce_sum_(tensors, group=None):
   return tensors
 
 
+def allreduce_max_(tensor, group=None):
+  """Element-wise maximum of a tensor over all ranks, in place (the cell counts of
+  a sharded batch: pc.PointCloud(num_cells_reduce=allreduce_max_))."""
+  if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+    dist.all_reduce(tensor, op=dist.ReduceOp.MAX, group=group)
+  return tensor
+
+
 def max_over_ranks(value, device, group=None):
   """Maximum of a Python float over all ranks (timings are reported as the
   slowest rank's)."""

@@ -71,6 +71,7 @@ class ProjectionGemm:
         c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),
         ptr(neighbors), ptr(ranges), ptr(weights), ptr(out), ptr(self.ws), c_sz(self.nbytes)))
     self._x_valid = self.backward_ws
+    self._x_grouped = False
     return out
 
   def backward(self, basis, features, neighbors, ranges, weights, out_grads, reuse_forward=True):
@@ -86,26 +87,41 @@ class ProjectionGemm:
         _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
         c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(features),
         ptr(neighbors), ptr(ranges), ptr(weights), ptr(out_grads),
-        c_int(int(reuse_forward and self._x_valid)), ptr(dbasis), ptr(dfeat), ptr(dw),
-        ptr(self.ws), c_sz(self.nbytes)))
+        c_int(int(reuse_forward and self._x_valid and not getattr(self, '_x_grouped', False))),
+        ptr(dbasis), ptr(dfeat), ptr(dw), ptr(self.ws), c_sz(self.nbytes)))
     return dbasis, dfeat, dw
 
-  def backward_grouped(self, basis, basis_pair, features, neighbors, ranges, weights, out_grads,
-                       order, plan, reuse_forward=True):
-    """The same gradients through tfgpc_mcconv_backward_grouped: the projection
-    gradients run once per distinct neighbor of a group of four samples (taken in
-    `order`) instead of once per pair."""
-    basis, features, weights = _f32(basis), _f32(features), _f32(weights)
-    neighbors, ranges, out_grads = _i32(neighbors), _i32(ranges), _f32(out_grads)
-    dbasis = torch.empty_like(basis)
+  def forward_grouped(self, basis_pair, features, weights, order, plan):
+    """The forward pass through tfgpc_mcconv_forward_grouped: the projection runs
+    once per distinct neighbor of a group of four samples (taken in `order`)
+    instead of once per pair; basis_pair [M, 2, K] bf16."""
+    features, weights = _f32(features), _f32(weights)
+    out = torch.empty((self.ns, self.cout), dtype=torch.float32, device=features.device)
+    self._ensure_workspace(features.shape[0])
+    _lib.check(_lib.lib().tfgpc_mcconv_forward_grouped(
+        _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
+        c_i64(features.shape[0]), c_i64(basis_pair.shape[0]), ptr(basis_pair), ptr(features),
+        ptr(weights), ptr(_i32(order)), ptr(plan), ptr(out), ptr(self.ws), c_sz(self.nbytes)))
+    self._x_valid = self.backward_ws
+    self._x_grouped = True
+    return out
+
+  def backward_grouped(self, basis_pair, features, ranges, weights, out_grads, order, plan,
+                       reuse_forward=True):
+    """The gradients through tfgpc_mcconv_backward_grouped (dbasis [M, K] fp32,
+    dfeat, dweights)."""
+    features, weights = _f32(features), _f32(weights)
+    ranges, out_grads = _i32(ranges), _f32(out_grads)
+    m, k = basis_pair.shape[0], basis_pair.shape[2]
+    dbasis = torch.empty((m, k), dtype=torch.float32, device=features.device)
     dfeat = torch.empty_like(features)
     dw = torch.empty_like(weights)
     self._ensure_workspace(features.shape[0])
+    reuse = reuse_forward and self._x_valid and getattr(self, '_x_grouped', False)
     _lib.check(_lib.lib().tfgpc_mcconv_backward_grouped(
         _stream(), c_int(self.k), c_int(self.c), c_int(self.cout), c_i64(self.ns),
-        c_i64(features.shape[0]), c_i64(basis.shape[0]), ptr(basis), ptr(basis_pair),
-        ptr(features), ptr(neighbors), ptr(ranges), ptr(weights), ptr(out_grads),
-        c_int(int(reuse_forward and self._x_valid)), ptr(_i32(order)), ptr(plan), ptr(dbasis),
+        c_i64(features.shape[0]), c_i64(m), ptr(basis_pair), ptr(features), ptr(ranges),
+        ptr(weights), ptr(out_grads), c_int(int(reuse)), ptr(_i32(order)), ptr(plan), ptr(dbasis),
         ptr(dfeat), ptr(dw), ptr(self.ws), c_sz(self.nbytes)))
     return dbasis, dfeat, dw
 
@@ -157,14 +173,16 @@ def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activati
 
 
 def kernel_basis_split(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
-                       alpha=0.2):
-  """kernel_basis that also returns every row as the bf16 (hi, mid) pair the
-  tensor-core kernels multiply with: (basis [M, K] float32, pair [M, 2, K] bf16)."""
+                       alpha=0.2, want_fp32=True):
+  """kernel_basis that returns every row as the bf16 (hi, mid) pair the
+  tensor-core kernels multiply with: (basis [M, K] float32 or None, pair
+  [M, 2, K] bf16)."""
   points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
   d, k = w1.shape
   m = neighbors.shape[0]
-  basis = torch.empty((m, k), dtype=torch.float32, device=points_in.device)
+  basis = (torch.empty((m, k), dtype=torch.float32, device=points_in.device) if want_fp32
+           else None)
   pair = torch.empty((m, 2, k), dtype=torch.bfloat16, device=points_in.device)
   _lib.check(_lib.lib().tfgpc_kernel_basis_split(
       _stream(), c_int(d), c_int(k), c_i64(m), ptr(points_in), ptr(points_out), ptr(neighbors),
@@ -193,6 +211,64 @@ def group_plan(neighborhood, order=None):
   return order, plan
 
 
+def _mlp_blocks(weights, biases):
+  """Per-layer tensors [G, H_{l-1}, H_l] / [G, 1, H_l] -> (flat weights, flat
+  biases, layer sizes as a host int32 array, D, G)."""
+  weights = [_f32(w) for w in weights]
+  biases = [_f32(b) for b in biases]
+  g, d, _ = weights[0].shape
+  sizes = (ctypes.c_int32 * len(weights))(*[int(w.shape[2]) for w in weights])
+  flat_w = torch.cat([w.reshape(-1) for w in weights]).contiguous()
+  flat_b = torch.cat([b.reshape(-1) for b in biases]).contiguous()
+  return flat_w, flat_b, sizes, int(d), int(g)
+
+
+def kernel_mlp_basis(points_in, points_out, neighbors, pdf, weights, biases, radius,
+                     activation=0, alpha=0.2):
+  """The kernel MLP with any number of hidden layers (tfgpc_kernel_mlp_basis):
+  weights[l] [G, H_{l-1}, H_l], biases[l] [G, 1, H_l] -> basis [M, G * H_last]."""
+  points_in, points_out, pdf, neighbors = _f32(points_in), _f32(points_out), _f32(pdf), _i32(neighbors)
+  flat_w, flat_b, sizes, d, g = _mlp_blocks(weights, biases)
+  m = neighbors.shape[0]
+  basis = torch.empty((m, g * int(sizes[len(sizes) - 1])), dtype=torch.float32,
+                      device=points_in.device)
+  _lib.check(_lib.lib().tfgpc_kernel_mlp_basis(
+      _stream(), c_int(d), c_int(g), c_int(len(sizes)), sizes, c_i64(m), ptr(points_in),
+      ptr(points_out), ptr(neighbors), ptr(pdf), ptr(flat_w), ptr(flat_b),
+      ctypes.c_float(1.0 / float(radius)), c_int(activation), ctypes.c_float(alpha), ptr(basis)))
+  return basis
+
+
+def kernel_mlp_grads(points_in, points_out, neighbors, pdf, weights, biases, radius, basis_grads,
+                     activation=0, alpha=0.2, point_grads=False):
+  """All gradients of kernel_mlp_basis (tfgpc_kernel_mlp_grads): ([d_weights],
+  [d_biases]) in the layouts of the inputs and, with point_grads, also
+  (d_points_in, d_points_out, d_pdf [M]); when points_in and points_out are the
+  same tensor, d_points_in and d_points_out are one tensor holding the sum."""
+  points_in, points_out, pdf, neighbors = _f32(points_in), _f32(points_out), _f32(pdf), _i32(neighbors)
+  basis_grads = _f32(basis_grads)
+  flat_w, flat_b, sizes, d, g = _mlp_blocks(weights, biases)
+  dw, db = torch.empty_like(flat_w), torch.empty_like(flat_b)
+  dpin = dpout = dpdf = None
+  if point_grads:
+    dpin = torch.empty_like(points_in)
+    dpout = dpin if points_out.data_ptr() == points_in.data_ptr() else torch.empty_like(points_out)
+    dpdf = torch.empty_like(pdf)
+  _lib.check(_lib.lib().tfgpc_kernel_mlp_grads(
+      _stream(), c_int(d), c_int(g), c_int(len(sizes)), sizes, c_i64(neighbors.shape[0]),
+      c_i64(points_in.shape[0]), c_i64(points_out.shape[0]), ptr(points_in), ptr(points_out),
+      ptr(neighbors), ptr(pdf), ptr(flat_w), ptr(flat_b), ctypes.c_float(1.0 / float(radius)),
+      c_int(activation), ctypes.c_float(alpha), ptr(basis_grads), ptr(dw), ptr(db), ptr(dpin),
+      ptr(dpout), ptr(dpdf)))
+  d_weights, d_biases, ow, ob = [], [], 0, 0
+  for w, b in zip(weights, biases):
+    d_weights.append(dw[ow:ow + w.numel()].reshape(w.shape)); ow += w.numel()
+    d_biases.append(db[ob:ob + b.numel()].reshape(b.shape)); ob += b.numel()
+  if point_grads:
+    return d_weights, d_biases, dpin, dpout, dpdf
+  return d_weights, d_biases
+
+
 def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, basis_grads,
                        activation=0, alpha=0.2):
   """Gradients of kernel_basis with respect to w1 and b1 (tfgpc_kernel_basis_grads)."""
@@ -209,17 +285,32 @@ def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, ba
   return dw1, db1
 
 
+# MCConv.py:27-31 / PointConv.py:27-31: name -> (activation code, slope) of the kernel-basis entries
+NON_LINEARITIES = {'relu': (0, 0.0), 'lrelu': (0, 0.2), 'leakyrelu': (0, 0.2),
+                   'leaky_relu': (0, 0.2), 'elu': (1, 0.0)}
+
+
 class MCConv:
   """Monte-Carlo convolution layer (MCConv.py:36-278) with explicit backward.
 
-  Weights use the reference's layouts: w1 [G, D, H], b1 [G, 1, H] (one hidden
-  layer kernel MLP, leaky ReLU), wf [G, C_in*H, C_out/G]."""
+  Weights use the reference's layouts: w1 [G, D, H], b1 [G, 1, H] for a kernel
+  MLP with one hidden layer, or lists of per-layer tensors ([G, H_{l-1}, H_l],
+  [G, 1, H_l]) for deeper ones (MCConv.py:92-135, 165-168); wf
+  [G, C_in*H_last, C_out/G].  non_linearity_type as in MCConv.py:27-31
+  ('relu', 'leaky_relu', 'elu')."""
 
-  def __init__(self, w1, b1, wf, num_features_in, grouped=True):
-    self.w1, self.b1, self.wf = _f32(w1), _f32(b1), _f32(wf)
+  def __init__(self, w1, b1, wf, num_features_in, grouped=True, non_linearity_type='leaky_relu'):
+    multi = isinstance(w1, (list, tuple))
+    self.kernel_weights = [_f32(w) for w in (w1 if multi else [w1])]
+    self.kernel_biases = [_f32(b) for b in (b1 if multi else [b1])]
+    self._list_form = multi
+    self.wf = _f32(wf)
+    self.w1, self.b1 = self.kernel_weights[0], self.kernel_biases[0]
     self.grouped = bool(grouped)
     self._grouped = None
-    self.num_mlps, self.dims, self.hidden = self.w1.shape
+    self.num_mlps, self.dims, _ = self.kernel_weights[0].shape
+    self.hidden = int(self.kernel_weights[-1].shape[2])
+    self.activation, self.alpha = NON_LINEARITIES[non_linearity_type.lower()]
     self.cin = int(num_features_in)
     self.cout = self.wf.shape[2] * self.num_mlps
     self.k = self.num_mlps * self.hidden
@@ -249,46 +340,79 @@ class MCConv:
     pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
     w1, b1 = self._flat_kernel_weights()
     ns = point_cloud_out._points.shape[0]
-    # wide layers run their backward pass on a group plan (see group_plan)
-    grouped = (keep_for_backward and self.grouped and neigh._neighbors.shape[0] > 0 and
+    p_in, p_out, ids = point_cloud_in._points, point_cloud_out._points, neigh._original_neigh_ids
+    one_layer = len(self.kernel_weights) == 1
+    # wide layers run on a group plan (see group_plan)
+    grouped = (one_layer and self.grouped and neigh._neighbors.shape[0] > 0 and
+               self.cout >= 128 and
                _lib.lib().tfgpc_mcconv_grouped_supported(c_int(self.k), c_int(self.cin)) != 0)
     if grouped:
-      basis, pair = kernel_basis_split(point_cloud_in._points, point_cloud_out._points,
-                                       neigh._original_neigh_ids, pdf, w1, b1, radius)
+      # the basis only as the bf16 pair the tensor-core kernels read
+      basis, pair = kernel_basis_split(p_in, p_out, ids, pdf, w1, b1, radius, self.activation,
+                                       self.alpha, want_fp32=False)
       self._grouped = (pair,) + group_plan(neigh)
+    elif one_layer:
+      basis = kernel_basis(p_in, p_out, ids, pdf, w1, b1, radius, self.activation, self.alpha)
+      self._grouped = None
     else:
-      basis = kernel_basis(point_cloud_in._points, point_cloud_out._points,
-                           neigh._original_neigh_ids, pdf, w1, b1, radius)
+      basis = kernel_mlp_basis(p_in, p_out, ids, pdf, self.kernel_weights, self.kernel_biases,
+                               radius, self.activation, self.alpha)
       self._grouped = None
     if (self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward):
       self._op = ProjectionGemm(self.k, self.cin, self.cout, ns, features.device,
                                 backward=keep_for_backward)
     wd = self._dense_weights()
-    out = self._op.forward(basis, features, neigh._original_neigh_ids,
-                           neigh._samples_neigh_ranges, wd)
+    if grouped:
+      out = self._op.forward_grouped(self._grouped[0], features, wd, self._grouped[1],
+                                     self._grouped[2])
+    else:
+      out = self._op.forward(basis, features, ids, neigh._samples_neigh_ranges, wd)
     if keep_for_backward:
       self._saved = (neigh, point_cloud_in, point_cloud_out, radius, pdf, basis,
                      _f32(features), wd, w1, b1)
     return out
 
-  def backward(self, out_grads):
+  def saved_basis(self):
+    """The kernel basis [M, K] of the last forward call as float32 (on the grouped
+    path it is kept as a bf16 pair: the sum of the two terms is returned)."""
+    basis = self._saved[5]
+    if basis is None:
+      pair = self._grouped[0]
+      basis = pair[:, 0, :].float() + pair[:, 1, :].float()
+    return basis
+
+  def backward(self, out_grads, point_grads=False):
     """Gradients of the last forward call: (d_features, d_w1, d_b1, d_wf) in the
-    layouts of the weights."""
+    layouts of the weights (d_w1 / d_b1 are lists if the layer was built from
+    lists).  With point_grads=True three more values follow: d_points_in,
+    d_points_out (the gradients through the kernel inputs, MCConv.py:264-269;
+    one tensor holding the sum of both if the two clouds share their point
+    tensor) and d_pdf [M], the gradient with respect to the per-pair densities,
+    which Neighborhood.pdf_point_grads carries on to the points."""
     neigh, pc_in, pc_out, radius, pdf, basis, features, wd, w1, b1 = self._saved
+    ids = neigh._original_neigh_ids
     if self._grouped is not None:
       pair, order, plan = self._grouped
       dbasis, dfeat, dwd = self._op.backward_grouped(
-          basis, pair, features, neigh._original_neigh_ids, neigh._samples_neigh_ranges, wd,
-          out_grads, order, plan)
+          pair, features, neigh._samples_neigh_ranges, wd, out_grads, order, plan)
     else:
-      dbasis, dfeat, dwd = self._op.backward(basis, features, neigh._original_neigh_ids,
-                                             neigh._samples_neigh_ranges, wd, out_grads)
-    dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, neigh._original_neigh_ids, pdf,
-                                  w1, b1, radius, dbasis)
-    dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()
-    db1 = db1.reshape(self.num_mlps, 1, self.hidden)
+      dbasis, dfeat, dwd = self._op.backward(basis, features, ids, neigh._samples_neigh_ranges,
+                                             wd, out_grads)
     dwf = (dwd.unsqueeze(0) if self.num_mlps == 1
            else blocks_of_dense_grad(dwd, self.num_mlps, self.cin, self.hidden))
+    if point_grads or len(self.kernel_weights) > 1:
+      res = kernel_mlp_grads(pc_in._points, pc_out._points, ids, pdf, self.kernel_weights,
+                             self.kernel_biases, radius, dbasis, self.activation, self.alpha,
+                             point_grads=point_grads)
+      dws, dbs = res[0], res[1]
+      head = (dfeat, dws if self._list_form else dws[0], dbs if self._list_form else dbs[0], dwf)
+      return head + tuple(res[2:]) if point_grads else head
+    dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, ids, pdf, w1, b1, radius, dbasis,
+                                  self.activation, self.alpha)
+    dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()
+    db1 = db1.reshape(self.num_mlps, 1, self.hidden)
+    if self._list_form:
+      return dfeat, [dw1], [db1], dwf
     return dfeat, dw1, db1, dwf
 
 
@@ -413,9 +537,6 @@ class KPConv(_ProjectedConv):
     return dfeat, dw
 
 
-# PointConv.py:27-31: name -> (activation code, slope) of tfgpc_kernel_basis
-NON_LINEARITIES = {'relu': (0, 0.0), 'lrelu': (0, 0.2), 'leakyrelu': (0, 0.2),
-                   'leaky_relu': (0, 0.2), 'elu': (1, 0.0)}
 
 
 class PointConv(_ProjectedConv):

@@ -31,7 +31,13 @@ def _to_dims(value, dims, device):
 class PointCloud:
   """Segmented point cloud: points [N, D] float32 and batch ids [N] int32."""
 
-  def __init__(self, points, batch_ids, batch_size=None):
+  def __init__(self, points, batch_ids, batch_size=None, num_cells_reduce=None):
+    # num_cells_reduce: for a cloud that is one shard of a batch spread over
+    # several ranks.  Grid.py:44-48 takes the cell counts as the maximum over the
+    # WHOLE batch; the callable gets this shard's counts ([D] int32 on the device)
+    # and returns the maximum over all shards (dist.allreduce_max_), so that every
+    # rank builds the keys the unsharded batch would have.
+    self._num_cells_reduce = num_cells_reduce
     self._points = torch.as_tensor(points).to(torch.float32).contiguous()
     self._batch_ids = torch.as_tensor(batch_ids, device=self._points.device).to(
         torch.int32).contiguous()
@@ -62,6 +68,8 @@ class Grid:
     sizes = self._aabb_max - self._aabb_min
     batch_num_cells = torch.ceil(sizes / self._cell_sizes).to(torch.int32)
     self._num_cells = torch.clamp(batch_num_cells.max(dim=0).values, min=1).to(torch.int32)
+    if pc._num_cells_reduce is not None:
+      self._num_cells = pc._num_cells_reduce(self._num_cells).to(torch.int32)
     self._num_cells_host = ops.read_device(self._num_cells)
     # custom_ops_wrapper.py:37-43
     self._scaled_aabb_min = self._aabb_min / self._cell_sizes
@@ -158,6 +166,29 @@ class Neighborhood:
     if self._pdf is None:
       self.compute_pdf(**kwargs)
     return self._pdf
+
+  def pdf_point_grads(self, pdf_grads, bandwidth=0.2, mode=0):
+    """Gradient of a loss with respect to the grid's points [N, D] (in their
+    original order) through the per-pair densities of get_pdf, given the loss's
+    gradient pdf_grads [M] with respect to those densities.  The chain of the
+    reference's autodiff: pdf[m] = point_pdf[neighbors[m, 0]] (Neighborhood.py:287),
+    point_pdf = ComputePdfWithPtGrads(sorted points, self neighborhood), whose
+    registered gradient is ComputePdfPtGrads (custom_ops_wrapper.py:159-169), and
+    sorted points = gather(points, sorted indices) (Grid.py:60-62)."""
+    g = self._grid
+    d = g._point_cloud._dimension
+    n = g._sorted_points.shape[0]
+    per_point = torch.zeros(n, dtype=torch.float32, device=g._sorted_points.device)
+    per_point.index_add_(0, self._neighbors[:, 0].to(torch.int64),
+                         torch.as_tensor(pdf_grads, dtype=torch.float32))
+    nb = self if self._equal_samples else Neighborhood(g, self._radii)
+    bw = _to_dims(bandwidth, d, self._radii.device)
+    grads_sorted = ops.compute_pdf_pt_grads(
+        g._sorted_points, nb._neighbors, nb._samples_neigh_ranges, torch.reciprocal(bw),
+        torch.reciprocal(self._radii), per_point, mode)
+    out = torch.empty_like(grads_sorted)
+    out[g._sorted_indices.to(torch.int64)] = grads_sorted
+    return out
 
 
 def sample(neighborhood, sample_mode='poisson'):

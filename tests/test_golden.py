@@ -69,7 +69,7 @@ def test_cuda_library_matches_golden(golden):
   dfeat, dw1, db1, dwf = layer.backward(t(golden["d_out"]))
   layer._op.check_status()
   close(neigh._point_pdf.cpu().numpy(), golden["point_pdf"])
-  close(layer._saved[5].cpu().numpy(), golden["basis"])
+  close(layer.saved_basis().cpu().numpy(), golden["basis"])
   close(out.cpu().numpy(), golden["out"])
   close(dfeat.cpu().numpy(), golden["d_feat"])
   close(dwf.cpu().numpy(), golden["d_wf"])

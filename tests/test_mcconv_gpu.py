@@ -148,7 +148,7 @@ def test_mcconv_layer_matches_oracle(d, g, h):
   out = layer.forward(t(feat), cloud, cloud, radius)
   dfeat, dw1, db1, dwf = layer.backward(t(d_out))
   layer._op.check_status()
-  close(layer._saved[5].cpu().numpy(), basis)
+  close(layer.saved_basis().cpu().numpy(), basis)
   close(out.cpu().numpy(), ref_out)
   close(dfeat.cpu().numpy(), ref_df)
   close(dwf.cpu().numpy(), ref_dwf)
@@ -191,3 +191,82 @@ def test_bounded_wait_runs_out_and_is_reported():
   # argument checks
   assert lib.tfgpc_debug_bounded_wait(stream, ptr(ws), c_sz(nbytes), ctypes.c_uint(0),
                                       ctypes.byref(returned)) == 1
+
+
+@pytest.mark.parametrize("hidden,g,act,own", [([8], 1, 'elu', False), ([6, 8], 1, 'leaky_relu', True),
+                                              ([8, 4], 2, 'elu', False), ([16], 1, 'relu', True),
+                                              ([5, 7, 8], 1, 'elu', True)])
+def test_mcconv_deep_kernel_mlp_and_point_gradients(hidden, g, act, own):
+  """Kernel MLPs with several hidden layers (MCConv.py:165-168) and the gradients
+  with respect to the point coordinates (monte_carlo_conv_test.py:182-219),
+  against the float64 layer of the oracle, whose analytic gradients are pinned
+  to finite differences in tests/test_oracle_known_answers.py."""
+  rng = np.random.default_rng(1000 + sum(hidden) + g)
+  b, n_pts, d, cin, cout, radius = 3, 1500, 3, 16, 32, 0.3
+  pts, bid = random_cloud(rng, b, n_pts, d)
+  if own:
+    smp, sbid = pts, bid
+  else:
+    smp, sbid = random_cloud(rng, b, 400, d)
+  feat = rng.normal(size=(n_pts, cin)).astype(F32)
+  sizes = [d] + hidden
+  ws = [rng.normal(size=(g, sizes[i], sizes[i + 1])).astype(F32) for i in range(len(hidden))]
+  bs = [(rng.normal(size=(g, 1, sizes[i + 1])) * 0.1).astype(F32) for i in range(len(hidden))]
+  wf = (rng.normal(size=(g, cin * hidden[-1], cout // g)) * 0.05).astype(F32)
+  d_out = rng.normal(size=(len(smp), cout)).astype(F32)
+  g_ref = pr.Grid(pts, bid, b, radius)
+  nb_ref = pr.Neighborhood(g_ref, radius, smp, sbid)
+  pdf = nb_ref.get_pdf(bandwidth=0.2, mode=0)
+  ref_out = pr.mcconv_layer(pts, smp, feat, nb_ref, pdf, ws, bs, wf, radius, act)
+  ref = pr.mcconv_layer_grads(pts, smp, feat, nb_ref, pdf, ws, bs, wf, radius, d_out, act)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  smp_cloud = cloud if own else pc.PointCloud(t(smp), t(sbid), b)
+  layer = mcconv.MCConv([t(w) for w in ws], [t(x) for x in bs], t(wf), cin,
+                        non_linearity_type=act)
+  out = layer.forward(t(feat), cloud, smp_cloud, radius)
+  dfeat, dws, dbs, dwf, dpin, dpout, dpdf = layer.backward(t(d_out), point_grads=True)
+  layer._op.check_status()
+  close(out.cpu().numpy(), ref_out)
+  close(dfeat.cpu().numpy(), ref["d_features"])
+  close(dwf.cpu().numpy(), ref["d_wf"])
+  for a, r in zip(dws, ref["d_weights"]):
+    close(a.cpu().numpy(), r, rel=2e-4)
+  for a, r in zip(dbs, ref["d_biases"]):
+    close(a.cpu().numpy(), r, rel=2e-4)
+  close(dpdf.cpu().numpy(), ref["d_pdf"], rel=2e-4)
+  if own:
+    assert dpin is dpout           # one cloud: one gradient, the sum of both roles
+    close(dpin.cpu().numpy(), ref["d_points_in"] + ref["d_points_out"], rel=2e-4)
+  else:
+    close(dpin.cpu().numpy(), ref["d_points_in"], rel=2e-4)
+    close(dpout.cpu().numpy(), ref["d_points_out"], rel=2e-4)
+
+
+@pytest.mark.parametrize("own", [True, False])
+def test_pdf_point_grads_follow_the_reference_chain(own):
+  """Neighborhood.pdf_point_grads: per-pair density gradients -> per-point sums ->
+  ComputePdfPtGrads on the sorted self neighborhood -> original point order."""
+  rng = np.random.default_rng(77)
+  b, n_pts, radius = 3, 2000, 0.25
+  pts, bid = random_cloud(rng, b, n_pts, 3)
+  g_ref = pr.Grid(pts, bid, b, radius)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  grid = pc.Grid(cloud, radius)
+  if own:
+    nb_ref, nb = pr.Neighborhood(g_ref, radius, pts, bid), pc.Neighborhood(grid, radius, cloud)
+  else:
+    smp, sbid = random_cloud(rng, b, 300, 3)
+    nb_ref = pr.Neighborhood(g_ref, radius, smp, sbid)
+    nb = pc.Neighborhood(grid, radius, pc.PointCloud(t(smp), t(sbid), b))
+  nb.get_pdf(bandwidth=0.2, mode=0)
+  gp = rng.normal(size=len(nb_ref.neighbors)).astype(F32)
+  got = nb.pdf_point_grads(t(gp), bandwidth=0.2, mode=0).cpu().numpy()
+  per_point = np.zeros(n_pts, np.float64)
+  np.add.at(per_point, nb_ref.neighbors[:, 0], gp)
+  self_ref = pr.Neighborhood(g_ref, radius)
+  inv = np.repeat(F32(1 / radius), 3); inv_bw = np.repeat(F32(1 / 0.2), 3)
+  ref_sorted = orc.compute_pdf_pt_grads(g_ref.sorted_points, self_ref.neighbors, self_ref.ranges,
+                                        inv_bw, inv, per_point.astype(F32), 0)
+  ref = np.empty_like(ref_sorted)
+  ref[g_ref.sorted_indices] = ref_sorted
+  close(got, ref, rel=2e-4)

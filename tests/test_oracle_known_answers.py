@@ -347,3 +347,68 @@ def test_pooling_matches_per_segment_loops(mode):
     ref = feat[bid == b].max(axis=0) if mode == 'max' else feat[bid == b].mean(axis=0)
     np.testing.assert_allclose(g[b], ref, rtol=1e-5, atol=1e-6)
   assert np.all(g[5] == (pr.LOWEST if mode == 'max' else 0))
+
+
+@pytest.mark.parametrize("hidden,act", [([8], 'elu'), ([8], 'leaky_relu'), ([6, 8], 'elu')])
+def test_mcconv_layer_gradients_match_finite_differences(hidden, act):
+  """monte_carlo_conv_test.py:110-219 (jacobians with respect to features, weights
+  and points; atol 1e-4, delta 1e-3) restated on the float64 layer of the oracle:
+  8 points, 4 samples, 2 clouds, radius sqrt(3) * 1.25, neighborhood and densities
+  held fixed while the points move, as in the reference's test."""
+  rng = np.random.default_rng(31)
+  n, ns, b, d, cin, cout = 8, 4, 2, 3, 8, 8
+  radius = float(np.sqrt(3) * 1.25)
+  pts = rng.uniform(0, 1, (n, d)).astype(F32); bid = np.repeat(np.arange(b), n // b).astype(np.int32)
+  smp = rng.uniform(0, 1, (ns, d)).astype(F32); sbid = np.repeat(np.arange(b), ns // b).astype(np.int32)
+  feat = rng.uniform(0, 1, (n, cin)).astype(F32)
+  grid = pr.Grid(pts, bid, b, radius)
+  neigh = pr.Neighborhood(grid, radius, smp, sbid)
+  pdf = neigh.get_pdf(bandwidth=0.2, mode=0)
+  sizes = [d] + hidden
+  ws = [rng.normal(size=(1, sizes[i], sizes[i + 1])) for i in range(len(hidden))]
+  bs = [rng.normal(size=(1, 1, sizes[i + 1])) * 0.1 for i in range(len(hidden))]
+  wf = rng.normal(size=(1, cin * hidden[-1], cout)) * 0.3
+  d_out = rng.normal(size=(ns, cout))
+
+  def loss(p=pts, s=smp, f=feat, w=ws, bb=bs, final=wf, dens=pdf):
+    return float((pr.mcconv_layer(p, s, f, neigh, dens, w, bb, final, radius, act) * d_out).sum())
+
+  g = pr.mcconv_layer_grads(pts, smp, feat, neigh, pdf, ws, bs, wf, radius, d_out, act)
+  delta = 1e-3
+
+  def fd(make):
+    """Central difference of the loss along every entry of an array."""
+    base, shape = make(None)
+    out = np.zeros(shape)
+    for idx in np.ndindex(*shape):
+      hi = loss(**make((idx, +delta))[0]); lo = loss(**make((idx, -delta))[0])
+      out[idx] = (hi - lo) / (2 * delta)
+    return out
+
+  def vary(name, arr):
+    def make(step):
+      if step is None:
+        return None, arr.shape
+      a = arr.astype(np.float64).copy()
+      a[step[0]] += step[1]
+      return {name: a}, arr.shape
+    return make
+
+  np.testing.assert_allclose(g["d_points_in"], fd(vary("p", pts)), atol=1e-4)
+  np.testing.assert_allclose(g["d_points_out"], fd(vary("s", smp)), atol=1e-4)
+  np.testing.assert_allclose(g["d_features"], fd(vary("f", feat)), atol=1e-4)
+  np.testing.assert_allclose(g["d_wf"], fd(vary("final", wf)), atol=1e-4)
+  np.testing.assert_allclose(g["d_pdf"], fd(vary("dens", pdf)), atol=2e-3, rtol=1e-3)
+  for layer in range(len(hidden)):
+    def make_w(step, layer=layer):
+      if step is None:
+        return None, ws[layer].shape
+      w2 = [w.copy() for w in ws]; w2[layer][step[0]] += step[1]
+      return {"w": w2}, ws[layer].shape
+    def make_b(step, layer=layer):
+      if step is None:
+        return None, bs[layer].shape
+      b2 = [x.copy() for x in bs]; b2[layer][step[0]] += step[1]
+      return {"bb": b2}, bs[layer].shape
+    np.testing.assert_allclose(g["d_weights"][layer], fd(make_w), atol=1e-4)
+    np.testing.assert_allclose(g["d_biases"][layer], fd(make_b), atol=1e-4)

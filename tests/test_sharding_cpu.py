@@ -90,3 +90,22 @@ def test_two_rank_allreduce_equals_single_process(tmp_path):
   # shard concatenation equals the single-process result (clouds are independent)
   np.testing.assert_allclose(full_out, ref_out, rtol=1e-5, atol=1e-5)
   np.testing.assert_allclose(full_df, ref_dfeat, rtol=1e-5, atol=1e-5)
+
+
+def test_bench_shards_concatenate_to_the_batch():
+  """bench.py --gpus N shards ONE batch by cloud: the shards of all ranks, put one
+  after the other, are the batch (batch ids re-based per shard)."""
+  import argparse
+  import bench
+  args = argparse.Namespace(clouds=8, points=64, cin=8, cout=16, hidden=8)
+  full = bench.make_inputs(args, 0)
+  for world in (1, 2, 3, 8):
+    parts = [bench.shard_inputs(full, args, r, world) for r in range(world)]
+    assert sum(c for _, c, _ in parts) == args.clouds
+    for idx, name in ((0, "points"), (2, "features"), (3, "gradients")):
+      assert np.array_equal(np.concatenate([p[0][idx] for p in parts]), full[idx]), name
+    first = 0
+    for (inp, clouds, lo) in parts:
+      assert lo == first
+      assert inp[1].min() == 0 and inp[1].max() == clouds - 1
+      first += len(inp[0])
