@@ -30,6 +30,10 @@ using namespace bptc;
 
 namespace {
 
+#ifdef TFGPC_TC_TIMING
+__device__ long long tt_array[160 * 5 * 8];
+#endif
+
 constexpr int kG = gp::kG;
 constexpr int kProdWarps = 8;
 constexpr int kMmaWarp = 8;
@@ -171,12 +175,16 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
         pr_n = __ldg(reinterpret_cast<const int2*>(rows_pair + r0 + brow) + (lane & 1));
     };
     if (walk.valid) prefetch();
+    TT_DECL
     while (walk.valid) {
+      TT_MARK(tp0)
       const int left = left_n;
       const int ids[8] = {ida_n.x, ida_n.y, ida_n.z, ida_n.w, idb_n.x, idb_n.y, idb_n.z, idb_n.w};
       const int2 pr = pr_n;
       walk.advance();
       if (walk.valid) prefetch();
+      TT_MARK(tp1)
+      TT_ADD(2, tp1 - tp0);
       // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  The MMAs read
       // whole steps of 16 rows, which are exactly one warp's rows: a warp with at
       // least one row zero-fills the rest of its 16, a warp without rows copies
@@ -186,8 +194,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         const uint32_t unit = (2 * item + kb) % kUnits;
-        mbar_wait(smem_u32(&bars->f_empty[unit]), (((2 * item + kb) / kUnits) & 1) ^ 1, abort_flag,
-                  err_flag);
+        TT_WAIT(0, smem_u32(&bars->f_empty[unit]), (((2 * item + kb) / kUnits) & 1) ^ 1);
         const uint32_t base = smem_u32(f_ring + (size_t)unit * kUnitBytes) + f_dst_lane;
         const int nv = left - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
@@ -200,10 +207,12 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
                      ::"r"(smem_u32(&bars->f_full[unit])) : "memory");
       }
+      TT_MARK(tp2)
+      TT_ADD(3, tp2 - tp1);
       // ---- Bx: the basis rows of the plan's pairs, zeros where there is none
       {
         const uint32_t stage = item & 1;
-        mbar_wait(smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
+        TT_WAIT(1, smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1);
         const int r = row_base + brow;
         const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + r * 128;
         if (left > 0) {
@@ -221,19 +230,26 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
                      ::"r"(smem_u32(&bars->bx_full[stage])) : "memory");
       }
       ++item;
+      TT_MARK(tp3)
+      TT_ADD(4, tp3 - tp2);
+      TT_ADD(6, 1);
     }
+#ifdef TFGPC_TC_TIMING
+    if (warp == 0 && lane == 0) TT_STORE(0);
+#endif
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t item = 0, tile_i = 0;
       UTile next = load_utile(group_begin, group_rows, groups, blockIdx.x);
+      TT_DECL
       for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
         const UTile t = next;
         next = load_utile(group_begin, group_rows, groups, g + gridDim.x);
         const int nb = t.blocks();
         if (nb == 0) continue;
         const uint32_t abuf = tile_i & 1;
-        mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((tile_i >> 1) & 1) ^ 1, abort_flag, err_flag);
+        TT_WAIT(0, smem_u32(&bars->acc_empty[abuf]), ((tile_i >> 1) & 1) ^ 1);
         tc_fence_after();
         const uint32_t d = tmem_base + abuf * 64;
         uint32_t accumulate = 0;
@@ -241,34 +257,44 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
           const uint32_t u0 = (2 * item) % kUnits;          // even: u0 + 1 is the next unit in memory
           const uint32_t fph = ((2 * item) / kUnits) & 1;
           const uint32_t stage = item & 1;
-          mbar_wait(smem_u32(&bars->f_full[u0]), fph, abort_flag, err_flag);
-          mbar_wait(smem_u32(&bars->f_full[u0 + 1]), fph, abort_flag, err_flag);
-          mbar_wait(smem_u32(&bars->bx_full[stage]), (item >> 1) & 1, abort_flag, err_flag);
+          TT_WAIT(1, smem_u32(&bars->f_full[u0]), fph);
+          TT_WAIT(1, smem_u32(&bars->f_full[u0 + 1]), fph);
+          TT_WAIT(2, smem_u32(&bars->bx_full[stage]), (item >> 1) & 1);
+          TT_MARK(tm0)
           fence_proxy_async();   // the copied rows were written through the generic proxy
           tc_fence_after();
+          TT_MARK(tm1)
+          TT_ADD(3, tm1 - tm0);
           const uint32_t f_hi = smem_u32(f_ring + (size_t)u0 * kUnitBytes), f_mid = f_hi + kPart;
           const uint32_t bx_hi = smem_u32(bx + (size_t)stage * kBxBytes), bx_mid = bx_hi + kPart;
           const int steps = (min(kRows, t.rows - b * kRows) + 15) >> 4;
+          // both operands MN-major: 8 rows (reduction index) per 1024-byte atom, a
+          // step of 16 rows is 2048 bytes (128 in the descriptor's 16-byte units);
+          // the two 64-channel blocks of A lie one ring unit apart
+          uint64_t da_hi = make_desc(f_hi, kUnitBytes, 1024);
+          uint64_t da_mid = make_desc(f_mid, kUnitBytes, 1024);
+          uint64_t db_hi = make_desc(bx_hi, 8192, 1024);
+          uint64_t db_mid = make_desc(bx_mid, 8192, 1024);
           for (int kk = 0; kk < steps; ++kk) {
-            // both operands MN-major: 8 rows (reduction index) per 1024-byte atom, a
-            // step of 16 rows is 2048 bytes; the two 64-channel blocks of A lie one
-            // ring unit apart
-            const uint64_t da_hi = make_desc(f_hi + kk * 2048, kUnitBytes, 1024);
-            const uint64_t da_mid = make_desc(f_mid + kk * 2048, kUnitBytes, 1024);
-            const uint64_t db_hi = make_desc(bx_hi + kk * 2048, 8192, 1024);
-            const uint64_t db_mid = make_desc(bx_mid + kk * 2048, 8192, 1024);
             umma_bf16(d, da_hi, db_mid, idesc, accumulate);
             umma_bf16(d, da_mid, db_hi, idesc, 1u);
             umma_bf16(d, da_hi, db_hi, idesc, 1u);
             accumulate = 1u;
+            da_hi += 128; da_mid += 128; db_hi += 128; db_mid += 128;
           }
+          TT_MARK(tm2)
+          TT_ADD(4, tm2 - tm1);
           umma_commit(smem_u32(&bars->f_empty[u0]));
           umma_commit(smem_u32(&bars->f_empty[u0 + 1]));
           umma_commit(smem_u32(&bars->bx_empty[stage]));
+          TT_MARK(tm3)
+          TT_ADD(5, tm3 - tm2);
         }
         umma_commit(smem_u32(&bars->acc_full[abuf]));
         ++tile_i;
       }
+      TT_ADD(6, item);
+      TT_STORE(1);
     }
   } else {
     // -------------------------------------------------------------- epilogue
@@ -281,6 +307,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
     const int c = quarter * 32 + lane;
     uint32_t tile_i = 0;
     UTile next = load_utile(group_begin, group_rows, groups, blockIdx.x);
+    TT_DECL
     for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
       const UTile t = next;
       next = load_utile(group_begin, group_rows, groups, g + gridDim.x);
@@ -299,7 +326,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
         continue;
       }
       const uint32_t abuf = tile_i & 1;
-      mbar_wait(smem_u32(&bars->acc_full[abuf]), (tile_i >> 1) & 1, abort_flag, err_flag);
+      TT_WAIT(0, smem_u32(&bars->acc_full[abuf]), (tile_i >> 1) & 1);
       tc_fence_after();
       const bool ok = !*abort_flag;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + abuf * 64;
@@ -324,6 +351,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[abuf]));
       ++tile_i;
     }
+#ifdef TFGPC_TC_TIMING
+    if (warp == kEpiWarp0 && lane == 0) { TT_ADD(6, tile_i); TT_STORE(4); }
+#endif
   }
   tc_fence_before();
   __syncthreads();
@@ -358,5 +388,12 @@ int basis_proj_fwd_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* plan,
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
+
+#ifdef TFGPC_TC_TIMING
+// Debug builds only: copies the timing words of the last launch to the host.
+extern "C" int tfgpc_debug_fwd_timing(long long* out, int count) {
+  return (int)cudaMemcpyFromSymbol(out, tt_array, sizeof(long long) * (size_t)count);
+}
+#endif
 
 }  // namespace tfgpc

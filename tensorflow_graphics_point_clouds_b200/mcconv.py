@@ -338,10 +338,10 @@ class MCConv:
               bandwidth=0.2, keep_for_backward=True):
     neigh = neighborhood or self.build_neighborhood(point_cloud_in, point_cloud_out, radius)
     pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
-    w1, b1 = self._flat_kernel_weights()
     ns = point_cloud_out._points.shape[0]
     p_in, p_out, ids = point_cloud_in._points, point_cloud_out._points, neigh._original_neigh_ids
     one_layer = len(self.kernel_weights) == 1
+    w1, b1 = self._flat_kernel_weights() if one_layer else (None, None)
     # wide layers run on a group plan (see group_plan)
     grouped = (one_layer and self.grouped and neigh._neighbors.shape[0] > 0 and
                self.cout >= 128 and
