@@ -339,7 +339,7 @@ class LayerRun:
     cloud = pc.PointCloud(x["pts"], x["bid"], self.clouds,
                           num_cells_reduce=tdist.allreduce_max_ if self.world > 1 else None)
     out = self.layer.forward(x["feat"], cloud, cloud, self.args.radius)
-    self.pairs = int(self.layer._saved[0]._neighbors.shape[0])
+    self.pairs = int(self.layer._saved[0].num_pairs)
     dfeat, dw1, db1, dwf = self.layer.backward(x["d_out"])
     if allreduce:
       tdist.allreduce_sum_([dwf, dw1, db1])   # the path's only exchange step

@@ -167,6 +167,29 @@ int tfgpc_original_neighbor_ids(void* stream, int64_t M,
                                 const float* pdf_by_original, int32_t* ids_out,
                                 float* pdf_out);
 
+/* ---- FindNeighbors fill pass with original ids and densities --------------
+ * tfgpc_find_neighbors_fill_ordered (sample_order may be NULL) that, in the same
+ * pass, also writes what pylib computes from the neighbor list afterwards:
+ * ids_out [M,2] = (sorted_indices[neighbors[m].x], neighbors[m].y), the pairs
+ * with the neighbor's index in the unsorted point order (pylib/pc/
+ * Neighborhood.py:246-250), and sample_pdf_out [ns], ComputePdf
+ * (compute_pdf_kernels.cu.cc:107-128) at every sample over its neighbors
+ * (inv_bandwidth [D], pdf_mode 0 / 1 as in tfgpc_compute_pdf, mode 1 with the
+ * number of points n).  For samples that are the grid's own points this is the
+ * density of tfgpc_compute_pdf_at_samples without walking the lists again;
+ * sample_pdf_out may be NULL (ids only), which is the cheaper combination: the
+ * densities take less time in a pass of their own over the finished lists. */
+int tfgpc_find_neighbors_fill_fused(
+    void* stream, int D, int64_t ns, const float* samples,
+    const int32_t* samples_batch_ids, const int32_t* sample_order, int64_t n,
+    const float* points, const int64_t* point_keys, const int32_t* ds,
+    int64_t batch_size, const int32_t* num_cells,
+    const float* scaled_aabb_min, const float* inv_cell_sizes,
+    const float* inv_radii, int max_neighs, const int32_t* ranges,
+    int64_t total, const int32_t* sorted_indices, const float* inv_bandwidth,
+    int pdf_mode, int32_t* neigh_out, int32_t* ids_out,
+    float* sample_pdf_out);
+
 /* ---- FindNeighbors count pass with built-in scratch ------------------------
  * No counterpart in the reference.  Same inputs, outputs and blocking
  * behaviour as tfgpc_find_neighbors_count, but without the ws / ws_bytes
@@ -414,17 +437,21 @@ int tfgpc_mcconv_backward_grouped(void* stream, int K, int C, int Cout,
  * [D,K] row-major (column k = mlp * hidden + h of the reference's
  * [num_mlps, D, hidden] weights), b1 [K].  activation 0 = leaky ReLU with slope
  * alpha (0.2 is tf.nn.leaky_relu's default, 0 gives ReLU), 1 = ELU.
+ * pdf_by_neighbor != 0: pdf is not the per-pair array but a table with one
+ * density per point of points_in, read at nbr.x (what pylib gathers into the
+ * per-pair array at Neighborhood.py:287); the same flag on every entry below.
  * _grads: basis_grads [M,K] -> dw1_out [D,K], db1_out [K] (overwritten). */
 int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M,
                        const float* points_in, const float* points_out,
                        const int32_t* neighbors, const float* pdf,
                        const float* w1, const float* b1, float inv_radius,
-                       int activation, float alpha, float* basis_out);
+                       int activation, float alpha, int pdf_by_neighbor,
+                       float* basis_out);
 int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
                              const float* points_in, const float* points_out,
                              const int32_t* neighbors, const float* pdf,
                              const float* w1, const float* b1, float inv_radius,
-                             int activation, float alpha,
+                             int activation, float alpha, int pdf_by_neighbor,
                              const float* basis_grads, float* dw1_out,
                              float* db1_out);
 /* tfgpc_kernel_basis that also writes every basis row as the bf16 pair the
@@ -436,7 +463,8 @@ int tfgpc_kernel_basis_split(void* stream, int D, int K, int64_t M,
                              const int32_t* neighbors, const float* pdf,
                              const float* w1, const float* b1,
                              float inv_radius, int activation, float alpha,
-                             float* basis_out, void* basis_pair_out);
+                             int pdf_by_neighbor, float* basis_out,
+                             void* basis_pair_out);
 
 /* ---- MCConv kernel MLP, general form ---------------------------------------
  * Replaces the TensorFlow ops of pylib/pc/layers/MCConv.py:163-171 and :264-269
@@ -461,14 +489,14 @@ int tfgpc_kernel_mlp_basis(void* stream, int D, int num_mlps, int num_layers,
                            const int32_t* neighbors, const float* pdf,
                            const float* weights, const float* biases,
                            float inv_radius, int activation, float alpha,
-                           float* basis_out);
+                           int pdf_by_neighbor, float* basis_out);
 int tfgpc_kernel_mlp_grads(void* stream, int D, int num_mlps, int num_layers,
                            const int32_t* layer_sizes, int64_t M, int64_t n_in,
                            int64_t ns, const float* points_in,
                            const float* points_out, const int32_t* neighbors,
                            const float* pdf, const float* weights,
                            const float* biases, float inv_radius,
-                           int activation, float alpha,
+                           int activation, float alpha, int pdf_by_neighbor,
                            const float* basis_grads, float* dweights_out,
                            float* dbiases_out, float* dpoints_in_out,
                            float* dpoints_out_out, float* dpdf_out);

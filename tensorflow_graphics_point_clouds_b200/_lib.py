@@ -40,6 +40,7 @@ SYMBOLS = {
     "tfgpc_find_neighbors_fill": c_int,
     "tfgpc_find_neighbors_count_ordered": c_int,
     "tfgpc_find_neighbors_fill_ordered": c_int,
+    "tfgpc_find_neighbors_fill_fused": c_int,
     "tfgpc_original_neighbor_ids": c_int,
     "tfgpc_find_neighbors_static_max_samples": c_i64,
     "tfgpc_find_neighbors_count_static": c_int,

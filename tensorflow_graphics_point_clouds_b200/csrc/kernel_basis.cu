@@ -59,7 +59,7 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
                     const int2* __restrict__ neigh, const float* __restrict__ pdf,
                     const float* __restrict__ w1, const float* __restrict__ b1, float inv_radius,
                     int act, float alpha, float* __restrict__ basis,
-                    __nv_bfloat16* __restrict__ pair) {
+                    __nv_bfloat16* __restrict__ pair, int pdf_by_nbr) {
   __shared__ float w_s[D * K + K];
   for (int i = threadIdx.x; i < D * K + K; i += kKbThreads)
     w_s[i] = i < D * K ? __ldg(w1 + i) : __ldg(b1 + i - D * K);
@@ -69,7 +69,7 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
     const int2 nb = __ldg(neigh + m);
     float diff[D];
     pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
-    const float inv_pdf = 1.0f / __ldg(pdf + m);
+    const float inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
     float* dst = basis + m * K;
     uint4 pr[K / 4];   // hi chunks, then mid chunks, of the bf16 pair
 #pragma unroll
@@ -118,7 +118,7 @@ kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
                           const float* __restrict__ pdf, const float* __restrict__ w1,
                           const float* __restrict__ b1, float inv_radius, int act, float alpha,
                           const float* __restrict__ dbasis, float* __restrict__ dw1,
-                          float* __restrict__ db1) {
+                          float* __restrict__ db1, int pdf_by_nbr) {
   constexpr int KT = K < kKTile ? K : kKTile;
   __shared__ float w_s[D * K + K];
   __shared__ float red[(D + 1) * KT];
@@ -139,7 +139,7 @@ kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
     const int2 nb = __ldg(neigh + m);
     float diff[D];
     pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
-    const float inv_pdf = 1.0f / __ldg(pdf + m);
+    const float inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
     const float* src = dbasis + m * K + k0;
 #pragma unroll
     for (int q = 0; q < KT / 8; ++q) {
@@ -304,7 +304,8 @@ using namespace tfgpc;
 static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float* points_in,
                              const float* points_out, const int32_t* neighbors, const float* pdf,
                              const float* w1, const float* b1, float inv_radius, int activation,
-                             float alpha, float* basis_out, __nv_bfloat16* pair_out) {
+                             float alpha, float* basis_out, __nv_bfloat16* pair_out,
+                             int pdf_by_nbr) {
   int rc = check_kb_args("KernelBasis", D, K, M, activation);
   if (rc) return rc;
   if (M == 0) return TFGPC_OK;
@@ -318,11 +319,11 @@ static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float*
   if ((uintptr_t)basis_out % 32 == 0) {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_out, pair_out)));
+        alpha, basis_out, pair_out, pdf_by_nbr)));
   } else {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_out, pair_out)));
+        alpha, basis_out, pair_out, pdf_by_nbr)));
   }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
@@ -332,29 +333,30 @@ extern "C" int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M, const f
                                   const float* points_out, const int32_t* neighbors,
                                   const float* pdf, const float* w1, const float* b1,
                                   float inv_radius, int activation, float alpha,
-                                  float* basis_out) {
+                                  int pdf_by_neighbor, float* basis_out) {
   return kernel_basis_impl(stream, D, K, M, points_in, points_out, neighbors, pdf, w1, b1,
-                           inv_radius, activation, alpha, basis_out, nullptr);
+                           inv_radius, activation, alpha, basis_out, nullptr, pdf_by_neighbor);
 }
 
 extern "C" int tfgpc_kernel_basis_split(void* stream, int D, int K, int64_t M,
                                         const float* points_in, const float* points_out,
                                         const int32_t* neighbors, const float* pdf,
                                         const float* w1, const float* b1, float inv_radius,
-                                        int activation, float alpha, float* basis_out,
-                                        void* basis_pair_out) {
+                                        int activation, float alpha, int pdf_by_neighbor,
+                                        float* basis_out, void* basis_pair_out) {
   TFGPC_REQUIRE(M == 0 || basis_pair_out, "KernelBasis got a null pointer");
   return kernel_basis_impl(stream, D, K, M, points_in, points_out, neighbors, pdf, w1, b1,
                            inv_radius, activation, alpha, basis_out,
-                           (__nv_bfloat16*)basis_pair_out);
+                           (__nv_bfloat16*)basis_pair_out, pdf_by_neighbor);
 }
 
 extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
                                         const float* points_in, const float* points_out,
                                         const int32_t* neighbors, const float* pdf,
                                         const float* w1, const float* b1, float inv_radius,
-                                        int activation, float alpha, const float* basis_grads,
-                                        float* dw1_out, float* db1_out) {
+                                        int activation, float alpha, int pdf_by_neighbor,
+                                        const float* basis_grads, float* dw1_out,
+                                        float* db1_out) {
   int rc = check_kb_args("KernelBasisGrads", D, K, M, activation);
   if (rc) return rc;
   TFGPC_REQUIRE(dw1_out && db1_out, "KernelBasisGrads got a null pointer");
@@ -372,11 +374,11 @@ extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
   if ((uintptr_t)basis_grads % 32 == 0) {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_grads_kernel<kD, kK, true><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_grads, dw1_out, db1_out)));
+        alpha, basis_grads, dw1_out, db1_out, pdf_by_neighbor)));
   } else {
     TFGPC_DIM_SWITCH(D, TFGPC_K_SWITCH(K, kernel_basis_grads_kernel<kD, kK, false><<<grid, kKbThreads, 0, st>>>(
         M, points_in, points_out, (const int2*)neighbors, pdf, w1, b1, inv_radius, activation,
-        alpha, basis_grads, dw1_out, db1_out)));
+        alpha, basis_grads, dw1_out, db1_out, pdf_by_neighbor)));
   }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;

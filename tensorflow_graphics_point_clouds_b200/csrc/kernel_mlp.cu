@@ -59,7 +59,7 @@ kernel_mlp_basis_kernel(MlpShape s, int64_t M, const float* __restrict__ p_in,
                         const float* __restrict__ p_out, const int2* __restrict__ neigh,
                         const float* __restrict__ pdf, const float* __restrict__ weights,
                         const float* __restrict__ biases, float inv_radius, int act, float alpha,
-                        float* __restrict__ basis) {
+                        int pdf_by_nbr, float* __restrict__ basis) {
   extern __shared__ float par[];
   load_params(s, weights, biases, par);
   __syncthreads();
@@ -71,7 +71,7 @@ kernel_mlp_basis_kernel(MlpShape s, int64_t M, const float* __restrict__ p_in,
     for (int d = 0; d < s.D; ++d)
       diff[d] = (__ldg(p_in + (int64_t)nb.x * s.D + d) - __ldg(p_out + (int64_t)nb.y * s.D + d)) *
                 inv_radius;
-    const float inv_pdf = 1.0f / __ldg(pdf + m);
+    const float inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
     for (int g = 0; g < s.G; ++g) {
       float a[kMaxWidth], b[kMaxWidth];
       for (int d = 0; d < s.D; ++d) a[d] = diff[d];
@@ -97,7 +97,8 @@ kernel_mlp_grads_kernel(MlpShape s, int64_t M, const float* __restrict__ p_in,
                         const float* __restrict__ p_out, const int2* __restrict__ neigh,
                         const float* __restrict__ pdf, const float* __restrict__ weights,
                         const float* __restrict__ biases, float inv_radius, int act, float alpha,
-                        const float* __restrict__ dbasis, float* __restrict__ dweights,
+                        int pdf_by_nbr, const float* __restrict__ dbasis,
+                        float* __restrict__ dweights,
                         float* __restrict__ dbiases, float* __restrict__ dp_in,
                         float* __restrict__ dp_out, float* __restrict__ dpdf) {
   extern __shared__ float smem[];
@@ -119,7 +120,7 @@ kernel_mlp_grads_kernel(MlpShape s, int64_t M, const float* __restrict__ p_in,
     float inv_pdf = 0.0f, dpdf_m = 0.0f;
     if (live) {
       nb = __ldg(neigh + m);
-      inv_pdf = 1.0f / __ldg(pdf + m);
+      inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
     }
     for (int d = 0; d < s.D; ++d) {
       diff[d] = live ? (__ldg(p_in + (int64_t)nb.x * s.D + d) - __ldg(p_out + (int64_t)nb.y * s.D + d)) *
@@ -227,7 +228,8 @@ extern "C" int tfgpc_kernel_mlp_basis(void* stream, int D, int num_mlps, int num
                                       const float* points_in, const float* points_out,
                                       const int32_t* neighbors, const float* pdf,
                                       const float* weights, const float* biases, float inv_radius,
-                                      int activation, float alpha, float* basis_out) {
+                                      int activation, float alpha, int pdf_by_neighbor,
+                                      float* basis_out) {
   MlpShape s;
   int rc = make_shape("KernelMlpBasis", D, num_mlps, num_layers, layer_sizes, &s);
   if (rc) return rc;
@@ -242,7 +244,7 @@ extern "C" int tfgpc_kernel_mlp_basis(void* stream, int D, int num_mlps, int num
   ProfScope prof(st, "kernel_mlp_basis");
   kernel_mlp_basis_kernel<<<grid, kMlpThreads, sizeof(float) * (size_t)s.params, st>>>(
       s, M, points_in, points_out, (const int2*)neighbors, pdf, weights, biases, inv_radius,
-      activation, alpha, basis_out);
+      activation, alpha, pdf_by_neighbor, basis_out);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
@@ -252,8 +254,9 @@ extern "C" int tfgpc_kernel_mlp_grads(void* stream, int D, int num_mlps, int num
                                       int64_t ns, const float* points_in, const float* points_out,
                                       const int32_t* neighbors, const float* pdf,
                                       const float* weights, const float* biases, float inv_radius,
-                                      int activation, float alpha, const float* basis_grads,
-                                      float* dweights_out, float* dbiases_out,
+                                      int activation, float alpha, int pdf_by_neighbor,
+                                      const float* basis_grads, float* dweights_out,
+                                      float* dbiases_out,
                                       float* dpoints_in_out, float* dpoints_out_out,
                                       float* dpdf_out) {
   MlpShape s;
@@ -284,8 +287,8 @@ extern "C" int tfgpc_kernel_mlp_grads(void* stream, int D, int num_mlps, int num
   ProfScope prof(st, "kernel_mlp_grads");
   kernel_mlp_grads_kernel<<<grid, kMlpThreads, smem, st>>>(
       s, M, points_in, points_out, (const int2*)neighbors, pdf, weights, biases, inv_radius,
-      activation, alpha, basis_grads, dweights_out, dbiases_out, dpoints_in_out, dpoints_out_out,
-      dpdf_out);
+      activation, alpha, pdf_by_neighbor, basis_grads, dweights_out, dbiases_out, dpoints_in_out,
+      dpoints_out_out, dpdf_out);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }

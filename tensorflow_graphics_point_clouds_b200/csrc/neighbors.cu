@@ -89,7 +89,25 @@ __device__ __forceinline__ bool within_radius(const float* s, const float* __res
   return d2 < 1.0f;
 }
 
-template <int D, bool FILL>
+// What the fused fill pass adds to the neighbor list: the same pairs with the
+// neighbor's index in the UNSORTED point order (Neighborhood.py:246-250) and the
+// (optionally) the Gaussian density estimate at every sample over its neighbors,
+// i.e. ComputePdf (compute_pdf_kernels.cu.cc:107-128) evaluated where the
+// candidate's coordinates are already in registers.  The ids cost two
+// instructions per hit; the densities cost more than a separate pass over the
+// finished lists does (here one lane in six holds a hit, there every lane works),
+// so the callers of this library ask for the ids only.
+struct FillExtras {
+  const int32_t* sorted_indices;   // [n] original index of sorted point j
+  int2* ids_out;                   // [M] (original neighbor index, sample)
+  const float* inv_bw;             // [D]
+  int pdf_mode;                    // 0: inv_bw as given, 1: sqrt(n_bw)
+  int64_t n_bw;
+  float* sample_pdf;               // [ns]
+};
+
+// MODE 0: count, 1: fill, 2: fill with FillExtras
+template <int D, int MODE>
 __global__ void __launch_bounds__(kFnThreads)
 find_neighbors_kernel(int64_t ns, const int32_t* __restrict__ order,
                       const float* __restrict__ samples,
@@ -99,13 +117,20 @@ find_neighbors_kernel(int64_t ns, const int32_t* __restrict__ order,
                       const float* __restrict__ smin_all, const float* __restrict__ inv_cell,
                       const float* __restrict__ inv_radii, int max_neighs,
                       int32_t* __restrict__ counts, const int32_t* __restrict__ ranges,
-                      int2* __restrict__ neigh_out) {
+                      int2* __restrict__ neigh_out, FillExtras ex) {
+  constexpr bool FILL = MODE != 0;
   constexpr int kOff = num_offsets<D>();
   constexpr int kChunks = (kOff + 31) / 32;
   const Grid<D> g = load_grid<D>(num_cells, inv_cell);
-  float inv_r[D];
+  float inv_r[D], bw[D];
 #pragma unroll
-  for (int d = 0; d < D; ++d) inv_r[d] = __ldg(inv_radii + d);
+  for (int d = 0; d < D; ++d) {
+    inv_r[d] = __ldg(inv_radii + d);
+    bw[d] = 0.0f;
+    // (inv_bw is only given, and only read, when densities are asked for)
+    if (MODE == 2 && ex.sample_pdf)
+      bw[d] = ex.pdf_mode == 1 ? sqrtf((float)ex.n_bw) : __ldg(ex.inv_bw + d);
+  }
   const int lane = lane_id();
   const unsigned lt_mask = (1u << lane) - 1u;
   const int64_t warps = ((int64_t)gridDim.x * kFnThreads) >> 5;
@@ -147,6 +172,7 @@ find_neighbors_kernel(int64_t ns, const int32_t* __restrict__ order,
       for (int d = 0; d < D; ++d) prev_cell[d] = cell[d];
     }
     int count = 0;
+    float density = 0.0f;
     int64_t out_base = 0;
     if (FILL) out_base = s ? (int64_t)__ldg(ranges + s - 1) : 0;
     const int limit = max_neighs > 0 ? max_neighs : INT32_MAX;
@@ -162,13 +188,30 @@ find_neighbors_kernel(int64_t ns, const int32_t* __restrict__ order,
           const unsigned m = __ballot_sync(0xffffffffu, hit);
           if (FILL && hit) {
             int pos = count + __popc(m & lt_mask);
-            if (pos < limit) neigh_out[out_base + pos] = make_int2(j, (int)s);
+            if (pos < limit) {
+              neigh_out[out_base + pos] = make_int2(j, (int)s);
+              if (MODE == 2)
+                ex.ids_out[out_base + pos] = make_int2(__ldg(ex.sorted_indices + j), (int)s);
+              if (MODE == 2 && ex.sample_pdf) {
+                float local = 1.0f;
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                  const float t = (__ldg(pts + (int64_t)j * D + d) - sp[d]) * bw[d] * inv_r[d];
+                  local *= bw[d] * expf(t * t * (-0.5f)) * 0.39894228f;
+                }
+                density += local;
+              }
+            }
           }
           count += __popc(m);
         }
       }
     }
     if (!FILL && lane == 0) counts[s] = min(count, limit);
+    if (MODE == 2 && ex.sample_pdf) {
+      density = warp_sum(density);
+      if (lane == 0) ex.sample_pdf[s] = density;
+    }
   }
 }
 
@@ -217,10 +260,10 @@ static int find_neighbors_count_impl(bool mapped_read, const int32_t* order,
   if (order) TFGPC_CUDA(cudaMemsetAsync(ranges_out, 0, sizeof(int32_t) * (size_t)ns, st));
   {
   ProfScope prof(st, "find_neighbors_count");
-  TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, false><<<grid, kFnThreads, 0, st>>>(
+  TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, 0><<<grid, kFnThreads, 0, st>>>(
       ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
       num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, ranges_out, nullptr,
-      nullptr));
+      nullptr, FillExtras{}));
   }
   TFGPC_LAUNCH_CHECK();
   rc = inclusive_scan_i32(st, ranges_out, ranges_out, ns, block_sums, total_dev);
@@ -259,24 +302,58 @@ static int find_neighbors_fill_impl(const int32_t* order,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
     const float* inv_cell_sizes, const float* inv_radii, int max_neighs, const int32_t* ranges,
-    int64_t total, int32_t* neigh_out) {
+    int64_t total, int32_t* neigh_out, const FillExtras* extras = nullptr) {
   int rc = check_fn_args(D, ns, n, batch_size, max_neighs);
   if (rc) return rc;
   TFGPC_REQUIRE(total >= 0 && total <= (int64_t)INT32_MAX, "FindNeighbors expects 0 <= total < 2^31");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (extras && extras->sample_pdf && ns > 0 && total == 0)   // no pair at all: every density is zero
+    TFGPC_CUDA(cudaMemsetAsync(extras->sample_pdf, 0, sizeof(float) * (size_t)ns, st));
   if (ns == 0 || total == 0) return TFGPC_OK;
   TFGPC_REQUIRE(samples && samples_batch_ids && points && point_keys && ds && num_cells &&
                 scaled_aabb_min && inv_cell_sizes && inv_radii && ranges && neigh_out,
                 "FindNeighbors got a null pointer");
-  cudaStream_t st = (cudaStream_t)stream;
   unsigned grid = min(blocks_for((ns + kFnSpan - 1) / kFnSpan, kFnThreads / 32),
                       (unsigned)(sm_count() * 32));
-  ProfScope prof(st, "find_neighbors_fill");
-  TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, true><<<grid, kFnThreads, 0, st>>>(
-      ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
-      num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,
-      (int2*)neigh_out));
+  if (extras) {
+    // samples the order leaves unvisited keep a density of zero
+    if (order && extras->sample_pdf)
+      TFGPC_CUDA(cudaMemsetAsync(extras->sample_pdf, 0, sizeof(float) * (size_t)ns, st));
+    ProfScope prof(st, "find_neighbors_fill_fused");
+    TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, 2><<<grid, kFnThreads, 0, st>>>(
+        ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+        num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,
+        (int2*)neigh_out, *extras));
+  } else {
+    ProfScope prof(st, "find_neighbors_fill");
+    TFGPC_DIM_SWITCH(D, find_neighbors_kernel<kD, 1><<<grid, kFnThreads, 0, st>>>(
+        ns, order, samples, samples_batch_ids, points, point_keys, (const int2*)ds, (int)batch_size,
+        num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs, nullptr, ranges,
+        (int2*)neigh_out, FillExtras{}));
+  }
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
+}
+
+// The fill pass that also writes the neighbor ids in the unsorted point order and
+// the density estimate at every sample (see FillExtras).
+extern "C" int tfgpc_find_neighbors_fill_fused(
+    void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
+    const int32_t* sample_order, int64_t n, const float* points, const int64_t* point_keys,
+    const int32_t* ds, int64_t batch_size, const int32_t* num_cells,
+    const float* scaled_aabb_min, const float* inv_cell_sizes, const float* inv_radii,
+    int max_neighs, const int32_t* ranges, int64_t total, const int32_t* sorted_indices,
+    const float* inv_bandwidth, int pdf_mode, int32_t* neigh_out, int32_t* ids_out,
+    float* sample_pdf_out) {
+  TFGPC_REQUIRE(pdf_mode == 0 || pdf_mode == 1, "FindNeighbors expects density mode 0 or 1");
+  TFGPC_REQUIRE(total == 0 || (sorted_indices && ids_out &&
+                               (!sample_pdf_out || pdf_mode == 1 || inv_bandwidth)),
+                "FindNeighbors got a null pointer");
+  FillExtras ex{sorted_indices, (int2*)ids_out, inv_bandwidth, pdf_mode, n, sample_pdf_out};
+  return find_neighbors_fill_impl(sample_order, stream, D, ns, samples, samples_batch_ids, n,
+                                  points, point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                  inv_cell_sizes, inv_radii, max_neighs, ranges, total, neigh_out,
+                                  &ex);
 }
 
 extern "C" int tfgpc_find_neighbors_fill(

@@ -110,12 +110,19 @@ def build_grid_ds(keys, num_cells_gpu, num_cells_cpu, batch_size):
   return ds
 
 
-def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, num_cells,
-                   scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs=0, sample_order=None):
-  """FindNeighbors (find_neighbors/cc/ops/find_neighbors_ops.cpp:42-61).
-  Returns (samples_neigh_indices [Ns], neigh_indices [M, 2]).  sample_order, a
-  permutation of the sample indices, only sets the sequence the samples are
-  worked on in (same result; faster when it keeps spatial neighbors together)."""
+class NeighborCount:
+  """Result of the count pass of FindNeighbors: the ranges [Ns], the number of
+  pairs, and the checked arguments the fill pass needs again."""
+
+  def __init__(self, ranges, total, args, order, dims):
+    self.ranges, self.total, self.args, self.order, self.dims = ranges, total, args, order, dims
+
+
+def find_neighbors_count(samples, samples_batch_ids, points, point_keys, grid_acc_ds, num_cells,
+                         scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs=0,
+                         sample_order=None):
+  """First half of FindNeighbors (find_neighbors_ops.cpp:158-187): ranges and the
+  number of pairs.  Blocks until the count is on the host."""
   samples, points = _f32(samples), _f32(points)
   sbid, nc = _i32(samples_batch_ids), _i32(num_cells)
   keys, ds = point_keys.contiguous(), _i32(grid_acc_ds)
@@ -138,24 +145,70 @@ def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, 
   nbytes = _lib.lib().tfgpc_find_neighbors_workspace_bytes(c_i64(ns))
   ws = _workspace(nbytes, dev)
   total = c_i64(0)
-  head = (_stream(), c_int(d), c_i64(ns), ptr(samples), ptr(sbid))
-  tail = (c_i64(n), ptr(points), ptr(keys), ptr(ds), c_i64(ds.shape[0]), ptr(nc), ptr(smin),
-          ptr(inv_c), ptr(inv_r), c_int(int(max_neighs)))
-  lib = _lib.lib()
-  if sample_order is None:
-    count, fill, common = lib.tfgpc_find_neighbors_count, lib.tfgpc_find_neighbors_fill, head + tail
-  else:
+  order = None
+  if sample_order is not None:
     order = _i32(sample_order)
     _dev_check(samples, order)
     if order.shape[0] != ns:
       raise _lib.TfgpcError(1, "FindNeighborsOp expects one entry of the order per sample.")
-    count, fill = lib.tfgpc_find_neighbors_count_ordered, lib.tfgpc_find_neighbors_fill_ordered
-    common = head + (ptr(order),) + tail
-  _lib.check(count(*common, ptr(ranges), ptr(ws), c_sz(nbytes), ctypes.byref(total)))
-  m = int(total.value)
+  # (tensors are kept alive by the object: the pointers below are reused by the fill pass)
+  keep = (samples, sbid, points, keys, ds, nc, smin, inv_c, inv_r)
+  head = (c_int(d), c_i64(ns), ptr(samples), ptr(sbid))
+  tail = (c_i64(n), ptr(points), ptr(keys), ptr(ds), c_i64(ds.shape[0]), ptr(nc), ptr(smin),
+          ptr(inv_c), ptr(inv_r), c_int(int(max_neighs)))
+  lib = _lib.lib()
+  if order is None:
+    _lib.check(lib.tfgpc_find_neighbors_count(_stream(), *head, *tail, ptr(ranges), ptr(ws),
+                                              c_sz(nbytes), ctypes.byref(total)))
+  else:
+    _lib.check(lib.tfgpc_find_neighbors_count_ordered(_stream(), *head, ptr(order), *tail,
+                                                      ptr(ranges), ptr(ws), c_sz(nbytes),
+                                                      ctypes.byref(total)))
+  return NeighborCount(ranges, int(total.value), (head, tail, keep), order, d)
+
+
+def find_neighbors_fill(count, sorted_indices=None, inv_bandwidth=None, pdf_mode=None):
+  """Second half of FindNeighbors (find_neighbors_ops.cpp:188-249) for a
+  NeighborCount: neigh_indices [M, 2].  With sorted_indices the same pass also
+  writes the pairs with the neighbor's original index: (neigh_indices,
+  original_ids [M, 2]); with a pdf_mode (and inv_bandwidth for mode 0) also the
+  density at every sample: (neigh_indices, original_ids, sample_pdf [Ns])."""
+  head, tail, _ = count.args
+  dev = count.ranges.device
+  m = count.total
   neigh = torch.empty((m, 2), dtype=torch.int32, device=dev)
-  _lib.check(fill(*common, ptr(ranges), c_i64(m), ptr(neigh)))
-  return ranges, neigh
+  lib = _lib.lib()
+  if sorted_indices is None:
+    if count.order is None:
+      _lib.check(lib.tfgpc_find_neighbors_fill(_stream(), *head, *tail, ptr(count.ranges),
+                                               c_i64(m), ptr(neigh)))
+    else:
+      _lib.check(lib.tfgpc_find_neighbors_fill_ordered(_stream(), *head, ptr(count.order), *tail,
+                                                       ptr(count.ranges), c_i64(m), ptr(neigh)))
+    return neigh
+  sorted_indices = _i32(sorted_indices)
+  inv_bw = None if inv_bandwidth is None else _f32(inv_bandwidth)
+  if pdf_mode == 0 and (inv_bw is None or inv_bw.shape[0] != count.dims):
+    raise _lib.TfgpcError(1, "ComputePDFOp expects one inverse bandwidth per dimension")
+  ids = torch.empty((m, 2), dtype=torch.int32, device=dev)
+  pdf = (None if pdf_mode is None else
+         torch.empty(count.ranges.shape[0], dtype=torch.float32, device=dev))
+  _lib.check(lib.tfgpc_find_neighbors_fill_fused(
+      _stream(), *head, ptr(count.order), *tail, ptr(count.ranges), c_i64(m), ptr(sorted_indices),
+      ptr(inv_bw), c_int(int(pdf_mode or 0)), ptr(neigh), ptr(ids), ptr(pdf)))
+  return (neigh, ids) if pdf is None else (neigh, ids, pdf)
+
+
+def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, num_cells,
+                   scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs=0, sample_order=None):
+  """FindNeighbors (find_neighbors/cc/ops/find_neighbors_ops.cpp:42-61).
+  Returns (samples_neigh_indices [Ns], neigh_indices [M, 2]).  sample_order, a
+  permutation of the sample indices, only sets the sequence the samples are
+  worked on in (same result; faster when it keeps spatial neighbors together)."""
+  count = find_neighbors_count(samples, samples_batch_ids, points, point_keys, grid_acc_ds,
+                               num_cells, scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs,
+                               sample_order)
+  return count.ranges, find_neighbors_fill(count)
 
 
 def original_neighbor_ids(neighbors, sorted_indices, pdf_by_original=None):

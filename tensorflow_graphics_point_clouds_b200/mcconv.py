@@ -157,9 +157,11 @@ def blocks_of_dense_grad(dw_dense, num_mlps, cin, hidden):
 
 
 def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
-                 alpha=0.2):
+                 alpha=0.2, pdf_by_neighbor=False):
   """basis[m, k] = act(diff_m . w1[:, k] + b1[k]) / pdf[m] (tfgpc_kernel_basis).
-  w1 [D, K], b1 [K]; neighbors hold (index into points_in, index into points_out)."""
+  w1 [D, K], b1 [K]; neighbors hold (index into points_in, index into points_out).
+  pdf_by_neighbor: pdf is a table with one density per point of points_in, read
+  at the pair's neighbor index, instead of the per-pair array."""
   points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
   d, k = w1.shape
@@ -168,12 +170,12 @@ def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activati
   _lib.check(_lib.lib().tfgpc_kernel_basis(
       _stream(), c_int(d), c_int(k), c_i64(m), ptr(points_in), ptr(points_out), ptr(neighbors),
       ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)), c_int(activation),
-      ctypes.c_float(alpha), ptr(basis)))
+      ctypes.c_float(alpha), c_int(int(pdf_by_neighbor)), ptr(basis)))
   return basis
 
 
 def kernel_basis_split(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
-                       alpha=0.2, want_fp32=True):
+                       alpha=0.2, want_fp32=True, pdf_by_neighbor=False):
   """kernel_basis that returns every row as the bf16 (hi, mid) pair the
   tensor-core kernels multiply with: (basis [M, K] float32 or None, pair
   [M, 2, K] bf16)."""
@@ -187,7 +189,7 @@ def kernel_basis_split(points_in, points_out, neighbors, pdf, w1, b1, radius, ac
   _lib.check(_lib.lib().tfgpc_kernel_basis_split(
       _stream(), c_int(d), c_int(k), c_i64(m), ptr(points_in), ptr(points_out), ptr(neighbors),
       ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)), c_int(activation),
-      ctypes.c_float(alpha), ptr(basis), ptr(pair)))
+      ctypes.c_float(alpha), c_int(int(pdf_by_neighbor)), ptr(basis), ptr(pair)))
   return basis, pair
 
 
@@ -224,7 +226,7 @@ def _mlp_blocks(weights, biases):
 
 
 def kernel_mlp_basis(points_in, points_out, neighbors, pdf, weights, biases, radius,
-                     activation=0, alpha=0.2):
+                     activation=0, alpha=0.2, pdf_by_neighbor=False):
   """The kernel MLP with any number of hidden layers (tfgpc_kernel_mlp_basis):
   weights[l] [G, H_{l-1}, H_l], biases[l] [G, 1, H_l] -> basis [M, G * H_last]."""
   points_in, points_out, pdf, neighbors = _f32(points_in), _f32(points_out), _f32(pdf), _i32(neighbors)
@@ -235,12 +237,13 @@ def kernel_mlp_basis(points_in, points_out, neighbors, pdf, weights, biases, rad
   _lib.check(_lib.lib().tfgpc_kernel_mlp_basis(
       _stream(), c_int(d), c_int(g), c_int(len(sizes)), sizes, c_i64(m), ptr(points_in),
       ptr(points_out), ptr(neighbors), ptr(pdf), ptr(flat_w), ptr(flat_b),
-      ctypes.c_float(1.0 / float(radius)), c_int(activation), ctypes.c_float(alpha), ptr(basis)))
+      ctypes.c_float(1.0 / float(radius)), c_int(activation), ctypes.c_float(alpha),
+      c_int(int(pdf_by_neighbor)), ptr(basis)))
   return basis
 
 
 def kernel_mlp_grads(points_in, points_out, neighbors, pdf, weights, biases, radius, basis_grads,
-                     activation=0, alpha=0.2, point_grads=False):
+                     activation=0, alpha=0.2, point_grads=False, pdf_by_neighbor=False):
   """All gradients of kernel_mlp_basis (tfgpc_kernel_mlp_grads): ([d_weights],
   [d_biases]) in the layouts of the inputs and, with point_grads, also
   (d_points_in, d_points_out, d_pdf [M]); when points_in and points_out are the
@@ -253,13 +256,13 @@ def kernel_mlp_grads(points_in, points_out, neighbors, pdf, weights, biases, rad
   if point_grads:
     dpin = torch.empty_like(points_in)
     dpout = dpin if points_out.data_ptr() == points_in.data_ptr() else torch.empty_like(points_out)
-    dpdf = torch.empty_like(pdf)
+    dpdf = torch.empty(neighbors.shape[0], dtype=torch.float32, device=pdf.device)
   _lib.check(_lib.lib().tfgpc_kernel_mlp_grads(
       _stream(), c_int(d), c_int(g), c_int(len(sizes)), sizes, c_i64(neighbors.shape[0]),
       c_i64(points_in.shape[0]), c_i64(points_out.shape[0]), ptr(points_in), ptr(points_out),
       ptr(neighbors), ptr(pdf), ptr(flat_w), ptr(flat_b), ctypes.c_float(1.0 / float(radius)),
-      c_int(activation), ctypes.c_float(alpha), ptr(basis_grads), ptr(dw), ptr(db), ptr(dpin),
-      ptr(dpout), ptr(dpdf)))
+      c_int(activation), ctypes.c_float(alpha), c_int(int(pdf_by_neighbor)), ptr(basis_grads),
+      ptr(dw), ptr(db), ptr(dpin), ptr(dpout), ptr(dpdf)))
   d_weights, d_biases, ow, ob = [], [], 0, 0
   for w, b in zip(weights, biases):
     d_weights.append(dw[ow:ow + w.numel()].reshape(w.shape)); ow += w.numel()
@@ -270,7 +273,7 @@ def kernel_mlp_grads(points_in, points_out, neighbors, pdf, weights, biases, rad
 
 
 def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, basis_grads,
-                       activation=0, alpha=0.2):
+                       activation=0, alpha=0.2, pdf_by_neighbor=False):
   """Gradients of kernel_basis with respect to w1 and b1 (tfgpc_kernel_basis_grads)."""
   points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
@@ -281,7 +284,8 @@ def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, ba
   _lib.check(_lib.lib().tfgpc_kernel_basis_grads(
       _stream(), c_int(d), c_int(k), c_i64(neighbors.shape[0]), ptr(points_in), ptr(points_out),
       ptr(neighbors), ptr(pdf), ptr(w1), ptr(b1), ctypes.c_float(1.0 / float(radius)),
-      c_int(activation), ctypes.c_float(alpha), ptr(basis_grads), ptr(dw1), ptr(db1)))
+      c_int(activation), ctypes.c_float(alpha), c_int(int(pdf_by_neighbor)), ptr(basis_grads),
+      ptr(dw1), ptr(db1)))
   return dw1, db1
 
 
@@ -337,7 +341,12 @@ class MCConv:
   def forward(self, features, point_cloud_in, point_cloud_out, radius, neighborhood=None,
               bandwidth=0.2, keep_for_backward=True):
     neigh = neighborhood or self.build_neighborhood(point_cloud_in, point_cloud_out, radius)
-    pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
+    # the densities as a per-point table where the neighborhood has them so (it
+    # then never forms the per-pair array), else per pair
+    pdf = neigh.pdf_by_neighbor_id(bandwidth=bandwidth, mode=0)
+    by_nbr = pdf is not None
+    if not by_nbr:
+      pdf = neigh.get_pdf(bandwidth=bandwidth, mode=0)
     ns = point_cloud_out._points.shape[0]
     p_in, p_out, ids = point_cloud_in._points, point_cloud_out._points, neigh._original_neigh_ids
     one_layer = len(self.kernel_weights) == 1
@@ -349,14 +358,15 @@ class MCConv:
     if grouped:
       # the basis only as the bf16 pair the tensor-core kernels read
       basis, pair = kernel_basis_split(p_in, p_out, ids, pdf, w1, b1, radius, self.activation,
-                                       self.alpha, want_fp32=False)
+                                       self.alpha, want_fp32=False, pdf_by_neighbor=by_nbr)
       self._grouped = (pair,) + group_plan(neigh)
     elif one_layer:
-      basis = kernel_basis(p_in, p_out, ids, pdf, w1, b1, radius, self.activation, self.alpha)
+      basis = kernel_basis(p_in, p_out, ids, pdf, w1, b1, radius, self.activation, self.alpha,
+                           pdf_by_neighbor=by_nbr)
       self._grouped = None
     else:
       basis = kernel_mlp_basis(p_in, p_out, ids, pdf, self.kernel_weights, self.kernel_biases,
-                               radius, self.activation, self.alpha)
+                               radius, self.activation, self.alpha, pdf_by_neighbor=by_nbr)
       self._grouped = None
     if (self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward):
       self._op = ProjectionGemm(self.k, self.cin, self.cout, ns, features.device,
@@ -370,6 +380,7 @@ class MCConv:
     if keep_for_backward:
       self._saved = (neigh, point_cloud_in, point_cloud_out, radius, pdf, basis,
                      _f32(features), wd, w1, b1)
+      self._pdf_by_nbr = by_nbr
     return out
 
   def saved_basis(self):
@@ -403,12 +414,12 @@ class MCConv:
     if point_grads or len(self.kernel_weights) > 1:
       res = kernel_mlp_grads(pc_in._points, pc_out._points, ids, pdf, self.kernel_weights,
                              self.kernel_biases, radius, dbasis, self.activation, self.alpha,
-                             point_grads=point_grads)
+                             point_grads=point_grads, pdf_by_neighbor=self._pdf_by_nbr)
       dws, dbs = res[0], res[1]
       head = (dfeat, dws if self._list_form else dws[0], dbs if self._list_form else dbs[0], dwf)
       return head + tuple(res[2:]) if point_grads else head
     dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, ids, pdf, w1, b1, radius, dbasis,
-                                  self.activation, self.alpha)
+                                  self.activation, self.alpha, pdf_by_neighbor=self._pdf_by_nbr)
     dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()
     db1 = db1.reshape(self.num_mlps, 1, self.hidden)
     if self._list_form:

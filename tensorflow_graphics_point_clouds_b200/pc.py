@@ -93,7 +93,9 @@ class Grid:
 
 
 class Neighborhood:
-  """Neighborhood.py:218-311."""
+  """Neighborhood.py:218-329.  The count pass runs in the constructor (ranges and
+  the number of pairs are known from then on); the neighbor list is written when
+  it is first asked for, in one pass together with the list in original ids."""
 
   def __init__(self, grid, radius, point_cloud_sample=None, max_neighbors=0):
     dev = grid._sorted_points.device
@@ -114,20 +116,39 @@ class Neighborhood:
     # a sequence that visits the samples cell by cell, where one is known (the
     # samples of a self neighborhood are the sorted points: already in it)
     self._sample_order = order
-    self._samples_neigh_ranges, self._neighbors = ops.find_neighbors(
+    self._count = ops.find_neighbors_count(
         smp._points, smp._batch_ids, grid._sorted_points, grid._sorted_keys, grid.get_DS(),
         grid._num_cells, grid._scaled_aabb_min, grid._inv_cell_sizes,
         torch.reciprocal(self._radii), max_neighbors, sample_order=order)
+    self._samples_neigh_ranges = self._count.ranges
+    self._nbrs = None
     self._orig_ids = None
     self._pdf = None
     self._point_pdf = None
+    self._sample_pdf = None
+    self._pdf_ready = False
+    self._transposed = None
+
+  @property
+  def num_pairs(self):
+    return self._count.total
+
+  def _fill(self):
+    """Writes the neighbor list [M, 2] (index into the sorted points, sample
+    index) and, in the same pass, the list with the neighbors' indices in the
+    unsorted point order (Neighborhood.py:246-250)."""
+    if self._nbrs is None:
+      self._nbrs, self._orig_ids = ops.find_neighbors_fill(self._count,
+                                                            self._grid._sorted_indices)
+
+  @property
+  def _neighbors(self):
+    self._fill()
+    return self._nbrs
 
   @property
   def _original_neigh_ids(self):
-    """Neighbor ids mapped back to the unsorted point order
-    (Neighborhood.py:246-250), built on first use."""
-    if self._orig_ids is None:
-      self._orig_ids, _ = ops.original_neighbor_ids(self._neighbors, self._grid._sorted_indices)
+    self._fill()
     return self._orig_ids
 
   def _samples_are_grid_points(self):
@@ -144,27 +165,60 @@ class Neighborhood:
     bw = _to_dims(bandwidth, d, self._radii.device)
     inv_bw, inv_r = torch.reciprocal(bw), torch.reciprocal(self._radii)
     g = self._grid
+    self._pdf = None
     if self._equal_samples:
       self._point_pdf = ops.compute_pdf_with_pt_grads(
           g._sorted_points, self._neighbors, self._samples_neigh_ranges, inv_bw, inv_r, mode)
-      self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
     elif self._samples_are_grid_points():
-      sample_pdf = ops.compute_pdf_at_samples(
+      # sample s is point s of the unsorted cloud
+      self._sample_pdf = ops.compute_pdf_at_samples(
           self._point_cloud_sampled._points, g._sorted_points, self._neighbors,
           self._samples_neigh_ranges, inv_bw, inv_r, mode)
-      # sample s is point s of the unsorted cloud: index by the neighbors' original ids
-      self._point_pdf = sample_pdf[g._sorted_indices.to(torch.int64)]
-      self._orig_ids, self._pdf = ops.original_neighbor_ids(self._neighbors, g._sorted_indices,
-                                                            sample_pdf)
+      self._point_pdf = None
     else:
       nb = Neighborhood(g, self._radii)
       self._point_pdf = ops.compute_pdf_with_pt_grads(
           g._sorted_points, nb._neighbors, nb._samples_neigh_ranges, inv_bw, inv_r, mode)
-      self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
+    self._pdf_ready = True
+
+  def pdf_by_neighbor_id(self, **kwargs):
+    """The densities as a table indexed by the FIRST column of _original_neigh_ids
+    (one value per point of the grid's cloud), where the neighborhood has them in
+    that form, else None: kernels that take the table read it in place of the
+    per-pair array of get_pdf."""
+    if not self._pdf_ready:
+      self.compute_pdf(**kwargs)
+    return self._sample_pdf
+
+  def point_pdf(self, **kwargs):
+    """Density of every point of the grid, in the SORTED order of the grid."""
+    if not self._pdf_ready:
+      self.compute_pdf(**kwargs)
+    if self._point_pdf is None:
+      self._point_pdf = self._sample_pdf[self._grid._sorted_indices.to(torch.int64)]
+    return self._point_pdf
+
+  def transpose(self):
+    """Neighborhood.py:318-329: the neighborhood with the roles of samples and
+    points exchanged (the samples' cloud on a grid of its own, searched around the
+    points of this one); a self neighborhood is its own transpose."""
+    if self._transposed is None:
+      if self._equal_samples:
+        self._transposed = self
+      else:
+        grid = Grid(self._point_cloud_sampled, self._radii)
+        self._transposed = Neighborhood(grid, self._radii, self._grid._point_cloud)
+    return self._transposed
 
   def get_pdf(self, **kwargs):
-    if self._pdf is None:
+    """[M] density of every pair's neighbor point (Neighborhood.py:287)."""
+    if not self._pdf_ready:
       self.compute_pdf(**kwargs)
+    if self._pdf is None:
+      if self._sample_pdf is not None:
+        self._pdf = self._sample_pdf[self._original_neigh_ids[:, 0].to(torch.int64)]
+      else:
+        self._pdf = self._point_pdf[self._neighbors[:, 0].to(torch.int64)]
     return self._pdf
 
   def pdf_point_grads(self, pdf_grads, bandwidth=0.2, mode=0):

@@ -39,7 +39,8 @@ def test_layer_step_full_size_against_fp64():
   out = layer.forward(feat, cloud, cloud, args.radius)
   dfeat, dw1, db1, dwf = layer.backward(d_out)
   layer._op.check_status()
-  neigh, _, _, radius, pdf, _, features, wd, w1f, b1f = layer._saved
+  neigh, _, _, radius, _, _, features, wd, w1f, b1f = layer._saved
+  pdf = neigh.get_pdf()            # per pair (the layer itself reads the per-point table)
   basis = layer.saved_basis()      # the grouped path keeps it as a bf16 pair: hi + mid
   nb = neigh._original_neigh_ids.long()
   n, c, k = features.shape[0], args.cin, args.hidden

@@ -68,7 +68,7 @@ def test_cuda_library_matches_golden(golden):
   out = layer.forward(t(golden["features"]), cloud, cloud, radius, neighborhood=neigh)
   dfeat, dw1, db1, dwf = layer.backward(t(golden["d_out"]))
   layer._op.check_status()
-  close(neigh._point_pdf.cpu().numpy(), golden["point_pdf"])
+  close(neigh.point_pdf().cpu().numpy(), golden["point_pdf"])
   close(layer.saved_basis().cpu().numpy(), golden["basis"])
   close(out.cpu().numpy(), golden["out"])
   close(dfeat.cpu().numpy(), golden["d_feat"])

@@ -406,7 +406,7 @@ def test_pdf_without_second_neighbor_search_matches_self_neighborhood():
   nb = pc.Neighborhood(pc.Grid(cloud, 0.2), 0.2, cloud)
   assert nb._samples_are_grid_points() and not nb._equal_samples
   close(nb.get_pdf(bandwidth=0.2, mode=0).cpu().numpy(), ref_pdf)
-  close(nb._point_pdf.cpu().numpy(), nb_ref.point_pdf)
+  close(nb.point_pdf().cpu().numpy(), nb_ref.point_pdf)
 
 
 @pytest.mark.parametrize("d", [2, 3, 4])
@@ -432,3 +432,54 @@ def test_find_neighbors_visiting_order_does_not_change_results(d):
   nb = pc.Neighborhood(g, 0.2, cloud)          # takes the ordered entries
   nb_ref = pr.Neighborhood(g_ref, 0.2, pts, bid)
   assert_neigh_equal(nb_ref, nb)
+
+
+def test_neighborhood_transpose():
+  """Neighborhood.py:318-329: the transposed neighborhood holds the same pairs
+  with the roles exchanged; a self neighborhood is its own transpose."""
+  rng = np.random.default_rng(9)
+  b = 3
+  pts, bid = random_cloud(rng, b, 2500, 3)
+  smp, sbid = random_cloud(rng, b, 400, 3)
+  g_ref, g = grid_pair(pts, bid, b, 0.2)
+  nb_ref, nb = neigh_pair(g_ref, g, 0.2, smp, sbid)
+  tr = nb.transpose()
+  assert tr is nb.transpose()                     # built once
+  assert tr._samples_neigh_ranges.shape[0] == len(pts)
+  pairs = nb._original_neigh_ids.cpu().numpy()     # (point, sample)
+  tpairs = tr._original_neigh_ids.cpu().numpy()    # (sample, point)
+  assert len(pairs) == len(tpairs)
+  key = lambda a, bb: np.sort(a.astype(np.int64) * 1_000_000 + bb)
+  assert np.array_equal(key(pairs[:, 0], pairs[:, 1]), key(tpairs[:, 1], tpairs[:, 0]))
+  # the oracle's search with the roles exchanged gives the same lists, bit for bit
+  gt_ref = pr.Grid(smp, sbid, b, 0.2)
+  nbt_ref = pr.Neighborhood(gt_ref, 0.2, pts, bid)
+  assert_neigh_equal(nbt_ref, tr)
+  own = pc.Neighborhood(g, 0.2)
+  assert own.transpose() is own
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_fused_fill_matches_separate_passes(mode):
+  """The fill pass that also writes original ids (and, on request, densities)
+  must give what the separate passes give: lists and ids bit for bit, densities
+  within 1e-4."""
+  rng = np.random.default_rng(21)
+  b = 4
+  pts, bid = random_cloud(rng, b, 6000, 3)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  g = pc.Grid(cloud, 0.15)
+  nb = pc.Neighborhood(g, 0.15, cloud)            # ids come from the fused pass
+  plain = ops.find_neighbors_fill(nb._count)
+  ids, _ = ops.original_neighbor_ids(plain, g._sorted_indices)
+  assert torch.equal(nb._neighbors, plain)
+  assert torch.equal(nb._original_neigh_ids, ids)
+  inv_bw = torch.full((3,), 1 / 0.2, device=DEV)
+  n2, i2, pdf = ops.find_neighbors_fill(nb._count, g._sorted_indices, inv_bw, mode)
+  assert torch.equal(n2, plain) and torch.equal(i2, ids)
+  nb.compute_pdf(bandwidth=0.2, mode=mode)
+  close(pdf.cpu().numpy(), nb.pdf_by_neighbor_id().cpu().numpy())
+  g_ref = pr.Grid(pts, bid, b, 0.15)
+  nb_ref = pr.Neighborhood(g_ref, 0.15, pts, bid)
+  close(nb.get_pdf().cpu().numpy(), nb_ref.get_pdf(bandwidth=0.2, mode=mode))
+  close(nb.point_pdf().cpu().numpy(), nb_ref.point_pdf)
