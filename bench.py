@@ -141,6 +141,11 @@ NCU_TRAFFIC_BYTES_PER_POINT = {
     "gemm_bf16x3_k_mn_image": (2.149690e9 + 2.100168e9) / 262144,
     "gemm_bf16x3_mn_k_image": (0.270630e9 + 2.103353e9) / 262144,
     "gemm_bf16x3_mn_mn": (2.415943e9 + 0.004868e9) / 262144,
+    # profiles/grouped_projection_kernels_8_clouds.md: bytes of one launch / 131072 points
+    "basis_proj_fwd_tcu": (0.388030e9 + 1.016499e9) / 131072,
+    "basis_proj_grads_tcu": (1.529835e9 + 0.318466e9) / 131072,
+    "gemm_bf16x3_mn_k_scatter": (1.088718e9 + 0.120507e9) / 131072,
+    "kernel_basis": (0.036006e9 + 0.212095e9) / 131072,
 }
 
 
@@ -165,6 +170,8 @@ def kernel_model(name, sizes):
     return "tensor", 2.0 * n * ck * co
   if name == "find_neighbors_fill":
     return "hbm", n * 36 + m * 8
+  if name == "find_neighbors_fill_fused":     # both forms of the list
+    return "hbm", n * 40 + m * 16
   if name == "find_neighbors_count":
     return "hbm", n * 36
   if name == "compute_pdf":
@@ -647,6 +654,7 @@ SIDE_MODELS = {
     "build_grid_ds": lambda n, m, s: n * 8,
     "find_neighbors_count": lambda n, m, s: n * 36,
     "find_neighbors_fill": lambda n, m, s: n * 36 + m * 8,
+    "find_neighbors_fill_fused": lambda n, m, s: n * 40 + m * 16,
     "compute_pdf": lambda n, m, s: n * 20 + m * 8,
     "sampling_poisson_pass": lambda n, m, s: (n * 8 + m * 12) / 8.0,
     "sampling_store_poisson": lambda n, m, s: n * 8 + s * 20,

@@ -137,7 +137,13 @@ class Neighborhood:
     """Writes the neighbor list [M, 2] (index into the sorted points, sample
     index) and, in the same pass, the list with the neighbors' indices in the
     unsorted point order (Neighborhood.py:246-250)."""
-    if self._nbrs is None:
+    if self._nbrs is not None:
+      return
+    if self._equal_samples:
+      # a self neighborhood mostly feeds the density estimate and the sampling,
+      # which read sorted ids only: the original-id list is built if asked for
+      self._nbrs = ops.find_neighbors_fill(self._count)
+    else:
       self._nbrs, self._orig_ids = ops.find_neighbors_fill(self._count,
                                                             self._grid._sorted_indices)
 
@@ -149,6 +155,8 @@ class Neighborhood:
   @property
   def _original_neigh_ids(self):
     self._fill()
+    if self._orig_ids is None:
+      self._orig_ids, _ = ops.original_neighbor_ids(self._nbrs, self._grid._sorted_indices)
     return self._orig_ids
 
   def _samples_are_grid_points(self):
