@@ -40,7 +40,11 @@ def parse_args():
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=20)
   ap.add_argument("--warmup", type=int, default=3)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-kernels"],
+                  help="ours: this library; reference: the CPU port of the reference path (the "
+                       "reference has no CPU kernels of its own); reference-kernels: the "
+                       "reference's own CUDA kernels recompiled for sm_100a (oracle/_ref), op by "
+                       "op beside this library's on the same inputs")
   ap.add_argument("--clouds", type=int, default=32)
   ap.add_argument("--points", type=int, default=16384)
   ap.add_argument("--radius", type=float, default=0.079)
@@ -50,6 +54,10 @@ def parse_args():
   ap.add_argument("--cpu-sample-clouds", type=int, default=1)
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--classifier-preset", default="three_level", choices=["three_level", "script"],
+                  help="classifier workload: three levels with radii 0.1 / 0.2 / sqrt(3), widths "
+                       "128 / 256 / 1024 and a 1024 -> 40 head, or the four levels of the "
+                       "reference's modelnet40_small.py script")
   ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                   help="strong: one batch of --clouds clouds sharded over the GPUs; "
                        "weak: --clouds clouds per GPU")
@@ -318,6 +326,98 @@ def run_reference(args, rank, world):
       "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
       "gpu_launches": 0,
   }
+  print(json.dumps(line), flush=True)
+
+
+
+# ------------------------------------------- the reference's own kernels -----
+
+def run_reference_kernels(args):
+  """Times the reference's own CUDA kernels (its *_kernels.cu.cc files compiled
+  unchanged for sm_100a into oracle/_ref by oracle/build_ref.py, behind a plain
+  CUDA device object) op by op against this library's kernels on the same GPU
+  and the same seeded inputs: CUDA-event times around the kernel sequence of each
+  op (second call, device buffers recycled, host copies excluded).  Prints one
+  JSON line with a row per op.  --clouds / --points set the size (8 clouds fit
+  the reference's [N, Cin, K] fp32 projection comfortably)."""
+  import torch
+  from oracle import ref_kernels as ref
+  from tensorflow_graphics_point_clouds_b200 import _lib, custom_ops as ops, pc, synthetic
+  if not ref.available():
+    print(json.dumps({"impl": "reference-kernels",
+                      "unavailable": "oracle/_ref is not built (needs the reference checkout "
+                                     "at build time)"}), flush=True)
+    return
+  clouds, per = args.clouds, args.points
+
+  def ours(fn, name_prefixes, reps=3):
+    for _ in range(2):
+      fn()
+    torch.cuda.synchronize()
+    _lib.profile_enable(True)
+    for _ in range(reps):
+      fn()
+    torch.cuda.synchronize()
+    rec = _lib.profile_collect()
+    _lib.profile_enable(False)
+    return sum(ms for n, ms in rec if n.startswith(name_prefixes)) / reps
+
+  radius, cin, k = 0.079, 128, 16
+  pts, bid = synthetic.uniform_clouds(clouds, per, seed=2)
+  n = len(pts)
+  rng = np.random.default_rng(0)
+  t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+  cloud = pc.PointCloud(t(pts), t(bid), clouds)
+  grid = pc.Grid(cloud, radius)
+  neigh = pc.Neighborhood(grid, radius)               # self neighborhood, sorted order
+  g_np = dict(sp=grid._sorted_points.cpu().numpy(), sb=grid._sorted_batch_ids.cpu().numpy(),
+              sk=grid._sorted_keys.cpu().numpy(), ds=grid.get_DS().cpu().numpy(),
+              nc=grid._num_cells.cpu().numpy(), smin=grid._scaled_aabb_min.cpu().numpy(),
+              ic=grid._inv_cell_sizes.cpu().numpy())
+  inv_r = np.repeat(F32(1) / F32(radius), 3)
+  inv_bw = np.repeat(F32(5.0), 3)
+  nb = neigh._neighbors.cpu().numpy(); rg = neigh._samples_neigh_ranges.cpu().numpy()
+  m = len(nb)
+  rows = []
+
+  def twice(fn):     # the second call reuses the harness' device buffers: kernels only
+    fn()
+    return fn()
+
+  _, ms = twice(lambda: ref.compute_keys(pts, bid, g_np["smin"], g_np["nc"], g_np["ic"]))
+  mine = ours(lambda: ops.compute_keys(cloud._points, cloud._batch_ids, grid._scaled_aabb_min,
+                                       grid._num_cells, grid._inv_cell_sizes), ("compute_keys",))
+  rows.append(("ComputeKeys", ms, mine))
+  _, ms = twice(lambda: ref.build_grid_ds(g_np["sk"], g_np["nc"], clouds))
+  mine = ours(lambda: ops.build_grid_ds(grid._sorted_keys, grid._num_cells, grid._num_cells_host,
+                                        clouds), ("build_grid_ds",))
+  rows.append(("BuildGridDs", ms, mine))
+  _, _, ms = twice(lambda: ref.find_neighbors(g_np["sp"], g_np["sb"], g_np["sp"], g_np["sk"],
+                                              g_np["ds"], g_np["nc"], g_np["smin"], g_np["ic"],
+                                              inv_r, capacity=m + 16))
+  mine = ours(lambda: pc.Neighborhood(grid, radius), ("find_neighbors", "scan_i32"))
+  rows.append(("FindNeighbors", ms, mine))
+  _, _, ms = twice(lambda: ref.compute_pdf(g_np["sp"], nb, rg, inv_bw, inv_r, 0))
+  mine = ours(lambda: ops.compute_pdf(grid._sorted_points, neigh._neighbors,
+                                      neigh._samples_neigh_ranges, t(inv_bw), t(inv_r), 0),
+              ("compute_pdf",))
+  rows.append(("ComputePdf", ms, mine))
+  basis = rng.standard_normal((m, k), dtype=F32)
+  feat = rng.standard_normal((n, cin), dtype=F32)
+  out, _, _, ms = twice(lambda: ref.basis_proj(basis, feat, nb, rg))
+  tb, tf = t(basis), t(feat)
+  mine = ours(lambda: ops.basis_proj(tb, tf, neigh._neighbors, neigh._samples_neigh_ranges),
+              ("basis_proj", "split_features"))
+  rows.append(("BasisProj [%d,%d,%d]" % (n, cin, k), ms, mine))
+  _, _, _, ms = twice(lambda: ref.sampling(g_np["sp"], g_np["sb"], g_np["sk"], g_np["nc"], nb, rg, 0))
+  mine = ours(lambda: pc.sample(neigh, "poisson"), ("sampling", "scan_i32"))
+  rows.append(("Sampling (Poisson)", ms, mine))
+
+  line = {"impl": "reference-kernels", "unit": "ms", "data": "synthetic",
+          "config": {"workload": "%d clouds x %d points uniform in [0,1)^3, radius %.3f, Cin %d, "
+                                 "K %d" % (clouds, per, radius, cin, k), "neighbor_pairs": int(m)},
+          "ops": [{"op": name, "reference_kernels_ms": r, "this_library_ms": o,
+                   "ratio": (r / o if o > 0 else None)} for name, r, o in rows]}
   print(json.dumps(line), flush=True)
 
 
@@ -768,9 +868,9 @@ def side_workload_line(args, device_index):
 
 
 def run_classifier_workload(args):
-  """Forward pass of the small classification network (widths 1-128-256-512-
-  1024-1024-40, MCConv with 4 kernel MLPs of 8 units) on 32 clouds of 1024 points
-  on one GPU: time per batch and the kernels it spends it in."""
+  """Forward pass of the small classification network (MCConv with 4 kernel MLPs
+  of 8 units per level; level layout by --classifier-preset) on 32 clouds of 1024
+  points on one GPU: time per batch and the kernels it spends it in."""
   import torch
   from tensorflow_graphics_point_clouds_b200 import _lib, build, classifier, synthetic
   if not torch.cuda.is_available():
@@ -778,11 +878,14 @@ def run_classifier_workload(args):
   build.build()
   dev = torch.device("cuda", 0)
   clouds, points = 32, 1024
-  radii = [0.1, 0.2, 0.4, 2 * np.sqrt(3)]
+  preset = classifier.PRESETS[args.classifier_preset]
+  radii = list(preset["radii"])
   pts, bid = synthetic.unit_sphere_shapes(clouds, points, seed=4)
   tp, tb = torch.from_numpy(pts).to(dev), torch.from_numpy(bid).to(dev)
   feat = torch.ones((len(pts), 1), dtype=torch.float32, device=dev)
-  net = classifier.SmallClassifier(synthetic.small_classifier_weights(40), radii, dev)
+  weights = synthetic.small_classifier_weights(40, preset["feature_sizes"],
+                                               head_layers=preset["head_layers"])
+  net = classifier.SmallClassifier(weights, radii, dev, preset["pool_before_head"])
   sampler = ClockSampler(0)
   sampler.start()
   for _ in range(max(args.warmup, 3)):
@@ -809,8 +912,9 @@ def run_classifier_workload(args):
       "metric": "classifier_forward_points_per_s", "value": clouds * points / (ms * 1e-3),
       "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
       "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
-      "config": {"workload": "classifier", "clouds": clouds, "points_per_cloud": points,
-                 "radii": [float(r) for r in radii]},
+      "config": {"workload": "classifier", "preset": args.classifier_preset, "clouds": clouds,
+                 "points_per_cloud": points, "radii": [float(r) for r in radii],
+                 "feature_sizes": list(preset["feature_sizes"])},
       "clocks": clocks, "kernels": kernels,
       "kernel_ms_per_step": sum(v["ms_per_step"] for v in kernels.values()),
   }
@@ -828,6 +932,9 @@ def main():
   elif args.workload != "mcconv":
     if rank == 0:
       run_side_workload(args)
+  elif args.impl == "reference-kernels":
+    if rank == 0:
+      run_reference_kernels(args)
   elif args.impl == "reference":
     run_reference(args, rank, world)
   else:

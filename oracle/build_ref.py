@@ -4,6 +4,7 @@ INFRASTRUCTURE; git-ignored output).  Only possible where the reference tree is
 mounted; on a machine without it the prebuilt library is used if present.
 
 Usage: python oracle/build_ref.py [/path/to/reference]
+(default: $TFG_REFERENCE_DIR, else ../reference relative to the repository)
 """
 import concurrent.futures
 import glob
@@ -15,8 +16,11 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT_DIR, "libtfg_ref_kernels.so")
-# where a checkout of the reference project lies (only needed to rebuild the library)
-DEFAULT_REFERENCE = os.environ.get("TFG_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+# Where a checkout of the reference project lies (only needed to rebuild the
+# library): TFG_REFERENCE_DIR, else a directory named "reference" beside this
+# repository.
+DEFAULT_REFERENCE = os.environ.get(
+    "TFG_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def build(reference=DEFAULT_REFERENCE, force=False):

@@ -390,7 +390,7 @@ def conv1x1(features, weights, bias):
 
 
 def small_classifier_forward(points, batch_ids, batch_size, features, weights, sample_radii,
-                             bn_eps=1e-3, leaky_alpha=0.3):
+                             bn_eps=1e-3, leaky_alpha=0.3, pool_before_head=False):
   """modelnet40_small.py:121-261 (MCConv variant) at inference with freshly
   initialised batch normalisations: hierarchy (PointHierarchy.py:40-98), per
   level MCConv (MCConv.py:163-194, 254-269), BN + LeakyReLU + Conv1x1 + BN +
@@ -411,7 +411,13 @@ def small_classifier_forward(points, batch_ids, batch_size, features, weights, s
     if i < last:
       x = act(x)
       x = act(conv1x1(x, *weights["conv1x1"][i]))
-  x = x[np.argsort(levels[-1][1], kind='stable')]
+  if pool_before_head:
+    # a last radius that leaves several points per cloud: mean over the cloud
+    # (GlobalAveragePooling, Pooling.py:90-96) instead of picking the single row
+    x = global_pool(x, levels[-1][1], batch_size, 'avg')
+  else:
+    x = x[np.argsort(levels[-1][1], kind='stable')]
   x = act(x)
-  x = act(conv1x1(x, *weights["dense"][0]))
-  return conv1x1(x, *weights["dense"][1])
+  for w, b in weights["dense"][:-1]:
+    x = act(conv1x1(x, w, b))
+  return conv1x1(x, *weights["dense"][-1])

@@ -14,8 +14,24 @@ KERAS_BN_EPS = 1e-3        # tf.keras.layers.BatchNormalization default epsilon
 KERAS_LEAKY_ALPHA = 0.3    # tf.keras.layers.LeakyReLU default slope
 
 
+# Level layouts: (sampling radii, feature sizes input -> per level -> head).
+# 'script': modelnet40_small.py:121-261, 331 (four levels, the last radius
+# 2 sqrt(3) leaves one point per cloud, two dense layers).  'three_level': three
+# levels with radii 0.1 / 0.2 / sqrt(3), widths 128 / 256 / 1024 and a single
+# 1024 -> 40 layer as head; sqrt(3) can leave several points per cloud, which are
+# averaged before the head.
+PRESETS = {
+    'script': dict(radii=(0.1, 0.2, 0.4, 2 * math.sqrt(3)),
+                   feature_sizes=(1, 128, 256, 512, 1024, 1024, 40), head_layers=2,
+                   pool_before_head=False),
+    'three_level': dict(radii=(0.1, 0.2, math.sqrt(3)), feature_sizes=(1, 128, 256, 1024, 40),
+                        head_layers=1, pool_before_head=True),
+}
+
+
 class SmallClassifier:
-  def __init__(self, weights, sample_radii, device):
+  def __init__(self, weights, sample_radii, device, pool_before_head=False):
+    self.pool_before_head = bool(pool_before_head)
     to = lambda a: torch.from_numpy(a).to(device)
     self.radii = [float(r) for r in sample_radii]
     self.convs = []
@@ -45,9 +61,12 @@ class SmallClassifier:
         x = self._bn_act(x)
     # return_sorted=True of the last convolution (modelnet40_small.py:249-254):
     # rows in ascending batch id; the last radius leaves one point per cloud
-    order = torch.argsort(clouds[-1]._batch_ids.long(), stable=True)
-    x = x[order].contiguous()
+    if self.pool_before_head:
+      x = mcconv.global_pool(x, clouds[-1], 'avg')
+    else:
+      order = torch.argsort(clouds[-1]._batch_ids.long(), stable=True)
+      x = x[order].contiguous()
     x = self._bn_act(x)
-    x = mcconv.conv1x1(x, *self.dense[0])
-    x = self._bn_act(x)
-    return mcconv.conv1x1(x, *self.dense[1])
+    for w, b in self.dense[:-1]:
+      x = self._bn_act(mcconv.conv1x1(x, w, b))
+    return mcconv.conv1x1(x, *self.dense[-1])

@@ -110,12 +110,13 @@ def unit_sphere_shapes(num_clouds, points_per_cloud, seed):
 
 
 def small_classifier_weights(seed, feature_sizes=(1, 128, 256, 512, 1024, 1024, 40), num_mlps=4,
-                             hidden=8):
+                             hidden=8, head_layers=2):
   """Random-init weights of the modelnet40_small.py network (MCConv variant):
   per level the MCConv weights, then a Conv1x1 except after the last level,
-  then the two dense layers of the head."""
+  then the dense layers of the head (feature_sizes = input, one size per level,
+  one per head layer)."""
   rng = np.random.default_rng(seed)
-  levels = len(feature_sizes) - 3
+  levels = len(feature_sizes) - 1 - head_layers
   out = {"conv": [], "conv1x1": [], "dense": []}
   for i in range(levels):
     cin, cout = feature_sizes[i], feature_sizes[i + 1]
@@ -123,7 +124,8 @@ def small_classifier_weights(seed, feature_sizes=(1, 128, 256, 512, 1024, 1024, 
     if i < levels - 1:
       out["conv1x1"].append((glorot_uniform(rng, cout, cout, (cout, cout)),
                              (rng.normal(size=(1, cout)) * 0.01).astype(F32)))
-  for cin, cout in ((feature_sizes[-3], feature_sizes[-2]), (feature_sizes[-2], feature_sizes[-1])):
+  for i in range(levels, levels + head_layers):
+    cin, cout = feature_sizes[i], feature_sizes[i + 1]
     out["dense"].append((glorot_uniform(rng, cin, cout, (cin, cout)),
                          (rng.normal(size=(1, cout)) * 0.01).astype(F32)))
   return out

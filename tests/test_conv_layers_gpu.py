@@ -143,3 +143,23 @@ def test_small_classifier_forward():
   out = net.forward(t(pts), t(bid), b, t(feat))
   assert out.shape == (b, 40)
   close(out.cpu().numpy(), ref)
+
+
+def test_three_level_classifier_forward():
+  """Three levels with sampling radii 0.1 / 0.2 / sqrt(3), widths 128 / 256 / 1024
+  and a 1024 -> 40 head on 32 clouds of 1024 points (the layout of the
+  benchmark's classifier configuration); the points the last radius leaves in a
+  cloud are averaged before the head."""
+  from tensorflow_graphics_point_clouds_b200 import classifier, synthetic
+  b = 32
+  preset = classifier.PRESETS['three_level']
+  pts, bid = synthetic.unit_sphere_shapes(b, 1024, seed=4)
+  feat = np.ones((len(pts), 1), F32)
+  weights = synthetic.small_classifier_weights(41, preset['feature_sizes'],
+                                               head_layers=preset['head_layers'])
+  ref = pr.small_classifier_forward(pts, bid, b, feat, weights, preset['radii'],
+                                    pool_before_head=True)
+  net = classifier.SmallClassifier(weights, preset['radii'], "cuda", pool_before_head=True)
+  out = net.forward(t(pts), t(bid), b, t(feat))
+  assert out.shape == (b, 40)
+  close(out.cpu().numpy(), ref)

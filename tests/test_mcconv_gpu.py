@@ -152,6 +152,10 @@ def test_mcconv_layer_matches_oracle(d, g, h):
   close(out.cpu().numpy(), ref_out)
   close(dfeat.cpu().numpy(), ref_df)
   close(dwf.cpu().numpy(), ref_dwf)
+  # The 64 kernel-MLP gradients are sums over all M pairs of dbasis / pdf * slope:
+  # dbasis itself carries the 3-pass bf16 error of two products in a row (up to
+  # ~6e-5 per value), and a pre-activation within fp32 rounding of zero takes the
+  # other slope than in the float64 reference; measured up to 1.4e-4.
   close(dw1.cpu().numpy(), ref_dw1, rel=2e-4)
   close(db1.cpu().numpy(), ref_db1, rel=2e-4)
 
