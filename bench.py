@@ -395,7 +395,7 @@ def run_reference_kernels(args):
   _, _, ms = twice(lambda: ref.find_neighbors(g_np["sp"], g_np["sb"], g_np["sp"], g_np["sk"],
                                               g_np["ds"], g_np["nc"], g_np["smin"], g_np["ic"],
                                               inv_r, capacity=m + 16))
-  mine = ours(lambda: pc.Neighborhood(grid, radius), ("find_neighbors", "scan_i32"))
+  mine = ours(lambda: pc.Neighborhood(grid, radius)._neighbors, ("find_neighbors", "scan_i32"))
   rows.append(("FindNeighbors", ms, mine))
   _, _, ms = twice(lambda: ref.compute_pdf(g_np["sp"], nb, rg, inv_bw, inv_r, 0))
   mine = ours(lambda: ops.compute_pdf(grid._sorted_points, neigh._neighbors,

@@ -167,6 +167,46 @@ int tfgpc_original_neighbor_ids(void* stream, int64_t M,
                                 const float* pdf_by_original, int32_t* ids_out,
                                 float* pdf_out);
 
+/* ---- Grid and neighbor count in one call ------------------------------------
+ * Replaces, for one cloud and one neighborhood on it, the chain PointCloud.
+ * get_AABB (pylib/pc/PointCloud.py:38-43) -> Grid (Grid.py:32-83: cell counts,
+ * ComputeKeys, argsort + gathers, BuildGridDs) -> first half of Neighborhood
+ * (Neighborhood.py:218-245: FindNeighbors up to the number of pairs), which in
+ * pylib -- and through the separate entries above -- reads the cell counts back
+ * to the host before it can size the tube array and once more for the number of
+ * pairs.  Here the cell counts stay on the device; the tube array and the key
+ * width of the sort are sized for max_cells cells per dimension (a bound the
+ * caller chooses, e.g. what the previous batch needed); ONE blocking read at the
+ * end returns the cell counts, whether they fit, and the number of pairs.
+ * cell_sizes, radii [D] are HOST arrays.  Samples: samples_are_points 0 = the
+ * given samples / samples_batch_ids [ns]; 1 = the points themselves in their own
+ * order (ns == n; they are visited in the sequence of the key sort); 2 = the
+ * sorted points (a self neighborhood, Neighborhood.py:229-233).
+ * Outputs [device, caller-allocated]: aabb_min/max [B,D] (already widened by
+ * 1e-9), num_cells [D], scaled_aabb_min [B,D], inv_cell_sizes, inv_radii [D],
+ * keys [n], sorted_indices [n], sorted_keys [n], sorted_points [n,D],
+ * sorted_batch_ids [n], ds [_ds_elems(D, B, max_cells)] int32 (the tubes fill
+ * the first B * num_cells[0] * num_cells[1] pairs; pass it to the fill entries
+ * as it is), ranges [ns]; [host] num_cells_host_out [D], total_out.  Returns
+ * TFGPC_ENOMEM (and the cell counts the grid asked for) if max_cells was too
+ * small: repeat with a larger bound.  Follow with one of the
+ * tfgpc_find_neighbors_fill* entries. */
+size_t tfgpc_grid_neighborhood_workspace_bytes(int64_t n, int64_t ns);
+size_t tfgpc_grid_neighborhood_ds_elems(int D, int64_t batch_size,
+                                        int max_cells);
+int tfgpc_grid_neighborhood_count(
+    void* stream, int D, int64_t n, const float* points,
+    const int32_t* batch_ids, int64_t batch_size, const float* cell_sizes,
+    const float* radii, int max_cells, int64_t ns, const float* samples,
+    const int32_t* samples_batch_ids, int samples_are_points, int max_neighs,
+    float* aabb_min_out, float* aabb_max_out, int32_t* num_cells_out,
+    float* scaled_aabb_min_out, float* inv_cell_sizes_out,
+    float* inv_radii_out, int64_t* keys_out, int32_t* sorted_indices_out,
+    int64_t* sorted_keys_out, float* sorted_points_out,
+    int32_t* sorted_batch_ids_out, int32_t* ds_out, int32_t* ranges_out,
+    void* ws, size_t ws_bytes, int32_t* num_cells_host_out,
+    int64_t* total_out);
+
 /* ---- FindNeighbors fill pass with original ids and densities --------------
  * tfgpc_find_neighbors_fill_ordered (sample_order may be NULL) that, in the same
  * pass, also writes what pylib computes from the neighbor list afterwards:

@@ -255,6 +255,22 @@ extern "C" int tfgpc_build_grid_ds(void* stream, int D, int64_t n, const int64_t
   return TFGPC_OK;
 }
 
+namespace tfgpc {
+// BuildGridDs into an array sized for `capacity` tubes, without the cell counts
+// on the host (grid_neighborhood.cu): the tubes occupy the first batch * C0 * C1
+// entries, whatever C0 and C1 turn out to be.
+int build_grid_ds_capacity(cudaStream_t st, int D, int64_t n, const int64_t* sorted_keys,
+                           const int32_t* num_cells, int64_t capacity, int32_t* ds_out) {
+  TFGPC_CUDA(cudaMemsetAsync(ds_out, 0, sizeof(int32_t) * 2 * (size_t)capacity, st));
+  if (n == 0) return TFGPC_OK;
+  ProfScope prof(st, "build_grid_ds");
+  TFGPC_DIM_SWITCH(D, build_grid_ds_kernel<kD><<<blocks_for(n, 256), 256, 0, st>>>(
+      n, sorted_keys, num_cells, capacity, (int2*)ds_out));
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+}  // namespace tfgpc
+
 extern "C" int tfgpc_compute_aabb(void* stream, int D, int64_t n, const float* points,
                                   const int32_t* batch_ids, int64_t batch_size, float* aabb_min_out,
                                   float* aabb_max_out) {

@@ -234,17 +234,20 @@ extern "C" size_t tfgpc_find_neighbors_workspace_bytes(int64_t ns) {
   return align_up((size_t)(scan_block_sums_elems(ns) + 1) * sizeof(int64_t), 256) + 256;
 }
 
-static int find_neighbors_count_impl(bool mapped_read, const int32_t* order,
+// read_mode 0: plain copy of the total (allocates nothing), 1: read through the
+// mapped page, 2: no read -- *total_dev_out receives the device address of the
+// 64-bit total and the call does not block
+static int find_neighbors_count_impl(int read_mode, const int32_t* order,
     void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
     const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
-    void* ws, size_t ws_bytes, int64_t* total_out) {
+    void* ws, size_t ws_bytes, int64_t* total_out, int64_t** total_dev_out = nullptr) {
   int rc = check_fn_args(D, ns, n, batch_size, max_neighs);
   if (rc) return rc;
   TFGPC_REQUIRE(total_out, "FindNeighbors got a null pointer");
   *total_out = 0;
-  if (ns == 0) return TFGPC_OK;
+  if (ns == 0) return TFGPC_OK;   // (read_mode 2: the caller treats ns == 0 itself)
   TFGPC_REQUIRE(samples && samples_batch_ids && ds && num_cells && scaled_aabb_min &&
                 inv_cell_sizes && inv_radii && ranges_out && ws && (n == 0 || (points && point_keys)),
                 "FindNeighbors got a null pointer");
@@ -268,8 +271,12 @@ static int find_neighbors_count_impl(bool mapped_read, const int32_t* order,
   TFGPC_LAUNCH_CHECK();
   rc = inclusive_scan_i32(st, ranges_out, ranges_out, ns, block_sums, total_dev);
   if (rc) return rc;
+  if (read_mode == 2) {
+    *total_dev_out = total_dev;
+    return TFGPC_OK;
+  }
   int64_t total = 0;
-  if (mapped_read) {
+  if (read_mode == 1) {
     rc = read_small(st, total_dev, sizeof(int64_t), &total);
     if (rc) return rc;
   } else {
@@ -285,13 +292,31 @@ static int find_neighbors_count_impl(bool mapped_read, const int32_t* order,
   return TFGPC_OK;
 }
 
+namespace tfgpc {
+// The count pass without its blocking read (grid_neighborhood.cu reads the total
+// together with the cell counts).
+int find_neighbors_count_async(const int32_t* order, void* stream, int D, int64_t ns,
+                               const float* samples, const int32_t* samples_batch_ids, int64_t n,
+                               const float* points, const int64_t* point_keys, const int32_t* ds,
+                               int64_t batch_size, const int32_t* num_cells,
+                               const float* scaled_aabb_min, const float* inv_cell_sizes,
+                               const float* inv_radii, int max_neighs, int32_t* ranges_out, void* ws,
+                               size_t ws_bytes, int64_t** total_dev_out) {
+  int64_t unused = 0;
+  return find_neighbors_count_impl(2, order, stream, D, ns, samples, samples_batch_ids, n, points,
+                                   point_keys, ds, batch_size, num_cells, scaled_aabb_min,
+                                   inv_cell_sizes, inv_radii, max_neighs, ranges_out, ws, ws_bytes,
+                                   &unused, total_dev_out);
+}
+}  // namespace tfgpc
+
 extern "C" int tfgpc_find_neighbors_count(
     void* stream, int D, int64_t ns, const float* samples, const int32_t* samples_batch_ids,
     int64_t n, const float* points, const int64_t* point_keys, const int32_t* ds,
     int64_t batch_size, const int32_t* num_cells, const float* scaled_aabb_min,
     const float* inv_cell_sizes, const float* inv_radii, int max_neighs, int32_t* ranges_out,
     void* ws, size_t ws_bytes, int64_t* total_out) {
-  return find_neighbors_count_impl(true, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
+  return find_neighbors_count_impl(1, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
                                   point_keys, ds, batch_size, num_cells, scaled_aabb_min,
                                   inv_cell_sizes, inv_radii, max_neighs, ranges_out, ws, ws_bytes,
                                   total_out);
@@ -373,7 +398,7 @@ extern "C" int tfgpc_find_neighbors_count_ordered(
     const int32_t* ds, int64_t batch_size, const int32_t* num_cells,
     const float* scaled_aabb_min, const float* inv_cell_sizes, const float* inv_radii,
     int max_neighs, int32_t* ranges_out, void* ws, size_t ws_bytes, int64_t* total_out) {
-  return find_neighbors_count_impl(true, sample_order, stream, D, ns, samples, samples_batch_ids,
+  return find_neighbors_count_impl(1, sample_order, stream, D, ns, samples, samples_batch_ids,
                                    n, points, point_keys, ds, batch_size, num_cells,
                                    scaled_aabb_min, inv_cell_sizes, inv_radii, max_neighs,
                                    ranges_out, ws, ws_bytes, total_out);
@@ -497,7 +522,7 @@ extern "C" int tfgpc_find_neighbors_count_static(
                 kStaticScratchBytes, (long long)ns);
   // Nothing in the scratch has to start at zero: the scan overwrites every tile
   // sum and the total before it reads them, so stale contents are harmless.
-  return find_neighbors_count_impl(false, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
+  return find_neighbors_count_impl(0, nullptr, stream, D, ns, samples, samples_batch_ids, n, points,
                                   point_keys, ds, batch_size, num_cells, scaled_aabb_min,
                                   inv_cell_sizes, inv_radii, max_neighs, ranges_out, scratch,
                                   kStaticScratchBytes, total_out);

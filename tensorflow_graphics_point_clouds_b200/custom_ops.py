@@ -211,6 +211,73 @@ def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, 
   return count.ranges, find_neighbors_fill(count)
 
 
+def grid_neighborhood_count(points, batch_ids, batch_size, cell_sizes, radii, max_cells,
+                            samples=None, samples_batch_ids=None, samples_are_points=0,
+                            max_neighs=0):
+  """Grid of a cloud and the count pass of one neighborhood on it in a single
+  call with a single blocking read (tfgpc_grid_neighborhood_count).  cell_sizes
+  and radii are sequences of D floats (host).  Returns a dict with the grid's
+  arrays, the NeighborCount of the neighborhood and the cell counts on the host;
+  raises TfgpcError(3) if a dimension needs more than max_cells cells (the
+  exception's `num_cells` attribute then holds what the grid asked for)."""
+  points, bid = _f32(points), _i32(batch_ids)
+  _dev_check(points, bid)
+  n, d = points.shape
+  dev = points.device
+  if samples_are_points == 0:
+    samples, sbid = _f32(samples), _i32(samples_batch_ids)
+    ns = samples.shape[0]
+  else:
+    samples = sbid = None
+    ns = n
+  b = int(batch_size)
+  lib = _lib.lib()
+  f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+  i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=dev)
+  i64 = lambda *shape: torch.empty(shape, dtype=torch.int64, device=dev)
+  g = dict(aabb_min=f32(b, d), aabb_max=f32(b, d), num_cells=i32(d), scaled_aabb_min=f32(b, d),
+           inv_cell_sizes=f32(d), inv_radii=f32(d), keys=i64(n), sorted_indices=i32(n),
+           sorted_keys=i64(n), sorted_points=f32(n, d), sorted_batch_ids=i32(n))
+  ds_elems = lib.tfgpc_grid_neighborhood_ds_elems(c_int(d), c_i64(b), c_int(int(max_cells)))
+  ds_flat = i32(ds_elems)
+  ranges = i32(ns)
+  nbytes = lib.tfgpc_grid_neighborhood_workspace_bytes(c_i64(n), c_i64(ns))
+  ws = _workspace(nbytes, dev)
+  cs = (ctypes.c_float * d)(*[float(v) for v in cell_sizes])
+  rr = (ctypes.c_float * d)(*[float(v) for v in radii])
+  nc_host = (ctypes.c_int32 * d)()
+  total = c_i64(0)
+  code = lib.tfgpc_grid_neighborhood_count(
+      _stream(), c_int(d), c_i64(n), ptr(points), ptr(bid), c_i64(b), cs, rr, c_int(int(max_cells)),
+      c_i64(ns), ptr(samples), ptr(sbid), c_int(int(samples_are_points)), c_int(int(max_neighs)),
+      ptr(g["aabb_min"]), ptr(g["aabb_max"]), ptr(g["num_cells"]), ptr(g["scaled_aabb_min"]),
+      ptr(g["inv_cell_sizes"]), ptr(g["inv_radii"]), ptr(g["keys"]), ptr(g["sorted_indices"]),
+      ptr(g["sorted_keys"]), ptr(g["sorted_points"]), ptr(g["sorted_batch_ids"]), ptr(ds_flat),
+      ptr(ranges), ptr(ws), c_sz(nbytes), nc_host, ctypes.byref(total))
+  g["num_cells_host"] = torch.tensor(list(nc_host), dtype=torch.int32)
+  if code != 0:
+    err = _lib.TfgpcError(code, lib.tfgpc_last_error().decode())
+    err.num_cells = list(nc_host)
+    raise err
+  c0, c1 = int(nc_host[0]), int(nc_host[1])
+  g["ds"] = ds_flat[:b * c0 * c1 * 2].reshape(b, c0, c1, 2)
+  # what the fill pass needs again (see find_neighbors_count)
+  if samples_are_points == 1:
+    smp, sb, order = points, bid, g["sorted_indices"]
+  elif samples_are_points == 2:
+    smp, sb, order = g["sorted_points"], g["sorted_batch_ids"], None
+  else:
+    smp, sb, order = samples, sbid, None
+  keep = (smp, sb, g["sorted_points"], g["sorted_keys"], ds_flat, g["num_cells"],
+          g["scaled_aabb_min"], g["inv_cell_sizes"], g["inv_radii"])
+  head = (c_int(d), c_i64(ns), ptr(smp), ptr(sb))
+  tail = (c_i64(n), ptr(g["sorted_points"]), ptr(g["sorted_keys"]), ptr(ds_flat), c_i64(b),
+          ptr(g["num_cells"]), ptr(g["scaled_aabb_min"]), ptr(g["inv_cell_sizes"]),
+          ptr(g["inv_radii"]), c_int(int(max_neighs)))
+  g["count"] = NeighborCount(ranges, int(total.value), (head, tail, keep), order, d)
+  return g
+
+
 def original_neighbor_ids(neighbors, sorted_indices, pdf_by_original=None):
   """(sorted_indices[neighbors[:, 0]], neighbors[:, 1]) and, optionally, the
   density of every pair's neighbor point (tfgpc_original_neighbor_ids)."""

@@ -335,8 +335,7 @@ class MCConv:
     """MCConv.py:254-261: grid of the input cloud, neighborhood around the
     output points."""
     from . import pc
-    grid = pc.Grid(point_cloud_in, radius)
-    return pc.Neighborhood(grid, radius, point_cloud_out)
+    return pc.grid_neighborhood(point_cloud_in, radius, point_cloud_out)
 
   def forward(self, features, point_cloud_in, point_cloud_out, radius, neighborhood=None,
               bandwidth=0.2, keep_for_backward=True):

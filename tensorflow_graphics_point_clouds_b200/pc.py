@@ -253,6 +253,83 @@ class Neighborhood:
     return out
 
 
+# Upper bound of cells per dimension that grid_neighborhood sizes its tube array
+# and sort keys for, per (dimension, batch size): it starts at 64 and is raised
+# to what a grid asked for when one did not fit.
+_MAX_CELLS = {}
+
+
+def grid_neighborhood(point_cloud, radius, point_cloud_sample=None, max_neighbors=0):
+  """Grid(point_cloud, radius) and Neighborhood(grid, radius, point_cloud_sample,
+  max_neighbors) built by ONE library call with ONE blocking read
+  (tfgpc_grid_neighborhood_count) where pylib's two constructors read back twice
+  (Grid.py:44-48 cell counts, Neighborhood.py:242-245 pair count).  Same objects,
+  same contents.  A cloud that is one shard of a distributed batch (num_cells_reduce
+  set) takes the separate constructors, which can reduce the cell counts over the
+  ranks in between."""
+  pc = point_cloud
+  if pc._num_cells_reduce is not None or pc._points.shape[0] == 0:
+    return Neighborhood(Grid(pc, radius), radius, point_cloud_sample, max_neighbors)
+  dev = pc._points.device
+  d = pc._dimension
+  radii = _to_dims(radius, d, dev)
+  # (a radius given as a device tensor costs a read of its own)
+  radii_host = torch.as_tensor(radius, dtype=torch.float32).reshape(-1).cpu().tolist()
+  if len(radii_host) == 1:
+    radii_host = radii_host * d
+  if point_cloud_sample is None:
+    mode, smp = 2, None
+  elif point_cloud_sample is pc:
+    mode, smp = 1, None
+  else:
+    mode, smp = 0, point_cloud_sample
+  key = (d, pc._batch_size)
+  max_cells = _MAX_CELLS.get(key, 64)
+  while True:
+    try:
+      g = ops.grid_neighborhood_count(
+          pc._points, pc._batch_ids, pc._batch_size, radii_host, radii_host, max_cells,
+          None if smp is None else smp._points, None if smp is None else smp._batch_ids,
+          mode, max_neighbors)
+      break
+    except ops._lib.TfgpcError as err:
+      asked = max(getattr(err, 'num_cells', [0]))
+      if err.code != 3 or asked <= max_cells:
+        raise
+      max_cells = min(4096, 1 << (asked - 1).bit_length())
+      _MAX_CELLS[key] = max_cells
+  grid = object.__new__(Grid)
+  grid._point_cloud = pc
+  grid._batch_size = pc._batch_size
+  grid._cell_sizes = radii
+  grid._aabb_min, grid._aabb_max = g["aabb_min"], g["aabb_max"]
+  if pc._aabb is None:
+    pc._aabb = (grid._aabb_min, grid._aabb_max)
+  grid._num_cells = g["num_cells"]
+  grid._num_cells_host = g["num_cells_host"]
+  grid._scaled_aabb_min = g["scaled_aabb_min"]
+  grid._inv_cell_sizes = g["inv_cell_sizes"]
+  grid._cur_keys = g["keys"]
+  grid._sorted_indices, grid._sorted_keys = g["sorted_indices"], g["sorted_keys"]
+  grid._sorted_points, grid._sorted_batch_ids = g["sorted_points"], g["sorted_batch_ids"]
+  grid._fast_DS = g["ds"]
+  nb = object.__new__(Neighborhood)
+  nb._radii = radii
+  nb._equal_samples = point_cloud_sample is None
+  nb._point_cloud_sampled = (PointCloud(grid._sorted_points, grid._sorted_batch_ids,
+                                        grid._batch_size)
+                             if point_cloud_sample is None else point_cloud_sample)
+  nb._grid = grid
+  nb.max_neighbors = max_neighbors
+  nb._sample_order = grid._sorted_indices if mode == 1 else None
+  nb._count = g["count"]
+  nb._samples_neigh_ranges = nb._count.ranges
+  nb._nbrs = nb._orig_ids = nb._pdf = nb._point_pdf = nb._sample_pdf = None
+  nb._pdf_ready = False
+  nb._transposed = None
+  return nb
+
+
 def sample(neighborhood, sample_mode='poisson'):
   """sampling.py:123-150 -> (PointCloud of the samples, original indices or None)."""
   mode = SAMPLE_MODES[sample_mode.lower()]
@@ -278,8 +355,7 @@ class PointHierarchy:
     self._sample_indices = []
     cur = point_cloud
     for cs in cell_sizes:
-      grid = Grid(cur, cs)
-      neigh = Neighborhood(grid, grid._cell_sizes)
+      neigh = grid_neighborhood(cur, cs)
       cur, idx = sample(neigh, sample_mode)
       self._neighborhoods.append(neigh)
       self._point_clouds.append(cur)

@@ -152,12 +152,8 @@ def test_mcconv_layer_matches_oracle(d, g, h):
   close(out.cpu().numpy(), ref_out)
   close(dfeat.cpu().numpy(), ref_df)
   close(dwf.cpu().numpy(), ref_dwf)
-  # The 64 kernel-MLP gradients are sums over all M pairs of dbasis / pdf * slope:
-  # dbasis itself carries the 3-pass bf16 error of two products in a row (up to
-  # ~6e-5 per value), and a pre-activation within fp32 rounding of zero takes the
-  # other slope than in the float64 reference; measured up to 1.4e-4.
-  close(dw1.cpu().numpy(), ref_dw1, rel=2e-4)
-  close(db1.cpu().numpy(), ref_db1, rel=2e-4)
+  close(dw1.cpu().numpy(), ref_dw1)         # measured: 2.0e-5
+  close(db1.cpu().numpy(), ref_db1)         # measured: 2.1e-5
 
 
 def test_bounded_wait_runs_out_and_is_reported():
@@ -234,16 +230,16 @@ def test_mcconv_deep_kernel_mlp_and_point_gradients(hidden, g, act, own):
   close(dfeat.cpu().numpy(), ref["d_features"])
   close(dwf.cpu().numpy(), ref["d_wf"])
   for a, r in zip(dws, ref["d_weights"]):
-    close(a.cpu().numpy(), r, rel=2e-4)
+    close(a.cpu().numpy(), r)
   for a, r in zip(dbs, ref["d_biases"]):
-    close(a.cpu().numpy(), r, rel=2e-4)
-  close(dpdf.cpu().numpy(), ref["d_pdf"], rel=2e-4)
+    close(a.cpu().numpy(), r)
+  close(dpdf.cpu().numpy(), ref["d_pdf"])
   if own:
     assert dpin is dpout           # one cloud: one gradient, the sum of both roles
-    close(dpin.cpu().numpy(), ref["d_points_in"] + ref["d_points_out"], rel=2e-4)
+    close(dpin.cpu().numpy(), ref["d_points_in"] + ref["d_points_out"])
   else:
-    close(dpin.cpu().numpy(), ref["d_points_in"], rel=2e-4)
-    close(dpout.cpu().numpy(), ref["d_points_out"], rel=2e-4)
+    close(dpin.cpu().numpy(), ref["d_points_in"])
+    close(dpout.cpu().numpy(), ref["d_points_out"])
 
 
 @pytest.mark.parametrize("own", [True, False])
@@ -273,4 +269,4 @@ def test_pdf_point_grads_follow_the_reference_chain(own):
                                         inv_bw, inv, per_point.astype(F32), 0)
   ref = np.empty_like(ref_sorted)
   ref[g_ref.sorted_indices] = ref_sorted
-  close(got, ref, rel=2e-4)
+  close(got, ref)

@@ -182,13 +182,7 @@ def test_compute_pdf_and_grads(d, mode):
                                    inv_r, gvec, mode)
   got_g = ops.compute_pdf_pt_grads(g._sorted_points, nb._neighbors, nb._samples_neigh_ranges,
                                    t(inv_bw), t(inv_r), t(gvec), mode)
-  # The point gradient is a sum of ~n/10 signed terms per coordinate, scattered by
-  # fp32 atomics in arbitrary order here and summed sequentially in the oracle:
-  # measured up to 1.3e-4 of max(|ref|, rms) where the terms cancel to a few
-  # percent of their size (same arithmetic per term; the reference's own kernel
-  # differs from the oracle by up to 4e-4 on such sums,
-  # tests/test_reference_kernels_gpu.py).
-  close(got_g.cpu().numpy(), ref_g, rel=2e-4)
+  close(got_g.cpu().numpy(), ref_g)      # measured: 1.2e-6
 
 
 def test_pdf_matches_sklearn_kde():
@@ -489,3 +483,53 @@ def test_fused_fill_matches_separate_passes(mode):
   nb_ref = pr.Neighborhood(g_ref, 0.15, pts, bid)
   close(nb.get_pdf().cpu().numpy(), nb_ref.get_pdf(bandwidth=0.2, mode=mode))
   close(nb.point_pdf().cpu().numpy(), nb_ref.point_pdf)
+
+
+@pytest.mark.parametrize("d,radius", [(2, 0.05), (3, 0.12), (4, 0.3)])
+@pytest.mark.parametrize("samples", ["self", "points", "other"])
+def test_grid_neighborhood_one_call(d, radius, samples):
+  """Grid and Neighborhood from the single-call entry equal the oracle's (and so
+  the separate constructors'), bit for bit, for the three kinds of samples."""
+  rng = np.random.default_rng(31 + d)
+  b = 3
+  pts, bid = random_cloud(rng, b, 3000, d)
+  g_ref = pr.Grid(pts, bid, b, radius)
+  cloud = pc.PointCloud(t(pts), t(bid), b)
+  if samples == "self":
+    nb = pc.grid_neighborhood(cloud, radius)
+    nb_ref = pr.Neighborhood(g_ref, radius)
+  elif samples == "points":
+    nb = pc.grid_neighborhood(cloud, radius, cloud, max_neighbors=7)
+    nb_ref = pr.Neighborhood(g_ref, radius, pts, bid, 7)
+  else:
+    smp, sbid = random_cloud(rng, b, 500, d)
+    nb = pc.grid_neighborhood(cloud, radius, pc.PointCloud(t(smp), t(sbid), b))
+    nb_ref = pr.Neighborhood(g_ref, radius, smp, sbid)
+  assert_grid_equal(g_ref, nb._grid)
+  assert np.array_equal(nb._grid._num_cells_host.numpy(), g_ref.num_cells)
+  assert_neigh_equal(nb_ref, nb)
+  assert nb.num_pairs == len(nb_ref.neighbors)
+  # what follows a neighborhood works on it as on one built by the constructors
+  two = pc.Neighborhood(pc.Grid(cloud, radius), radius,
+                        None if samples == "self" else nb._point_cloud_sampled,
+                        7 if samples == "points" else 0)
+  assert torch.equal(nb.get_pdf(), two.get_pdf())
+
+
+def test_grid_neighborhood_repeats_with_larger_bound():
+  """A grid with more cells per dimension than the call was sized for is reported
+  (status 3 with the counts asked for) and the wrapper repeats the call."""
+  rng = np.random.default_rng(5)
+  pts, bid = random_cloud(rng, 2, 4000, 2)
+  cloud = pc.PointCloud(t(pts), t(bid), 2)
+  with pytest.raises(TfgpcError) as e:
+    ops.grid_neighborhood_count(cloud._points, cloud._batch_ids, 2, [0.004, 0.004],
+                                [0.004, 0.004], 64, samples_are_points=2)
+  assert e.value.code == 3 and max(e.value.num_cells) > 64
+  pc._MAX_CELLS.pop((2, 2), None)
+  nb = pc.grid_neighborhood(cloud, 0.004)
+  assert pc._MAX_CELLS[(2, 2)] >= max(e.value.num_cells)
+  g_ref = pr.Grid(pts, bid, 2, 0.004)
+  assert_grid_equal(g_ref, nb._grid)
+  assert_neigh_equal(pr.Neighborhood(g_ref, 0.004), nb)
+  pc._MAX_CELLS.pop((2, 2), None)
