@@ -270,7 +270,12 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
               umma_commit(smem_u32(&bars->f_empty[slot]));
             }
           } else {
-            // (2) D2 = dXcat * Bx^T: reduction over the 64 (slot, k) columns
+            // (2) D2 = dXcat * Bx^T: reduction over the 64 (slot, k) columns.  Only
+            // the columns of rows that exist are computed (N in steps of 16): the
+            // tensor core reads that much less of Bx from shared memory.
+            const int rows_b = min(kRows, t.rows - b * kRows);
+            const uint32_t n16 = (uint32_t)((rows_b + 15) & ~15);
+            const uint32_t idesc2n = (idesc2 & ~(0x3Fu << 17)) | ((n16 >> 3) << 17);
             mbar_wait(smem_u32(&bars->bx_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
             fence_proxy_async();
             tc_fence_after();
@@ -282,9 +287,9 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
               const uint64_t da_mid = make_desc(dx_mid + kk * 32, 16, 1024);
               const uint64_t db_hi = make_desc(bx_hi + kk * 32, 16, 1024);
               const uint64_t db_mid = make_desc(bx_mid + kk * 32, 16, 1024);
-              umma_bf16(d2, da_hi, db_mid, idesc2, accumulate);
-              umma_bf16(d2, da_mid, db_hi, idesc2, 1u);
-              umma_bf16(d2, da_hi, db_hi, idesc2, 1u);
+              umma_bf16(d2, da_hi, db_mid, idesc2n, accumulate);
+              umma_bf16(d2, da_mid, db_hi, idesc2n, 1u);
+              umma_bf16(d2, da_hi, db_hi, idesc2n, 1u);
               accumulate = 1u;
             }
             umma_commit(smem_u32(&bars->bx_empty[abuf]));

@@ -146,6 +146,22 @@ aabb_kernel(int64_t n, const float* __restrict__ pts, const int32_t* __restrict_
       hi[d] = fmaxf(hi[d], v);
     }
   }
+  // The common case, a whole warp inside one cloud: fold the 32 boxes with
+  // shuffles and let one lane issue the atomics (min and max are exact and
+  // order-independent, so the result is the same).
+  const unsigned active = __activemask();
+  const int cur0 = __shfl_sync(active, cur, __ffs(active) - 1);
+  if (active == 0xffffffffu && __all_sync(active, cur == cur0)) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        lo[d] = fminf(lo[d], __shfl_xor_sync(0xffffffffu, lo[d], o));
+        hi[d] = fmaxf(hi[d], __shfl_xor_sync(0xffffffffu, hi[d], o));
+      }
+    }
+    if ((threadIdx.x & 31) != 0) return;
+  }
   if (cur >= 0 && cur < batch_size) {
 #pragma unroll
     for (int d = 0; d < D; ++d) {
