@@ -788,8 +788,7 @@ def side_workload_line(args, device_index):
   def step(record):
     cloud = pc.PointCloud(tp, tb, batch)
     if args.workload == "neighbors":
-      grid = pc.Grid(cloud, radii[0])
-      neigh = pc.Neighborhood(grid, radii[0])
+      neigh = pc.grid_neighborhood(cloud, radii[0])
       neigh.compute_pdf(bandwidth=0.2, mode=0)
       if record:
         sizes.append((tp.shape[0], neigh._neighbors.shape[0], 0))
@@ -798,8 +797,7 @@ def side_workload_line(args, device_index):
     for mode in ("poisson", "average"):
       cur = cloud
       for r in radii:
-        grid = pc.Grid(cur, r)
-        neigh = pc.Neighborhood(grid, r)
+        neigh = pc.grid_neighborhood(cur, r)
         nxt, _ = pc.sample(neigh, mode)
         if record:
           sizes.append((cur._points.shape[0], neigh._neighbors.shape[0], nxt._points.shape[0]))

@@ -190,14 +190,30 @@ int tfgpc_original_neighbor_ids(void* stream, int64_t M,
  * as it is), ranges [ns]; [host] num_cells_host_out [D], total_out.  Returns
  * TFGPC_ENOMEM (and the cell counts the grid asked for) if max_cells was too
  * small: repeat with a larger bound.  Follow with one of the
- * tfgpc_find_neighbors_fill* entries. */
+ * tfgpc_find_neighbors_fill* entries.
+ * A cloud that is one shard of a batch held by several processes needs the cell
+ * counts of the whole batch (Grid.py:44-48: the maximum over all clouds):
+ * tfgpc_grid_cells computes the boxes, this shard's counts and the scaled minima
+ * / inverse sizes WITHOUT blocking; the caller reduces num_cells over the
+ * processes on the same stream (a max all-reduce) and passes the result as
+ * num_cells_in [D, device] together with the arrays tfgpc_grid_cells wrote
+ * (aabb_*_out, scaled_aabb_min_out, inv_*_out are then inputs).  num_cells_in
+ * NULL: the entry computes all of that itself.  num_cells_in is not modified
+ * and must not alias num_cells_out, which receives the counts in use. */
 size_t tfgpc_grid_neighborhood_workspace_bytes(int64_t n, int64_t ns);
 size_t tfgpc_grid_neighborhood_ds_elems(int D, int64_t batch_size,
                                         int max_cells);
+int tfgpc_grid_cells(void* stream, int D, int64_t n, const float* points,
+                     const int32_t* batch_ids, int64_t batch_size,
+                     const float* cell_sizes, const float* radii,
+                     float* aabb_min_out, float* aabb_max_out,
+                     int32_t* num_cells_out, float* scaled_aabb_min_out,
+                     float* inv_cell_sizes_out, float* inv_radii_out);
 int tfgpc_grid_neighborhood_count(
     void* stream, int D, int64_t n, const float* points,
     const int32_t* batch_ids, int64_t batch_size, const float* cell_sizes,
-    const float* radii, int max_cells, int64_t ns, const float* samples,
+    const float* radii, int max_cells, const int32_t* num_cells_in,
+    int64_t ns, const float* samples,
     const int32_t* samples_batch_ids, int samples_are_points, int max_neighs,
     float* aabb_min_out, float* aabb_max_out, int32_t* num_cells_out,
     float* scaled_aabb_min_out, float* inv_cell_sizes_out,

@@ -43,6 +43,7 @@ SYMBOLS = {
     "tfgpc_grid_neighborhood_workspace_bytes": c_sz,
     "tfgpc_grid_neighborhood_ds_elems": c_sz,
     "tfgpc_grid_neighborhood_count": c_int,
+    "tfgpc_grid_cells": c_int,
     "tfgpc_find_neighbors_fill_fused": c_int,
     "tfgpc_original_neighbor_ids": c_int,
     "tfgpc_find_neighbors_static_max_samples": c_i64,

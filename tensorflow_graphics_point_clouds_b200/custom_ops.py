@@ -211,15 +211,43 @@ def find_neighbors(samples, samples_batch_ids, points, point_keys, grid_acc_ds, 
   return count.ranges, find_neighbors_fill(count)
 
 
+def _host_floats(values, d):
+  return (ctypes.c_float * d)(*[float(v) for v in values])
+
+
+def grid_cells(points, batch_ids, batch_size, cell_sizes, radii):
+  """Bounding boxes (widened by 1e-9), cells per dimension, scaled box minima and
+  inverse cell sizes / radii of a cloud, all left on the device, without a
+  blocking read (tfgpc_grid_cells): the part of Grid.py:38-48 before the cell
+  counts are needed on the host.  For a shard of a distributed batch the caller
+  max-reduces `num_cells` over the ranks and hands the dict to
+  grid_neighborhood_count(cells=...)."""
+  points, bid = _f32(points), _i32(batch_ids)
+  _dev_check(points, bid)
+  n, d = points.shape
+  dev, b = points.device, int(batch_size)
+  f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+  c = dict(aabb_min=f32(b, d), aabb_max=f32(b, d),
+           num_cells=torch.empty(d, dtype=torch.int32, device=dev), scaled_aabb_min=f32(b, d),
+           inv_cell_sizes=f32(d), inv_radii=f32(d))
+  _lib.check(_lib.lib().tfgpc_grid_cells(
+      _stream(), c_int(d), c_i64(n), ptr(points), ptr(bid), c_i64(b), _host_floats(cell_sizes, d),
+      _host_floats(radii, d), ptr(c["aabb_min"]), ptr(c["aabb_max"]), ptr(c["num_cells"]),
+      ptr(c["scaled_aabb_min"]), ptr(c["inv_cell_sizes"]), ptr(c["inv_radii"])))
+  return c
+
+
 def grid_neighborhood_count(points, batch_ids, batch_size, cell_sizes, radii, max_cells,
                             samples=None, samples_batch_ids=None, samples_are_points=0,
-                            max_neighs=0):
+                            max_neighs=0, cells=None):
   """Grid of a cloud and the count pass of one neighborhood on it in a single
   call with a single blocking read (tfgpc_grid_neighborhood_count).  cell_sizes
   and radii are sequences of D floats (host).  Returns a dict with the grid's
   arrays, the NeighborCount of the neighborhood and the cell counts on the host;
   raises TfgpcError(3) if a dimension needs more than max_cells cells (the
-  exception's `num_cells` attribute then holds what the grid asked for)."""
+  exception's `num_cells` attribute then holds what the grid asked for).
+  cells: the dict of grid_cells for this cloud, its num_cells possibly reduced
+  over the shards of a batch; the call then continues from those counts."""
   points, bid = _f32(points), _i32(batch_ids)
   _dev_check(points, bid)
   n, d = points.shape
@@ -235,21 +263,27 @@ def grid_neighborhood_count(points, batch_ids, batch_size, cell_sizes, radii, ma
   f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
   i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=dev)
   i64 = lambda *shape: torch.empty(shape, dtype=torch.int64, device=dev)
-  g = dict(aabb_min=f32(b, d), aabb_max=f32(b, d), num_cells=i32(d), scaled_aabb_min=f32(b, d),
-           inv_cell_sizes=f32(d), inv_radii=f32(d), keys=i64(n), sorted_indices=i32(n),
-           sorted_keys=i64(n), sorted_points=f32(n, d), sorted_batch_ids=i32(n))
+  g = dict(keys=i64(n), sorted_indices=i32(n), sorted_keys=i64(n), sorted_points=f32(n, d),
+           sorted_batch_ids=i32(n), num_cells=i32(d))
+  if cells is None:
+    g.update(aabb_min=f32(b, d), aabb_max=f32(b, d), scaled_aabb_min=f32(b, d),
+             inv_cell_sizes=f32(d), inv_radii=f32(d))
+    cells_in = None
+  else:
+    g.update({k: cells[k] for k in ("aabb_min", "aabb_max", "scaled_aabb_min", "inv_cell_sizes",
+                                     "inv_radii")})
+    cells_in = _i32(cells["num_cells"])
   ds_elems = lib.tfgpc_grid_neighborhood_ds_elems(c_int(d), c_i64(b), c_int(int(max_cells)))
   ds_flat = i32(ds_elems)
   ranges = i32(ns)
   nbytes = lib.tfgpc_grid_neighborhood_workspace_bytes(c_i64(n), c_i64(ns))
   ws = _workspace(nbytes, dev)
-  cs = (ctypes.c_float * d)(*[float(v) for v in cell_sizes])
-  rr = (ctypes.c_float * d)(*[float(v) for v in radii])
+  cs, rr = _host_floats(cell_sizes, d), _host_floats(radii, d)
   nc_host = (ctypes.c_int32 * d)()
   total = c_i64(0)
   code = lib.tfgpc_grid_neighborhood_count(
       _stream(), c_int(d), c_i64(n), ptr(points), ptr(bid), c_i64(b), cs, rr, c_int(int(max_cells)),
-      c_i64(ns), ptr(samples), ptr(sbid), c_int(int(samples_are_points)), c_int(int(max_neighs)),
+      ptr(cells_in), c_i64(ns), ptr(samples), ptr(sbid), c_int(int(samples_are_points)), c_int(int(max_neighs)),
       ptr(g["aabb_min"]), ptr(g["aabb_max"]), ptr(g["num_cells"]), ptr(g["scaled_aabb_min"]),
       ptr(g["inv_cell_sizes"]), ptr(g["inv_radii"]), ptr(g["keys"]), ptr(g["sorted_indices"]),
       ptr(g["sorted_keys"]), ptr(g["sorted_points"]), ptr(g["sorted_batch_ids"]), ptr(ds_flat),

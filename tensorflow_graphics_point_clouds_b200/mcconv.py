@@ -494,8 +494,7 @@ class _ProjectedConv:
     if neighborhood is not None:
       return neighborhood
     from . import pc
-    grid = pc.Grid(point_cloud_in, radius)
-    return pc.Neighborhood(grid, radius, point_cloud_out)
+    return pc.grid_neighborhood(point_cloud_in, radius, point_cloud_out)
 
   def _project(self, basis, features, neigh, weights, ns, keep_for_backward):
     if self._op is None or self._op.ns != ns or self._op.backward_ws != keep_for_backward:

@@ -21,7 +21,25 @@ SAMPLE_MODES = {'average': 1, 'cell average': 1, 'cell_average': 1,
                 'poisson': 0, 'poisson disk': 0, 'poisson_disk': 0}
 
 
+# Small per-dimension constants (radii, bandwidths) given as Python numbers are
+# uploaded once per value and device: creating a device tensor from host data
+# blocks the host until the stream has drained, once per call otherwise.  The
+# cached tensors are never written to.
+_DIMS_CACHE = {}
+
+
 def _to_dims(value, dims, device):
+  if not torch.is_tensor(value):
+    flat = [float(v) for v in (value if hasattr(value, '__len__') else [value])]
+    key = (tuple(flat), dims, str(device))
+    t = _DIMS_CACHE.get(key)
+    if t is None:
+      if len(_DIMS_CACHE) > 256:
+        _DIMS_CACHE.clear()
+      t = torch.tensor(flat * dims if len(flat) == 1 else flat, dtype=torch.float32,
+                       device=device)
+      _DIMS_CACHE[key] = t
+    return t
   t = torch.as_tensor(value, dtype=torch.float32, device=device).reshape(-1)
   if t.shape[0] == 1:
     t = t.repeat(dims)
@@ -264,17 +282,18 @@ def grid_neighborhood(point_cloud, radius, point_cloud_sample=None, max_neighbor
   max_neighbors) built by ONE library call with ONE blocking read
   (tfgpc_grid_neighborhood_count) where pylib's two constructors read back twice
   (Grid.py:44-48 cell counts, Neighborhood.py:242-245 pair count).  Same objects,
-  same contents.  A cloud that is one shard of a distributed batch (num_cells_reduce
-  set) takes the separate constructors, which can reduce the cell counts over the
-  ranks in between."""
+  same contents.  For a cloud that is one shard of a distributed batch
+  (num_cells_reduce set) the cell counts are reduced over the ranks on the device,
+  between tfgpc_grid_cells and the main call: still one blocking read."""
   pc = point_cloud
-  if pc._num_cells_reduce is not None or pc._points.shape[0] == 0:
+  if pc._points.shape[0] == 0:
     return Neighborhood(Grid(pc, radius), radius, point_cloud_sample, max_neighbors)
   dev = pc._points.device
   d = pc._dimension
   radii = _to_dims(radius, d, dev)
   # (a radius given as a device tensor costs a read of its own)
-  radii_host = torch.as_tensor(radius, dtype=torch.float32).reshape(-1).cpu().tolist()
+  radii_host = (radius.detach().reshape(-1).cpu().tolist() if torch.is_tensor(radius) else
+                [float(v) for v in (radius if hasattr(radius, '__len__') else [radius])])
   if len(radii_host) == 1:
     radii_host = radii_host * d
   if point_cloud_sample is None:
@@ -285,12 +304,18 @@ def grid_neighborhood(point_cloud, radius, point_cloud_sample=None, max_neighbor
     mode, smp = 0, point_cloud_sample
   key = (d, pc._batch_size)
   max_cells = _MAX_CELLS.get(key, 64)
+  cells = None
+  if pc._num_cells_reduce is not None:
+    # (the reduced counts are the same on every rank, so every rank takes the same
+    # turns through the loop below; the reduction itself happens once)
+    cells = ops.grid_cells(pc._points, pc._batch_ids, pc._batch_size, radii_host, radii_host)
+    cells["num_cells"] = pc._num_cells_reduce(cells["num_cells"]).to(torch.int32)
   while True:
     try:
       g = ops.grid_neighborhood_count(
           pc._points, pc._batch_ids, pc._batch_size, radii_host, radii_host, max_cells,
           None if smp is None else smp._points, None if smp is None else smp._batch_ids,
-          mode, max_neighbors)
+          mode, max_neighbors, cells=cells)
       break
     except ops._lib.TfgpcError as err:
       asked = max(getattr(err, 'num_cells', [0]))

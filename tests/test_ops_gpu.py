@@ -533,3 +533,35 @@ def test_grid_neighborhood_repeats_with_larger_bound():
   assert_grid_equal(g_ref, nb._grid)
   assert_neigh_equal(pr.Neighborhood(g_ref, 0.004), nb)
   pc._MAX_CELLS.pop((2, 2), None)
+
+
+def test_grid_neighborhood_one_call_with_reduced_cell_counts():
+  """A shard of a distributed batch: the cell counts pass through the caller's
+  reduction on the device (here a stand-in that raises them, as a larger cloud on
+  another rank would) and the one-call form equals the separate constructors
+  given the same reduction."""
+  rng = np.random.default_rng(77)
+  b = 3
+  pts, bid = random_cloud(rng, b, 3000, 3)
+  pts *= np.array([0.6, 1.0, 0.8], F32)
+  other = torch.tensor([9, 7, 8], dtype=torch.int32, device=DEV)
+  calls = []
+
+  def reduce(counts):
+    calls.append(1)
+    return torch.maximum(counts, other)
+
+  cloud = pc.PointCloud(t(pts), t(bid), b, num_cells_reduce=reduce)
+  nb = pc.grid_neighborhood(cloud, 0.15, cloud)
+  assert len(calls) == 1
+  cloud2 = pc.PointCloud(t(pts), t(bid), b, num_cells_reduce=reduce)
+  g2 = pc.Grid(cloud2, 0.15)
+  nb2 = pc.Neighborhood(g2, 0.15, cloud2)
+  assert nb._grid._num_cells.cpu().tolist() == [9, 7, 8]
+  for name in ("_num_cells", "_scaled_aabb_min", "_cur_keys", "_sorted_indices", "_sorted_keys",
+               "_sorted_points", "_sorted_batch_ids"):
+    assert torch.equal(getattr(nb._grid, name), getattr(g2, name)), name
+  assert torch.equal(nb._grid.get_DS(), g2.get_DS())
+  assert torch.equal(nb._samples_neigh_ranges, nb2._samples_neigh_ranges)
+  assert torch.equal(nb._neighbors, nb2._neighbors)
+  assert torch.equal(nb._original_neigh_ids, nb2._original_neigh_ids)
