@@ -496,7 +496,13 @@ int tfgpc_mcconv_backward_grouped(void* stream, int K, int C, int Cout,
  * pdf_by_neighbor != 0: pdf is not the per-pair array but a table with one
  * density per point of points_in, read at nbr.x (what pylib gathers into the
  * per-pair array at Neighborhood.py:287); the same flag on every entry below.
+ * pdf_by_neighbor == 2 (these three entries, D == 3): points_in is the packed
+ * table of tfgpc_pack_points_density, [n_in,4] = (x, y, z, 1 / density),
+ * 16-byte aligned, and pdf is not read (may be NULL): one 16-byte gather per
+ * pair instead of four scattered loads; same results, bit for bit.
  * _grads: basis_grads [M,K] -> dw1_out [D,K], db1_out [K] (overwritten). */
+int tfgpc_pack_points_density(void* stream, int64_t n, const float* points,
+                              const float* pdf, float* packed_out);
 int tfgpc_kernel_basis(void* stream, int D, int K, int64_t M,
                        const float* points_in, const float* points_out,
                        const int32_t* neighbors, const float* pdf,

@@ -44,6 +44,7 @@ SYMBOLS = {
     "tfgpc_grid_neighborhood_ds_elems": c_sz,
     "tfgpc_grid_neighborhood_count": c_int,
     "tfgpc_grid_cells": c_int,
+    "tfgpc_pack_points_density": c_int,
     "tfgpc_find_neighbors_fill_fused": c_int,
     "tfgpc_original_neighbor_ids": c_int,
     "tfgpc_find_neighbors_static_max_samples": c_i64,

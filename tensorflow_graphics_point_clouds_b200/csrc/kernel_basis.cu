@@ -52,6 +52,38 @@ __device__ __forceinline__ void pair_diff(const float* __restrict__ p_in,
     diff[d] = (__ldg(p_in + (int64_t)nb.x * D + d) - __ldg(p_out + (int64_t)nb.y * D + d)) * inv_radius;
 }
 
+// diff and 1 / density of pair m.  pdf_mode 0: density per pair, 1: a table with
+// one density per point of p_in, 2 (D == 3): p_in is the packed table of
+// pack_points_density_kernel, (x, y, z, 1 / density) per point -- ONE 16-byte
+// gather per pair in place of three coordinate loads and a density load, which
+// matters because these kernels are bound by the number of scattered loads a warp
+// issues, not by bytes.
+template <int D>
+__device__ __forceinline__ float pair_inputs(const float* __restrict__ p_in,
+                                             const float* __restrict__ p_out,
+                                             const float* __restrict__ pdf, int2 nb, int64_t m,
+                                             float inv_radius, int pdf_mode, float* diff) {
+  if (D == 3 && pdf_mode == 2) {
+    const float4 pp = __ldg(reinterpret_cast<const float4*>(p_in) + nb.x);
+    const float* q = p_out + (int64_t)nb.y * 3;
+    diff[0] = (pp.x - __ldg(q)) * inv_radius;
+    diff[1] = (pp.y - __ldg(q + 1)) * inv_radius;
+    diff[2] = (pp.z - __ldg(q + 2)) * inv_radius;
+    return pp.w;
+  }
+  pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
+  return 1.0f / __ldg(pdf + (pdf_mode ? (int64_t)nb.x : m));
+}
+
+__global__ void pack_points_density_kernel(int64_t n, const float* __restrict__ pts,
+                                           const float* __restrict__ pdf,
+                                           float4* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = make_float4(__ldg(pts + 3 * i), __ldg(pts + 3 * i + 1), __ldg(pts + 3 * i + 2),
+                       1.0f / __ldg(pdf + i));
+}
+
 // WIDE: rows are 32-byte aligned, 256-bit accesses are allowed.
 template <int D, int K, bool WIDE>
 __global__ void __launch_bounds__(kKbThreads)
@@ -68,8 +100,7 @@ kernel_basis_kernel(int64_t M, const float* __restrict__ p_in, const float* __re
        m += (int64_t)gridDim.x * kKbThreads) {
     const int2 nb = __ldg(neigh + m);
     float diff[D];
-    pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
-    const float inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
+    const float inv_pdf = pair_inputs<D>(p_in, p_out, pdf, nb, m, inv_radius, pdf_by_nbr, diff);
     float* dst = basis + m * K;
     uint4 pr[K / 4];   // hi chunks, then mid chunks, of the bf16 pair
 #pragma unroll
@@ -138,8 +169,7 @@ kernel_basis_grads_kernel(int64_t M, const float* __restrict__ p_in,
        m += (int64_t)gridDim.x * kKbThreads) {
     const int2 nb = __ldg(neigh + m);
     float diff[D];
-    pair_diff<D>(p_in, p_out, nb, inv_radius, diff);
-    const float inv_pdf = 1.0f / __ldg(pdf + (pdf_by_nbr ? (int64_t)nb.x : m));
+    const float inv_pdf = pair_inputs<D>(p_in, p_out, pdf, nb, m, inv_radius, pdf_by_nbr, diff);
     const float* src = dbasis + m * K + k0;
 #pragma unroll
     for (int q = 0; q < KT / 8; ++q) {
@@ -301,6 +331,28 @@ int check_kb_args(const char* op, int D, int K, int64_t M, int act) {
 
 using namespace tfgpc;
 
+static int check_pdf_mode(const char* op, int D, int mode, const float* points_in) {
+  TFGPC_REQUIRE(mode >= 0 && mode <= 2, "%s expects pdf_by_neighbor 0, 1 or 2", op);
+  TFGPC_REQUIRE(mode != 2 || (D == 3 && (uintptr_t)points_in % 16 == 0),
+                "%s: the packed point table (pdf_by_neighbor 2) needs D == 3 and 16-byte alignment",
+                op);
+  return TFGPC_OK;
+}
+
+extern "C" int tfgpc_pack_points_density(void* stream, int64_t n, const float* points,
+                                         const float* pdf, float* packed_out) {
+  TFGPC_REQUIRE(n >= 0 && n < (int64_t)INT32_MAX, "PackPointsDensity expects 0 <= n < 2^31");
+  if (n == 0) return TFGPC_OK;
+  TFGPC_REQUIRE(points && pdf && packed_out, "PackPointsDensity got a null pointer");
+  TFGPC_REQUIRE((uintptr_t)packed_out % 16 == 0, "PackPointsDensity expects a 16-byte aligned output");
+  cudaStream_t st = (cudaStream_t)stream;
+  ProfScope prof(st, "pack_points_density");
+  pack_points_density_kernel<<<blocks_for(n, 256), 256, 0, st>>>(n, points, pdf,
+                                                               (float4*)packed_out);
+  TFGPC_LAUNCH_CHECK();
+  return TFGPC_OK;
+}
+
 static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float* points_in,
                              const float* points_out, const int32_t* neighbors, const float* pdf,
                              const float* w1, const float* b1, float inv_radius, int activation,
@@ -309,8 +361,10 @@ static int kernel_basis_impl(void* stream, int D, int K, int64_t M, const float*
   int rc = check_kb_args("KernelBasis", D, K, M, activation);
   if (rc) return rc;
   if (M == 0) return TFGPC_OK;
-  TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && (basis_out || pair_out),
-                "KernelBasis got a null pointer");
+  TFGPC_REQUIRE(points_in && points_out && neighbors && (pdf || pdf_by_nbr == 2) && w1 && b1 &&
+                (basis_out || pair_out), "KernelBasis got a null pointer");
+  rc = check_pdf_mode("KernelBasis", D, pdf_by_nbr, points_in);
+  if (rc) return rc;
   TFGPC_REQUIRE((uintptr_t)basis_out % 16 == 0 && (uintptr_t)pair_out % 32 == 0,
                 "KernelBasis expects 16-byte aligned outputs (32 for the bf16 pair)");
   cudaStream_t st = (cudaStream_t)stream;
@@ -364,8 +418,10 @@ extern "C" int tfgpc_kernel_basis_grads(void* stream, int D, int K, int64_t M,
   TFGPC_CUDA(cudaMemsetAsync(dw1_out, 0, sizeof(float) * (size_t)D * K, st));
   TFGPC_CUDA(cudaMemsetAsync(db1_out, 0, sizeof(float) * (size_t)K, st));
   if (M == 0) return TFGPC_OK;
-  TFGPC_REQUIRE(points_in && points_out && neighbors && pdf && w1 && b1 && basis_grads,
-                "KernelBasisGrads got a null pointer");
+  TFGPC_REQUIRE(points_in && points_out && neighbors && (pdf || pdf_by_neighbor == 2) && w1 &&
+                b1 && basis_grads, "KernelBasisGrads got a null pointer");
+  rc = check_pdf_mode("KernelBasisGrads", D, pdf_by_neighbor, points_in);
+  if (rc) return rc;
   TFGPC_REQUIRE((uintptr_t)basis_grads % 16 == 0,
                 "KernelBasisGrads expects 16-byte aligned gradients");
   const int kt = K < kKTile ? K : kKTile;

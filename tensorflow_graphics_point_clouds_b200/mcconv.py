@@ -156,13 +156,28 @@ def blocks_of_dense_grad(dw_dense, num_mlps, cin, hidden):
   return torch.stack(out, dim=0)
 
 
+def pack_points_density(points, pdf):
+  """[n, 4] table (x, y, z, 1 / density) of a 3-D cloud and its per-point
+  densities (tfgpc_pack_points_density): points_in of the kernel-basis entries
+  with pdf_by_neighbor=2."""
+  points, pdf = _f32(points), _f32(pdf).reshape(-1)
+  n = points.shape[0]
+  if points.shape[1] != 3 or pdf.shape[0] != n:
+    raise _lib.TfgpcError(1, "PackPointsDensity expects [n, 3] points and [n] densities")
+  out = torch.empty((n, 4), dtype=torch.float32, device=points.device)
+  _lib.check(_lib.lib().tfgpc_pack_points_density(_stream(), c_i64(n), ptr(points), ptr(pdf),
+                                                  ptr(out)))
+  return out
+
+
 def kernel_basis(points_in, points_out, neighbors, pdf, w1, b1, radius, activation=0,
                  alpha=0.2, pdf_by_neighbor=False):
   """basis[m, k] = act(diff_m . w1[:, k] + b1[k]) / pdf[m] (tfgpc_kernel_basis).
   w1 [D, K], b1 [K]; neighbors hold (index into points_in, index into points_out).
   pdf_by_neighbor: pdf is a table with one density per point of points_in, read
   at the pair's neighbor index, instead of the per-pair array."""
-  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  points_in, points_out = _f32(points_in), _f32(points_out)
+  pdf = None if pdf is None else _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
   d, k = w1.shape
   m = neighbors.shape[0]
@@ -179,7 +194,8 @@ def kernel_basis_split(points_in, points_out, neighbors, pdf, w1, b1, radius, ac
   """kernel_basis that returns every row as the bf16 (hi, mid) pair the
   tensor-core kernels multiply with: (basis [M, K] float32 or None, pair
   [M, 2, K] bf16)."""
-  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  points_in, points_out = _f32(points_in), _f32(points_out)
+  pdf = None if pdf is None else _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
   d, k = w1.shape
   m = neighbors.shape[0]
@@ -275,7 +291,8 @@ def kernel_mlp_grads(points_in, points_out, neighbors, pdf, weights, biases, rad
 def kernel_basis_grads(points_in, points_out, neighbors, pdf, w1, b1, radius, basis_grads,
                        activation=0, alpha=0.2, pdf_by_neighbor=False):
   """Gradients of kernel_basis with respect to w1 and b1 (tfgpc_kernel_basis_grads)."""
-  points_in, points_out, pdf = _f32(points_in), _f32(points_out), _f32(pdf)
+  points_in, points_out = _f32(points_in), _f32(points_out)
+  pdf = None if pdf is None else _f32(pdf)
   w1, b1, neighbors = _f32(w1), _f32(b1).reshape(-1), _i32(neighbors)
   basis_grads = _f32(basis_grads)
   d, k = w1.shape
@@ -354,14 +371,18 @@ class MCConv:
     grouped = (one_layer and self.grouped and neigh._neighbors.shape[0] > 0 and
                self.cout >= 128 and
                _lib.lib().tfgpc_mcconv_grouped_supported(c_int(self.k), c_int(self.cin)) != 0)
+    # (points, 1 / density) as one 16-byte row per point: one gather per pair
+    kb_in, kb_pdf, kb_mode = p_in, pdf, int(by_nbr)
+    if one_layer and by_nbr and self.dims == 3:
+      kb_in, kb_pdf, kb_mode = pack_points_density(p_in, pdf), None, 2
     if grouped:
       # the basis only as the bf16 pair the tensor-core kernels read
-      basis, pair = kernel_basis_split(p_in, p_out, ids, pdf, w1, b1, radius, self.activation,
-                                       self.alpha, want_fp32=False, pdf_by_neighbor=by_nbr)
+      basis, pair = kernel_basis_split(kb_in, p_out, ids, kb_pdf, w1, b1, radius, self.activation,
+                                       self.alpha, want_fp32=False, pdf_by_neighbor=kb_mode)
       self._grouped = (pair,) + group_plan(neigh)
     elif one_layer:
-      basis = kernel_basis(p_in, p_out, ids, pdf, w1, b1, radius, self.activation, self.alpha,
-                           pdf_by_neighbor=by_nbr)
+      basis = kernel_basis(kb_in, p_out, ids, kb_pdf, w1, b1, radius, self.activation, self.alpha,
+                           pdf_by_neighbor=kb_mode)
       self._grouped = None
     else:
       basis = kernel_mlp_basis(p_in, p_out, ids, pdf, self.kernel_weights, self.kernel_biases,
@@ -380,6 +401,7 @@ class MCConv:
       self._saved = (neigh, point_cloud_in, point_cloud_out, radius, pdf, basis,
                      _f32(features), wd, w1, b1)
       self._pdf_by_nbr = by_nbr
+      self._kb_inputs = (kb_in, kb_pdf, kb_mode)
     return out
 
   def saved_basis(self):
@@ -417,8 +439,9 @@ class MCConv:
       dws, dbs = res[0], res[1]
       head = (dfeat, dws if self._list_form else dws[0], dbs if self._list_form else dbs[0], dwf)
       return head + tuple(res[2:]) if point_grads else head
-    dw1, db1 = kernel_basis_grads(pc_in._points, pc_out._points, ids, pdf, w1, b1, radius, dbasis,
-                                  self.activation, self.alpha, pdf_by_neighbor=self._pdf_by_nbr)
+    kb_in, kb_pdf, kb_mode = self._kb_inputs
+    dw1, db1 = kernel_basis_grads(kb_in, pc_out._points, ids, kb_pdf, w1, b1, radius, dbasis,
+                                  self.activation, self.alpha, pdf_by_neighbor=kb_mode)
     dw1 = dw1.reshape(self.dims, self.num_mlps, self.hidden).permute(1, 0, 2).contiguous()
     db1 = db1.reshape(self.num_mlps, 1, self.hidden)
     if self._list_form:

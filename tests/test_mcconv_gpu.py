@@ -270,3 +270,38 @@ def test_pdf_point_grads_follow_the_reference_chain(own):
   ref = np.empty_like(ref_sorted)
   ref[g_ref.sorted_indices] = ref_sorted
   close(got, ref)
+
+
+@pytest.mark.parametrize("act,alpha", [(0, 0.2), (1, 0.0)])
+def test_kernel_basis_packed_point_table(act, alpha):
+  """points_in as the packed (x, y, z, 1 / density) table gives the results of
+  the density table read at the neighbor index: the basis (fp32 rows and bf16
+  pair) bit for bit, the weight gradients up to the order of their atomic sums."""
+  rng = np.random.default_rng(41)
+  n, ns, m, k = 5000, 900, 40000, 16
+  p_in = t(rng.uniform(0, 1, (n, 3)).astype(np.float32))
+  p_out = t(rng.uniform(0, 1, (ns, 3)).astype(np.float32))
+  nbrs = t(np.stack([rng.integers(0, n, m), np.sort(rng.integers(0, ns, m))], 1).astype(np.int32))
+  pdf = t(rng.uniform(0.5, 30.0, n).astype(np.float32))
+  w1 = t(rng.standard_normal((3, k)).astype(np.float32))
+  b1 = t(rng.standard_normal(k).astype(np.float32))
+  packed = mcconv.pack_points_density(p_in, pdf)
+  assert torch.equal(packed[:, :3], p_in) and torch.equal(packed[:, 3], 1.0 / pdf)
+  ref, ref_pair = mcconv.kernel_basis_split(p_in, p_out, nbrs, pdf, w1, b1, 0.3, act, alpha,
+                                            pdf_by_neighbor=1)
+  got, got_pair = mcconv.kernel_basis_split(packed, p_out, nbrs, None, w1, b1, 0.3, act, alpha,
+                                            pdf_by_neighbor=2)
+  assert torch.equal(got, ref) and torch.equal(got_pair.view(torch.int16), ref_pair.view(torch.int16))
+  assert torch.equal(mcconv.kernel_basis(packed, p_out, nbrs, None, w1, b1, 0.3, act, alpha,
+                                         pdf_by_neighbor=2), ref)
+  dbasis = t(rng.standard_normal((m, k)).astype(np.float32))
+  dw_ref, db_ref = mcconv.kernel_basis_grads(p_in, p_out, nbrs, pdf, w1, b1, 0.3, dbasis, act,
+                                             alpha, pdf_by_neighbor=1)
+  dw, db = mcconv.kernel_basis_grads(packed, p_out, nbrs, None, w1, b1, 0.3, dbasis, act, alpha,
+                                     pdf_by_neighbor=2)
+  close(dw.cpu().numpy(), dw_ref.cpu().numpy(), 1e-5)
+  close(db.cpu().numpy(), db_ref.cpu().numpy(), 1e-5)
+  # the packed table exists for D = 3 only
+  with pytest.raises(mcconv._lib.TfgpcError):
+    mcconv.kernel_basis(packed[:, :2].contiguous(), p_out[:, :2].contiguous(), nbrs, None,
+                        w1[:2].contiguous(), b1, 0.3, act, alpha, pdf_by_neighbor=2)

@@ -66,9 +66,14 @@ def _worker(rank, world, port, result_dir):
                                     d_out[mask], w1, b1, wf, e - b, 0.25)
     g = [torch.from_numpy(d_wf.copy())]
     tdist.allreduce_sum_(g)
+    # cell counts of the whole batch = maximum of the shards' counts
+    from oracle import pylib_ref as pr
+    own = pr.Grid(pts[mask], local_bid.numpy().astype(np.int32), e - b, 0.25).num_cells
+    cells = tdist.allreduce_max_(torch.from_numpy(np.asarray(own, np.int32).copy()))
     slowest = tdist.max_over_ranks(float(rank + 1), "cpu")
     np.savez(os.path.join(result_dir, "rank%d.npz" % rank), out=out, d_feat=d_feat,
-             d_wf=g[0].numpy(), mask=mask, slowest=slowest)
+             d_wf=g[0].numpy(), mask=mask, slowest=slowest, cells=cells.numpy(),
+             own_cells=np.asarray(own, np.int32))
   finally:
     dist.destroy_process_group()
 
@@ -81,7 +86,11 @@ def test_two_rank_allreduce_equals_single_process(tmp_path):
   ref_out, ref_dfeat, ref_dwf = layer_grads(pts, bid, feat, d_out, w1, b1, wf, clouds, 0.25)
   outs = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
   full_out = np.zeros_like(ref_out); full_df = np.zeros_like(ref_dfeat)
+  from oracle import pylib_ref as pr
+  batch_cells = np.asarray(pr.Grid(pts, bid, clouds, 0.25).num_cells)
+  assert np.array_equal(np.maximum(outs[0]["own_cells"], outs[1]["own_cells"]), batch_cells)
   for o in outs:
+    assert np.array_equal(o["cells"], batch_cells)
     full_out[o["mask"]] = o["out"]
     full_df[o["mask"]] = o["d_feat"]
     assert o["slowest"] == float(world)
