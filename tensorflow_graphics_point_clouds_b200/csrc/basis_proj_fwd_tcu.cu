@@ -143,66 +143,66 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
 
   if (warp < kProdWarps) {
     // ------------------------------------------------------------- producers
-    // warp w owns rows 16 w .. 16 w + 15 of every block of 128 rows.  The plan
-    // entries of block i+1 are fetched into registers while the copies of block i
-    // are issued; every copy signals the consumer's barrier when it lands.
-    const int row_base = warp * 16;
-    // F: lanes 0-15 copy row `it`, lanes 16-31 row `it + 8` of the warp's 16;
-    // lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
+    // warp w owns the rows r with r % 8 == w of every block (a group's rows fill
+    // the first ceil(rows / 16) steps of 16 rows, so all eight warps get the same
+    // share of them, however few rows the group has).  The plan entries of block
+    // i+1 are fetched into registers while the copies of block i are issued;
+    // every copy signals the consumer's barrier when it lands.
+    // F: in iteration `it` lanes 0-15 copy row 16 it + w, lanes 16-31 row
+    // 16 it + 8 + w; lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
     const int l4 = lane >> 4, part = (lane >> 3) & 1, j = lane & 7;
+    const int frow = 8 * l4 + warp;                 // this lane's row in iteration 0
     const __nv_bfloat16* const fs_lane = fs + part * kC + j * 8;
-    const uint32_t f_dst_lane = part * kPart + (row_base + 8 * l4) * 128;
-    // Bx: lane -> (row lane / 2 of the warp's 16, slots 2 (lane % 2) and 2 (lane % 2) + 1)
-    const int brow = lane >> 1, bq0 = 2 * (lane & 1);
+    // (row % 8 == warp: the swizzle term is a constant)
+    const uint32_t f_dst_lane = part * kPart + frow * 128 + ((j ^ warp) << 4);
+    // Bx: the same rows; lane -> (slot q, chunk c4 = part * 2 + half of the 16 functions)
+    const int bq = (lane >> 2) & 3, c4 = lane & 3;
+    const __nv_bfloat16* const bp_lane = basis_pair + (c4 >> 1) * kK + (c4 & 1) * 8;
+    const uint32_t bx_dst_lane = (c4 >> 1) * kPart + frow * 128 + (((2 * bq + (c4 & 1)) ^ warp) << 4);
     uint32_t item = 0;
     UWalk walk;
     walk.init(group_begin, group_rows, groups);
-    // plan entries of the next block: the ids of this lane's eight rows (the plan
-    // starts every group on a multiple of four rows: 16-byte loads) and the pair
-    // indices of its two slots
-    int left_n = 0;
-    int4 ida_n = make_int4(0, 0, 0, 0), idb_n = ida_n;
-    int2 pr_n = make_int2(-1, -1);
+    // plan entries of the next block: the ids of this lane's (up to) eight rows and
+    // the pair indices of its two slots
+    int rows_n = 0;
+    int ids_n[8], pr_n[8];
     auto prefetch = [&]() {
-      const int r0 = walk.t.ra + walk.b * kRows + row_base;        // first row of this warp
-      left_n = walk.t.rows - walk.b * kRows - row_base;             // rows of the warp that exist (may be <= 0)
-      const int4* idp = reinterpret_cast<const int4*>(rows_id + r0 + 8 * l4);
-      ida_n = idb_n = make_int4(0, 0, 0, 0);
-      if (8 * l4 < left_n) ida_n = __ldg(idp);
-      if (8 * l4 + 4 < left_n) idb_n = __ldg(idp + 1);
-      pr_n = make_int2(-1, -1);
-      if (brow < left_n)
-        pr_n = __ldg(reinterpret_cast<const int2*>(rows_pair + r0 + brow) + (lane & 1));
+      const int r0 = walk.t.ra + walk.b * kRows;                    // first row of the block
+      rows_n = min(kRows, walk.t.rows - walk.b * kRows);           // rows of the block that exist
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const bool have = 16 * it + frow < rows_n;
+        ids_n[it] = have ? __ldg(rows_id + r0 + 16 * it + frow) : 0;
+        pr_n[it] = have ? __ldg(reinterpret_cast<const int32_t*>(rows_pair + r0 + 16 * it + frow) + bq)
+                        : -1;
+      }
     };
     if (walk.valid) prefetch();
     TT_DECL
     while (walk.valid) {
       TT_MARK(tp0)
-      const int left = left_n;
-      const int ids[8] = {ida_n.x, ida_n.y, ida_n.z, ida_n.w, idb_n.x, idb_n.y, idb_n.z, idb_n.w};
-      const int2 pr = pr_n;
+      const int rows = rows_n;
+      const int rows16 = (rows + 15) & ~15;     // the MMAs read whole steps of 16 rows
+      int ids[8], pr[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
       walk.advance();
       if (walk.valid) prefetch();
       TT_MARK(tp1)
       TT_ADD(2, tp1 - tp0);
-      // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  The MMAs read
-      // whole steps of 16 rows, which are exactly one warp's rows: a warp with at
-      // least one row zero-fills the rest of its 16, a warp without rows copies
-      // nothing (its step is never read).  (An id beyond the group's rows may be
-      // anything: it is only used as the address of a copy of zero bytes, so it is
-      // replaced by 0.)
+      // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  Rows between
+      // the group's last row and the end of its last step are zero-filled (their
+      // id was replaced by 0: it is only the address of a copy of zero bytes).
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         const uint32_t unit = (2 * item + kb) % kUnits;
         TT_WAIT(0, smem_u32(&bars->f_empty[unit]), (((2 * item + kb) / kUnits) & 1) ^ 1);
         const uint32_t base = smem_u32(f_ring + (size_t)unit * kUnitBytes) + f_dst_lane;
-        const int nv = left - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-          // row row_base + 8 * l4 + it: (row % 8) == it, the swizzle is a constant
-          if (left > 0)
-            cp_async16_zfill(base + it * 128 + ((j ^ it) << 4),
-                             fs_lane + (int64_t)(it < nv ? ids[it] : 0) * 2 * kC + kb * 64, it < nv);
+          if (16 * it < rows16)
+            cp_async16_zfill(base + it * (16 * 128),
+                             fs_lane + (int64_t)ids[it] * 2 * kC + kb * 64, 16 * it + frow < rows);
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
                      ::"r"(smem_u32(&bars->f_full[unit])) : "memory");
@@ -213,18 +213,13 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       {
         const uint32_t stage = item & 1;
         TT_WAIT(1, smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1);
-        const int r = row_base + brow;
-        const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + r * 128;
-        if (left > 0) {
+        const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + bx_dst_lane;
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int m = u == 0 ? pr.x : pr.y;
-            const __nv_bfloat16* src = basis_pair + (int64_t)(m < 0 ? 0 : m) * (2 * kK);
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4)   // (hi | mid part, half of the 16 basis functions)
-              cp_async16_zfill(base + (c4 >> 1) * kPart + (((2 * (bq0 + u) + (c4 & 1)) ^ (r & 7)) << 4),
-                               src + (c4 >> 1) * kK + (c4 & 1) * 8, m >= 0);
-          }
+        for (int it = 0; it < 8; ++it) {
+          const int m = pr[it];
+          if (16 * it < rows16)
+            cp_async16_zfill(base + it * (16 * 128),
+                             bp_lane + (int64_t)(m < 0 ? 0 : m) * (2 * kK), m >= 0);
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
                      ::"r"(smem_u32(&bars->bx_full[stage])) : "memory");

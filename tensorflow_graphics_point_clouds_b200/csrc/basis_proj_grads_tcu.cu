@@ -160,49 +160,56 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
 
   if (warp < kProdWarps) {
     // ------------------------------------------------------------- producers
-    // warp w owns rows 16 w .. 16 w + 15 of every block.  The plan entries of
-    // block i+1 are fetched into registers while the copies of block i are issued.
-    const int row_base = warp * 16;
-    // F: lanes 0-15 copy row `it`, lanes 16-31 row `it + 8` of the warp's 16;
-    // lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
+    // warp w owns the rows r with r % 8 == w of every block: a group's rows fill
+    // the first rows of a block, so all eight warps get the same share of them,
+    // however few the group has.  The plan entries of block i+1 are fetched into
+    // registers while the copies of block i are issued.
+    // F: in iteration `it` lanes 0-15 copy row 16 it + w, lanes 16-31 row
+    // 16 it + 8 + w; lane -> (hi | mid part, 16-byte chunk j of the 64-channel block)
     const int l4 = lane >> 4, part = (lane >> 3) & 1, j = lane & 7;
-    const int idx_row = (lane & 7) + 8 * l4;
+    const int frow = 8 * l4 + warp;                 // this lane's row in iteration 0
     const __nv_bfloat16* const fs_lane = fs + part * kC + j * 8;
-    const uint32_t f_dst_lane = part * kPart + (row_base + 8 * l4) * 128;
-    // Bx: per step two rows (lane / 16), lane -> (slot q, chunk c4 = part * 2 + half)
+    // (row % 8 == warp: the swizzle term is a constant)
+    const uint32_t f_dst_lane = part * kPart + frow * 128 + ((j ^ warp) << 4);
+    // Bx: the same rows; lane -> (slot q, chunk c4 = part * 2 + half of the 16 functions)
     const int bq = (lane >> 2) & 3, c4 = lane & 3;
     const __nv_bfloat16* const bp_lane = basis_pair + (c4 >> 1) * kK + (c4 & 1) * 8;
+    const uint32_t bx_dst_lane = (c4 >> 1) * kPart + frow * 128 + (((2 * bq + (c4 & 1)) ^ warp) << 4);
     uint32_t unit = 0, item = 0;
     UWalk walk;
     walk.init(group_begin, group_rows, groups);
-    int left_n = 0, idx_n = 0, pr0_n = -1, pr1_n = -1;
+    int rows_n = 0;
+    int ids_n[8], pr_n[8];
     auto prefetch = [&]() {
-      const int r0 = walk.t.ra + walk.b * kRows + row_base;        // first row of this warp
-      left_n = walk.t.rows - walk.b * kRows - row_base;             // rows of the warp that exist (may be <= 0)
-      idx_n = ((lane & 8) == 0 && idx_row < left_n) ? __ldg(rows_id + r0 + idx_row) : 0;
-      // pair indices of rows 0-7 (pr0) and 8-15 (pr1): lane -> (row lane / 4, slot lane % 4)
-      const int32_t* pp = reinterpret_cast<const int32_t*>(rows_pair + r0);
-      pr0_n = (lane >> 2) < left_n ? __ldg(pp + lane) : -1;
-      pr1_n = 8 + (lane >> 2) < left_n ? __ldg(pp + 32 + lane) : -1;
+      const int r0 = walk.t.ra + walk.b * kRows;                    // first row of the block
+      rows_n = min(kRows, walk.t.rows - walk.b * kRows);           // rows of the block that exist
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const bool have = 16 * it + frow < rows_n;
+        ids_n[it] = have ? __ldg(rows_id + r0 + 16 * it + frow) : 0;
+        pr_n[it] = have ? __ldg(reinterpret_cast<const int32_t*>(rows_pair + r0 + 16 * it + frow) + bq)
+                        : -1;
+      }
     };
     if (walk.valid) prefetch();
     while (walk.valid) {
-      const int left = left_n, my_idx = idx_n, pr0 = pr0_n, pr1 = pr1_n;
+      const int rows = rows_n;
+      const int rows16 = (rows + 15) & ~15;   // rows the MMAs of the dfeat product read
+      int ids[8], pr[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
       walk.advance();
       if (walk.valid) prefetch();
-      // ---- F: two 64-channel blocks
+      // ---- F: two 64-channel blocks (rows beyond the group's are not read back)
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb, ++unit) {
         const uint32_t slot = unit % kSlots;
         mbar_wait(smem_u32(&bars->f_empty[slot]), ((unit / kSlots) & 1) ^ 1, abort_flag, err_flag);
         const uint32_t base = smem_u32(f_ring + (size_t)slot * kSlotBytes) + f_dst_lane;
-        const int nv = left - 8 * l4;   // this lane's rows `it` with it < nv exist
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-          const int idx = __shfl_sync(0xffffffffu, my_idx, it, 16);
-          // row row_base + 8 * l4 + it: (row % 8) == it, the swizzle is a constant
-          if (it < nv)
-            cp_async16(base + it * 128 + ((j ^ it) << 4), fs_lane + (int64_t)idx * 2 * kC + kb * 64);
+          if (16 * it + frow < rows)
+            cp_async16(base + it * (16 * 128), fs_lane + (int64_t)ids[it] * 2 * kC + kb * 64);
         }
         // arrives on the slot's barrier once this thread's copies have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
@@ -212,14 +219,13 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
       {
         const uint32_t stage = item & 1;
         mbar_wait(smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
-        const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + (c4 >> 1) * kPart;
+        const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + bx_dst_lane;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-          const int row16 = 2 * it + l4;                 // row of the warp's 16
-          const int m = __shfl_sync(0xffffffffu, it < 4 ? pr0 : pr1, 4 * (row16 & 7) + bq);
-          const int r = row_base + row16;
-          cp_async16_zfill(base + r * 128 + (((2 * bq + (c4 & 1)) ^ (r & 7)) << 4),
-                           bp_lane + (int64_t)(m < 0 ? 0 : m) * (2 * kK), m >= 0);
+          const int m = pr[it];
+          if (16 * it < rows16)
+            cp_async16_zfill(base + it * (16 * 128),
+                             bp_lane + (int64_t)(m < 0 ? 0 : m) * (2 * kK), m >= 0);
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
                      ::"r"(smem_u32(&bars->bx_full[stage])) : "memory");
