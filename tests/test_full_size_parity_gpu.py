@@ -91,6 +91,14 @@ def test_uniform_clouds_layer_neighborhood():
   same(nb._neighbors, nb_ref.neighbors)
   same(nb._original_neigh_ids, nb_ref.original_neigh_ids)
   close(nb.get_pdf(bandwidth=0.2, mode=0).cpu().numpy(), nb_ref.get_pdf(bandwidth=0.2, mode=0))
+  # the same grid and neighborhood from the single call with one blocking read
+  # (what MCConv.build_neighborhood uses)
+  cloud1 = pc.PointCloud(t(pts), t(bid), 32)
+  one = pc.grid_neighborhood(cloud1, radius, cloud1)
+  assert_grid(g_ref, one._grid)
+  same(one._samples_neigh_ranges, nb_ref.ranges)
+  same(one._neighbors, nb_ref.neighbors)
+  same(one._original_neigh_ids, nb_ref.original_neigh_ids)
 
 
 @pytest.mark.parametrize("mode", [0, 1])
