@@ -46,9 +46,11 @@ constexpr uint32_t kBxBytes = 2 * kPart;
 constexpr uint32_t kTmemCols = 128;    // two accumulators of 64 columns
 constexpr size_t kSmemBytes = (size_t)kUnits * kUnitBytes + 2 * kBxBytes + 1024 + 256;
 
+// One pair of barriers per block-sized slot (two ring units of features and one
+// Bx stage): the MMA-issuing thread, which is what bounds this kernel, then waits
+// once and commits once per block.
 struct Barriers {
-  uint64_t f_full[kUnits], f_empty[kUnits];
-  uint64_t bx_full[2], bx_empty[2];
+  uint64_t slot_full[2], slot_empty[2];
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -121,13 +123,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kUnits; ++i) {
-      mbar_init(smem_u32(&bars->f_full[i]), kProdWarps * 32);
-      mbar_init(smem_u32(&bars->f_empty[i]), 1);
-    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bars->bx_full[i]), kProdWarps * 32);
-      mbar_init(smem_u32(&bars->bx_empty[i]), 1);
+      mbar_init(smem_u32(&bars->slot_full[i]), kProdWarps * 32);
+      mbar_init(smem_u32(&bars->slot_empty[i]), 1);
       mbar_init(smem_u32(&bars->acc_full[i]), 1);
       mbar_init(smem_u32(&bars->acc_empty[i]), 8);
     }
@@ -193,10 +191,11 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  Rows between
       // the group's last row and the end of its last step are zero-filled (their
       // id was replaced by 0: it is only the address of a copy of zero bytes).
+      const uint32_t stage = item & 1;
+      TT_WAIT(0, smem_u32(&bars->slot_empty[stage]), ((item >> 1) & 1) ^ 1);
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
-        const uint32_t unit = (2 * item + kb) % kUnits;
-        TT_WAIT(0, smem_u32(&bars->f_empty[unit]), (((2 * item + kb) / kUnits) & 1) ^ 1);
+        const uint32_t unit = 2 * stage + kb;
         const uint32_t base = smem_u32(f_ring + (size_t)unit * kUnitBytes) + f_dst_lane;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -204,15 +203,11 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
             cp_async16_zfill(base + it * (16 * 128),
                              fs_lane + (int64_t)ids[it] * 2 * kC + kb * 64, 16 * it + frow < rows);
         }
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
-                     ::"r"(smem_u32(&bars->f_full[unit])) : "memory");
       }
       TT_MARK(tp2)
       TT_ADD(3, tp2 - tp1);
       // ---- Bx: the basis rows of the plan's pairs, zeros where there is none
       {
-        const uint32_t stage = item & 1;
-        TT_WAIT(1, smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1);
         const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + bx_dst_lane;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -221,8 +216,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
             cp_async16_zfill(base + it * (16 * 128),
                              bp_lane + (int64_t)(m < 0 ? 0 : m) * (2 * kK), m >= 0);
         }
+        // arrives on the slot's barrier once all of this thread's copies have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];"
-                     ::"r"(smem_u32(&bars->bx_full[stage])) : "memory");
+                     ::"r"(smem_u32(&bars->slot_full[stage])) : "memory");
       }
       ++item;
       TT_MARK(tp3)
@@ -249,12 +245,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
         const uint32_t d = tmem_base + abuf * 64;
         uint32_t accumulate = 0;
         for (int b = 0; b < nb; ++b, ++item) {
-          const uint32_t u0 = (2 * item) % kUnits;          // even: u0 + 1 is the next unit in memory
-          const uint32_t fph = ((2 * item) / kUnits) & 1;
           const uint32_t stage = item & 1;
-          TT_WAIT(1, smem_u32(&bars->f_full[u0]), fph);
-          TT_WAIT(1, smem_u32(&bars->f_full[u0 + 1]), fph);
-          TT_WAIT(2, smem_u32(&bars->bx_full[stage]), (item >> 1) & 1);
+          const uint32_t u0 = 2 * stage;                    // u0 + 1 is the next unit in memory
+          TT_WAIT(1, smem_u32(&bars->slot_full[stage]), (item >> 1) & 1);
           TT_MARK(tm0)
           fence_proxy_async();   // the copied rows were written through the generic proxy
           tc_fence_after();
@@ -279,9 +272,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
           }
           TT_MARK(tm2)
           TT_ADD(4, tm2 - tm1);
-          umma_commit(smem_u32(&bars->f_empty[u0]));
-          umma_commit(smem_u32(&bars->f_empty[u0 + 1]));
-          umma_commit(smem_u32(&bars->bx_empty[stage]));
+          umma_commit(smem_u32(&bars->slot_empty[stage]));   // free once these MMAs have read it
           TT_MARK(tm3)
           TT_ADD(5, tm3 - tm2);
         }
