@@ -326,11 +326,13 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
   } else {
     // -------------------------------------------------------------- epilogue
     // Two warps per quarter of the tensor-memory lanes.  D1 (lanes = rows): warp
-    // half 0 stores, for every slot q in which the row has a pair, the 16 columns
+    // half 1 stores, for every slot q in which the row has a pair, the 16 columns
     // of q as that pair's dbasis row.  D2 (lanes = channels, columns = rows): half
     // h takes the 32-row column blocks h and h + 2; for every row the warp adds
     // its 32 channels to the neighbor's gradient row, 128 contiguous bytes per
-    // instruction.
+    // instruction.  (D1 goes to half 1 because a group of ~67 rows gives half 0
+    // the rows 0-31 and 64-66 and half 1 only the rows 32-63: the reductions, which
+    // share the LSU with the copy warps, are what the accumulators wait for.)
     const int quarter = warp & 3;
     const int half = (warp - kEpiWarp0) >> 2;
     const int r = quarter * 32 + lane;        // this thread's accumulator row
@@ -348,13 +350,13 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
         pts[u] = c < rows ? __ldg(rows_id + r_first + c) : 0;
       }
       int4 pr = make_int4(-1, -1, -1, -1);
-      if (half == 0 && r < rows) pr = __ldg(rows_pair + r_first + r);
+      if (half == 1 && r < rows) pr = __ldg(rows_pair + r_first + r);
       const uint32_t abuf = item & 1;
       mbar_wait(smem_u32(&bars->acc_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
       tc_fence_after();
       const bool ok = !*abort_flag;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + abuf * kAccCols;
-      if (half == 0) {
+      if (half == 1) {
         const int prq[4] = {pr.x, pr.y, pr.z, pr.w};
 #pragma unroll
         for (int q = 0; q < kG; ++q) {
