@@ -512,6 +512,29 @@ def timed_steps(run, steps, barrier, collect_kernels):
   return e0.elapsed_time(e1) / steps, records
 
 
+def bind_near_gpu(index):
+  """Restricts this process to the host cores NVML lists as nearest to GPU `index`
+  (its NUMA node), so that the pinned buffers of the end-to-end variant are first
+  touched there instead of wherever the launcher happened to start the rank.
+  Reads NVML only.  Returns the number of cores kept, or None if nothing changed
+  (no NVML, no NUMA information, or the cores lie outside this process's set)."""
+  try:
+    import pynvml
+    pynvml.nvmlInit()
+    handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+    n = max(os.cpu_count() or 1, max(os.sched_getaffinity(0)) + 1)
+    words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n + 63) // 64)
+    near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+    allowed = os.sched_getaffinity(0)
+    keep = near & allowed
+    if keep and keep != allowed:
+      os.sched_setaffinity(0, keep)
+      return len(keep)
+  except Exception:
+    pass
+  return None
+
+
 def e2e_steps(run, steps, barrier):
   """End to end: every step copies its inputs from pinned host memory and its
   results back to pinned host memory.  The copies run on two copy streams so that
@@ -597,6 +620,8 @@ def run_ours(args, rank, local_rank, world):
       dist.barrier()
       torch.cuda.synchronize()
 
+  # several ranks on one host: keep each near its own GPU before any pinned buffer exists
+  near_cores = bind_near_gpu(local_rank) if world > 1 else None
   strong = args.scaling == "strong"
   full_inputs = make_inputs(args, 0 if strong else rank)
   if strong:
@@ -654,8 +679,11 @@ def run_ours(args, rank, local_rank, world):
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "h2d_gbs_per_rank": [round(float(g[0]), 2) for g in gathered],
            "d2h_gbs_per_rank": [round(float(g[1]), 2) for g in gathered],
+           "host_cores_near_gpu": near_cores,
            "note": "bytes per step are this rank's; GB/s = bytes / the rank's own step time, both "
-                   "directions in flight at once with the kernels"}
+                   "directions in flight at once with the kernels; host_cores_near_gpu: cores "
+                   "rank 0 was bound to before its pinned buffers were allocated (null: no "
+                   "NUMA information, nothing bound)"}
 
   # ---- weak scaling beside a strong multi-GPU run: every rank its own batch
   weak = None
