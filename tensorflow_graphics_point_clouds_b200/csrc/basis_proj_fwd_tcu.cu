@@ -39,18 +39,29 @@ constexpr int kProdWarps = 8;
 constexpr int kMmaWarp = 8;
 constexpr int kEpiWarp0 = 9;
 constexpr int kThreads = 17 * 32;
-constexpr int kUnits = 4;              // ring of 64-channel feature blocks; a block of rows takes two
-constexpr uint32_t kPart = 16384;      // one 128 x 128-byte operand tile (hi or mid)
+#ifndef TFGPC_FWD_SLOTS
+#define TFGPC_FWD_SLOTS 3
+#endif
+// Shared memory holds kSlots block-sized slots (two 64-channel feature units and
+// one Bx stage each).  A block is at most kBlk rows: 96 instead of 128 leaves room
+// for a third slot, i.e. lets the copy warps run two blocks ahead of the MMAs;
+// groups of four samples have ~67 rows at 32 neighbors per point, larger ones take
+// a second block.
+constexpr int kSlots = TFGPC_FWD_SLOTS;
+constexpr int kBlk = kSlots == 3 ? 96 : 128;   // rows per block (a multiple of 16)
+constexpr int kSteps = kBlk / 16;
+constexpr int kUnits = 2 * kSlots;     // 64-channel feature blocks; a block of rows takes two
+constexpr uint32_t kPart = kBlk * 128; // one kBlk x 128-byte operand tile (hi or mid)
 constexpr uint32_t kUnitBytes = 2 * kPart;
 constexpr uint32_t kBxBytes = 2 * kPart;
 constexpr uint32_t kTmemCols = 128;    // two accumulators of 64 columns
-constexpr size_t kSmemBytes = (size_t)kUnits * kUnitBytes + 2 * kBxBytes + 1024 + 256;
+constexpr size_t kSmemBytes = (size_t)kUnits * kUnitBytes + kSlots * kBxBytes + 1024 + 256;
 
 // One pair of barriers per block-sized slot (two ring units of features and one
 // Bx stage): the MMA-issuing thread, which is what bounds this kernel, then waits
 // once and commits once per block.
 struct Barriers {
-  uint64_t slot_full[2], slot_empty[2];
+  uint64_t slot_full[kSlots], slot_empty[kSlots];
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -58,7 +69,7 @@ struct Barriers {
 
 struct UTile {
   int ra, rows;
-  __device__ __forceinline__ int blocks() const { return (rows + kRows - 1) / kRows; }
+  __device__ __forceinline__ int blocks() const { return (rows + kBlk - 1) / kBlk; }
 };
 
 __device__ __forceinline__ UTile load_utile(const int32_t* __restrict__ group_begin,
@@ -118,14 +129,16 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* f_ring = smem;
   uint8_t* bx = f_ring + (size_t)kUnits * kUnitBytes;
-  Barriers* bars = (Barriers*)(bx + 2 * kBxBytes);
+  Barriers* bars = (Barriers*)(bx + kSlots * kBxBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kSlots; ++i) {
       mbar_init(smem_u32(&bars->slot_full[i]), kProdWarps * 32);
       mbar_init(smem_u32(&bars->slot_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->acc_full[i]), 1);
       mbar_init(smem_u32(&bars->acc_empty[i]), 8);
     }
@@ -163,12 +176,12 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
     // plan entries of the next block: the ids of this lane's (up to) eight rows and
     // the pair indices of its two slots
     int rows_n = 0;
-    int ids_n[8], pr_n[8];
+    int ids_n[kSteps], pr_n[kSteps];
     auto prefetch = [&]() {
-      const int r0 = walk.t.ra + walk.b * kRows;                    // first row of the block
-      rows_n = min(kRows, walk.t.rows - walk.b * kRows);           // rows of the block that exist
+      const int r0 = walk.t.ra + walk.b * kBlk;                    // first row of the block
+      rows_n = min(kBlk, walk.t.rows - walk.b * kBlk);           // rows of the block that exist
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
+      for (int it = 0; it < kSteps; ++it) {
         const bool have = 16 * it + frow < rows_n;
         ids_n[it] = have ? __ldg(rows_id + r0 + 16 * it + frow) : 0;
         pr_n[it] = have ? __ldg(reinterpret_cast<const int32_t*>(rows_pair + r0 + 16 * it + frow) + bq)
@@ -181,9 +194,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       TT_MARK(tp0)
       const int rows = rows_n;
       const int rows16 = (rows + 15) & ~15;     // the MMAs read whole steps of 16 rows
-      int ids[8], pr[8];
+      int ids[kSteps], pr[kSteps];
 #pragma unroll
-      for (int it = 0; it < 8; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
+      for (int it = 0; it < kSteps; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
       walk.advance();
       if (walk.valid) prefetch();
       TT_MARK(tp1)
@@ -191,14 +204,14 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       // ---- F: two 64-channel blocks (units 2 item and 2 item + 1).  Rows between
       // the group's last row and the end of its last step are zero-filled (their
       // id was replaced by 0: it is only the address of a copy of zero bytes).
-      const uint32_t stage = item & 1;
-      TT_WAIT(0, smem_u32(&bars->slot_empty[stage]), ((item >> 1) & 1) ^ 1);
+      const uint32_t stage = item % kSlots;
+      TT_WAIT(0, smem_u32(&bars->slot_empty[stage]), ((item / kSlots) & 1) ^ 1);
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         const uint32_t unit = 2 * stage + kb;
         const uint32_t base = smem_u32(f_ring + (size_t)unit * kUnitBytes) + f_dst_lane;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < kSteps; ++it) {
           if (16 * it < rows16)
             cp_async16_zfill(base + it * (16 * 128),
                              fs_lane + (int64_t)ids[it] * 2 * kC + kb * 64, 16 * it + frow < rows);
@@ -210,7 +223,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
       {
         const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + bx_dst_lane;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < kSteps; ++it) {
           const int m = pr[it];
           if (16 * it < rows16)
             cp_async16_zfill(base + it * (16 * 128),
@@ -245,9 +258,9 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
         const uint32_t d = tmem_base + abuf * 64;
         uint32_t accumulate = 0;
         for (int b = 0; b < nb; ++b, ++item) {
-          const uint32_t stage = item & 1;
+          const uint32_t stage = item % kSlots;
           const uint32_t u0 = 2 * stage;                    // u0 + 1 is the next unit in memory
-          TT_WAIT(1, smem_u32(&bars->slot_full[stage]), (item >> 1) & 1);
+          TT_WAIT(1, smem_u32(&bars->slot_full[stage]), (item / kSlots) & 1);
           TT_MARK(tm0)
           fence_proxy_async();   // the copied rows were written through the generic proxy
           tc_fence_after();
@@ -255,7 +268,7 @@ basis_proj_fwd_tcu_kernel(int64_t ns, int64_t groups, const int32_t* __restrict_
           TT_ADD(3, tm1 - tm0);
           const uint32_t f_hi = smem_u32(f_ring + (size_t)u0 * kUnitBytes), f_mid = f_hi + kPart;
           const uint32_t bx_hi = smem_u32(bx + (size_t)stage * kBxBytes), bx_mid = bx_hi + kPart;
-          const int steps = (min(kRows, t.rows - b * kRows) + 15) >> 4;
+          const int steps = (min(kBlk, t.rows - b * kBlk) + 15) >> 4;
           // both operands MN-major: 8 rows (reduction index) per 1024-byte atom, a
           // step of 16 rows is 2048 bytes (128 in the descriptor's 16-byte units);
           // the two 64-channel blocks of A lie one ring unit apart
