@@ -13,7 +13,7 @@
 // With dXcat[c, (q, k)] the concatenated gradients of the group's samples q:
 //   (1) D1[128 rows, 64] = F[rows, 128 c] * dXcat: the 16 columns of slot q are
 //       the dbasis row of the pair through which sample q sees this neighbor;
-//   (2) D2[128 c, 128 rows] = dXcat * Bx^T, Bx[row, (q, k)] = basis row of that
+//   (2) D2[128 c, rows] = dXcat * Bx^T, Bx[row, (q, k)] = basis row of that
 //       pair (zero where sample q does not see the neighbor): column `row` is the
 //       whole group's contribution to dfeat[j], added with ONE reduction.
 // fp32 accuracy comes from the 3-pass bf16 split of both operands.
@@ -26,7 +26,7 @@
 //   dXcat  the operand image the dX GEMM wrote for this group (one 32 KB bulk copy).
 // Roles: warps 0-7 issue the copies (they compute nothing: every copy signals the
 // consumer's barrier when it lands); warps 8 and 9 issue the MMAs of (1) and (2);
-// warp 10 fetches dXcat; warps 11-18 drain the accumulators (double buffered in
+// warp 10 fetches dXcat; warps 11-18 drain the accumulators (three buffers in
 // tensor memory).  Every mbarrier wait is bounded.
 #include "basis_proj_tc.cuh"
 #include "group_plan.cuh"
@@ -44,20 +44,30 @@ constexpr int kMmaWarp = 8;
 constexpr int kDxWarp = 10;
 constexpr int kEpiWarp0 = 11;
 constexpr int kThreads = 19 * 32;
-constexpr int kSlots = 3;
-constexpr uint32_t kPart = 16384;
+// A block is at most kBlk = 96 rows of a group (groups of four samples have ~67
+// rows at 32 neighbors per point; larger ones take a second block): D2 then needs
+// 96 accumulator columns, and THREE accumulator buffers fit tensor memory, so the
+// MMAs run two blocks ahead of the epilogue's reductions instead of one.  The
+// MMAs of D1 still span 128 rows; the 32 beyond a block read whatever follows it
+// in shared memory and their accumulator rows are never read.
+constexpr int kBlk = 96;
+constexpr int kSteps = kBlk / 16;
+constexpr int kAccBufs = 3;
+constexpr int kSlots = 4;
+constexpr uint32_t kPart = kBlk * 128;     // one operand tile of a block (hi or mid)
 constexpr uint32_t kSlotBytes = 2 * kPart;
 constexpr uint32_t kBxBytes = 2 * kPart;
-constexpr uint32_t kDxBytes = 2 * kPart;
+constexpr uint32_t kDxPart = 16384;        // hi (or mid) half of a group's dX image
+constexpr uint32_t kDxBytes = 2 * kDxPart;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kAccCols = 192;     // D1 (64 columns) + D2 (128 columns)
+constexpr uint32_t kAccCols = 64 + kBlk;   // D1 (64 columns) + D2 (one column per row)
 constexpr size_t kSmemBytes = (size_t)kSlots * kSlotBytes + 2 * kBxBytes + 2 * kDxBytes + 1024 + 256;
 
 struct Barriers {
   uint64_t f_full[kSlots], f_empty[kSlots];
   uint64_t bx_full[2], bx_empty[2];
   uint64_t dx_full[2], dx_empty[2];
-  uint64_t acc_full[2], acc_empty[2];
+  uint64_t acc_full[kAccBufs], acc_empty[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -65,7 +75,7 @@ struct Barriers {
 // Rows of one group: [ra, ra + rows).
 struct UTile {
   int ra, rows;
-  __device__ __forceinline__ int blocks() const { return (rows + kRows - 1) / kRows; }
+  __device__ __forceinline__ int blocks() const { return (rows + kBlk - 1) / kBlk; }
 };
 
 __device__ __forceinline__ UTile load_utile(const int32_t* __restrict__ group_begin,
@@ -78,7 +88,7 @@ __device__ __forceinline__ UTile load_utile(const int32_t* __restrict__ group_be
   return t;
 }
 
-// Walk over the (group, 128-row block) items of this CTA with the next group's
+// Walk over the (group, block of kBlk rows) items of this CTA with the next group's
 // descriptor already on its way.
 struct UWalk {
   const int32_t *gb, *gr;
@@ -139,6 +149,8 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
       mbar_init(smem_u32(&bars->bx_empty[i]), 1);
       mbar_init(smem_u32(&bars->dx_full[i]), 1);
       mbar_init(smem_u32(&bars->dx_empty[i]), 2);
+    }
+    for (int i = 0; i < kAccBufs; ++i) {
       mbar_init(smem_u32(&bars->acc_full[i]), 2);
       mbar_init(smem_u32(&bars->acc_empty[i]), 8);
     }
@@ -179,12 +191,12 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
     UWalk walk;
     walk.init(group_begin, group_rows, groups);
     int rows_n = 0;
-    int ids_n[8], pr_n[8];
+    int ids_n[kSteps], pr_n[kSteps];
     auto prefetch = [&]() {
-      const int r0 = walk.t.ra + walk.b * kRows;                    // first row of the block
-      rows_n = min(kRows, walk.t.rows - walk.b * kRows);           // rows of the block that exist
+      const int r0 = walk.t.ra + walk.b * kBlk;                    // first row of the block
+      rows_n = min(kBlk, walk.t.rows - walk.b * kBlk);           // rows of the block that exist
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
+      for (int it = 0; it < kSteps; ++it) {
         const bool have = 16 * it + frow < rows_n;
         ids_n[it] = have ? __ldg(rows_id + r0 + 16 * it + frow) : 0;
         pr_n[it] = have ? __ldg(reinterpret_cast<const int32_t*>(rows_pair + r0 + 16 * it + frow) + bq)
@@ -195,9 +207,9 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
     while (walk.valid) {
       const int rows = rows_n;
       const int rows16 = (rows + 15) & ~15;   // rows the MMAs of the dfeat product read
-      int ids[8], pr[8];
+      int ids[kSteps], pr[kSteps];
 #pragma unroll
-      for (int it = 0; it < 8; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
+      for (int it = 0; it < kSteps; ++it) { ids[it] = ids_n[it]; pr[it] = pr_n[it]; }
       walk.advance();
       if (walk.valid) prefetch();
       // ---- F: two 64-channel blocks (rows beyond the group's are not read back)
@@ -207,7 +219,7 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
         mbar_wait(smem_u32(&bars->f_empty[slot]), ((unit / kSlots) & 1) ^ 1, abort_flag, err_flag);
         const uint32_t base = smem_u32(f_ring + (size_t)slot * kSlotBytes) + f_dst_lane;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < kSteps; ++it) {
           if (16 * it + frow < rows)
             cp_async16(base + it * (16 * 128), fs_lane + (int64_t)ids[it] * 2 * kC + kb * 64);
         }
@@ -221,7 +233,7 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
         mbar_wait(smem_u32(&bars->bx_empty[stage]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
         const uint32_t base = smem_u32(bx + (size_t)stage * kBxBytes) + bx_dst_lane;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < kSteps; ++it) {
           const int m = pr[it];
           if (16 * it < rows16)
             cp_async16_zfill(base + it * (16 * 128),
@@ -245,10 +257,10 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
         if (nb == 0) continue;
         const uint32_t dbuf = tile_i & 1;
         mbar_wait(smem_u32(&bars->dx_full[dbuf]), (tile_i >> 1) & 1, abort_flag, err_flag);
-        const uint32_t dx_hi = smem_u32(dx + (size_t)dbuf * kDxBytes), dx_mid = dx_hi + kPart;
+        const uint32_t dx_hi = smem_u32(dx + (size_t)dbuf * kDxBytes), dx_mid = dx_hi + kDxPart;
         for (int b = 0; b < nb; ++b, ++item) {
-          const uint32_t abuf = item & 1;
-          mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((item >> 1) & 1) ^ 1, abort_flag, err_flag);
+          const uint32_t abuf = item % kAccBufs;
+          mbar_wait(smem_u32(&bars->acc_empty[abuf]), ((item / kAccBufs) & 1) ^ 1, abort_flag, err_flag);
           tc_fence_after();
           const uint32_t d1 = tmem_base + abuf * kAccCols, d2 = d1 + 64;
           if (first) {
@@ -279,13 +291,14 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
             // (2) D2 = dXcat * Bx^T: reduction over the 64 (slot, k) columns.  Only
             // the columns of rows that exist are computed (N in steps of 16): the
             // tensor core reads that much less of Bx from shared memory.
-            const int rows_b = min(kRows, t.rows - b * kRows);
+            const int rows_b = min(kBlk, t.rows - b * kBlk);
             const uint32_t n16 = (uint32_t)((rows_b + 15) & ~15);
             const uint32_t idesc2n = (idesc2 & ~(0x3Fu << 17)) | ((n16 >> 3) << 17);
-            mbar_wait(smem_u32(&bars->bx_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
+            const uint32_t stage = item & 1;
+            mbar_wait(smem_u32(&bars->bx_full[stage]), (item >> 1) & 1, abort_flag, err_flag);
             fence_proxy_async();
             tc_fence_after();
-            const uint32_t bx_hi = smem_u32(bx + (size_t)abuf * kBxBytes), bx_mid = bx_hi + kPart;
+            const uint32_t bx_hi = smem_u32(bx + (size_t)stage * kBxBytes), bx_mid = bx_hi + kPart;
             uint32_t accumulate = 0;
 #pragma unroll
             for (int kk = 0; kk < kG; ++kk) {
@@ -298,7 +311,7 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
               umma_bf16(d2, da_hi, db_hi, idesc2n, 1u);
               accumulate = 1u;
             }
-            umma_commit(smem_u32(&bars->bx_empty[abuf]));
+            umma_commit(smem_u32(&bars->bx_empty[stage]));
           }
           umma_commit(smem_u32(&bars->acc_full[abuf]));
         }
@@ -341,8 +354,8 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
     walk.init(group_begin, group_rows, groups);
     uint32_t item = 0;
     for (; walk.valid; walk.advance(), ++item) {
-      const int r_first = walk.t.ra + walk.b * kRows;
-      const int rows = min(kRows, walk.t.rows - walk.b * kRows);   // rows in this block
+      const int r_first = walk.t.ra + walk.b * kBlk;
+      const int rows = min(kBlk, walk.t.rows - walk.b * kBlk);   // rows in this block
       int pts[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -351,8 +364,8 @@ basis_proj_grads_tcu_kernel(int64_t ns, int64_t M, int64_t groups,
       }
       int4 pr = make_int4(-1, -1, -1, -1);
       if (half == 1 && r < rows) pr = __ldg(rows_pair + r_first + r);
-      const uint32_t abuf = item & 1;
-      mbar_wait(smem_u32(&bars->acc_full[abuf]), (item >> 1) & 1, abort_flag, err_flag);
+      const uint32_t abuf = item % kAccBufs;
+      mbar_wait(smem_u32(&bars->acc_full[abuf]), (item / kAccBufs) & 1, abort_flag, err_flag);
       tc_fence_after();
       const bool ok = !*abort_flag;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + abuf * kAccCols;
@@ -436,8 +449,8 @@ int basis_proj_grads_tcu(cudaStream_t st, int64_t ns, int64_t M, const void* pla
   kern<<<grid, kThreads, kSmemBytes, st>>>(ns, M, v.groups, v.group_begin, v.group_rows, v.rows_id,
                                            v.rows_pair, basis_pair, fs, ranges,
                                            (const uint8_t*)image, dbasis, dfeat,
-                                           make_idesc(kRows, 16 * kG, false, true),
-                                           make_idesc(kRows, kC, false, false), err_flag);
+                                           make_idesc(128, 16 * kG, false, true),
+                                           make_idesc(kC, 128, false, false), err_flag);
   TFGPC_LAUNCH_CHECK();
   return TFGPC_OK;
 }
