@@ -108,7 +108,7 @@ extern "C" int tfgpc_read_device(void* stream, const void* device_src, size_t by
 }
 
 extern "C" const char* tfgpc_last_error(void) { return tfgpc::g_err; }
-extern "C" int tfgpc_version(void) { return 1; }
+extern "C" int tfgpc_version(void) { return 2; }   // 2: pdf_by_neighbor on the kernel-basis entries
 
 extern "C" int tfgpc_profile_enable(int on) {
   tfgpc::g_prof_on = on != 0;
