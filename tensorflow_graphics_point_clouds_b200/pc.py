@@ -275,6 +275,7 @@ class Neighborhood:
 # and sort keys for, per (dimension, batch size): it starts at 64 and is raised
 # to what a grid asked for when one did not fit.
 _MAX_CELLS = {}
+_ONE_CALL_CELLS_LIMIT = 1024
 
 
 def grid_neighborhood(point_cloud, radius, point_cloud_sample=None, max_neighbors=0):
@@ -321,7 +322,12 @@ def grid_neighborhood(point_cloud, radius, point_cloud_sample=None, max_neighbor
       asked = max(getattr(err, 'num_cells', [0]))
       if err.code != 3 or asked <= max_cells:
         raise
-      max_cells = min(4096, 1 << (asked - 1).bit_length())
+      bigger = 1 << (asked - 1).bit_length()
+      if bigger > _ONE_CALL_CELLS_LIMIT or pc._batch_size * float(bigger) ** d >= 4e18:
+        # a grid this fine would make the call's fixed-size tube array (or its sort
+        # keys) too large: the separate constructors size both exactly
+        return Neighborhood(Grid(pc, radius), radius, point_cloud_sample, max_neighbors)
+      max_cells = bigger
       _MAX_CELLS[key] = max_cells
   grid = object.__new__(Grid)
   grid._point_cloud = pc

@@ -533,6 +533,15 @@ def test_grid_neighborhood_repeats_with_larger_bound():
   assert_grid_equal(g_ref, nb._grid)
   assert_neigh_equal(pr.Neighborhood(g_ref, 0.004), nb)
   pc._MAX_CELLS.pop((2, 2), None)
+  # a grid finer than the one-call form sizes for: the separate constructors take over
+  pts1, bid1 = random_cloud(rng, 1, 3000, 2)
+  cloud1 = pc.PointCloud(t(pts1), t(bid1), 1)
+  nb1 = pc.grid_neighborhood(cloud1, 0.0006, cloud1)
+  g1_ref = pr.Grid(pts1, bid1, 1, 0.0006)
+  assert max(g1_ref.num_cells) > pc._ONE_CALL_CELLS_LIMIT
+  assert_grid_equal(g1_ref, nb1._grid)
+  assert_neigh_equal(pr.Neighborhood(g1_ref, 0.0006, pts1, bid1), nb1)
+  assert (2, 1) not in pc._MAX_CELLS or pc._MAX_CELLS[(2, 1)] <= pc._ONE_CALL_CELLS_LIMIT
 
 
 def test_grid_neighborhood_one_call_with_reduced_cell_counts():
